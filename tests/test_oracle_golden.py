@@ -1,0 +1,228 @@
+"""Pin the CPU oracle to fixtures produced by the reference itself (tests/golden/make_golden.py).
+
+These mirror the reference's own planner tests (tests/test_pd.py:56-115), its CPU
+transport simulation (tests/test_stage_engine.py:118-126) and its finalize tests
+(tests/test_kv_cache.py:38-58, tests/test_fp8_kv_cache.py:141-152).
+"""
+
+import random
+
+import numpy as np
+import pytest
+
+from oracle import handoff_oracle as ho
+from tests.conftest import golden_json, golden_npz, load_pool, oracle_pool, pool_equal
+
+
+def named(pool, segments):
+    spans = {
+        name: getattr(pool, name)
+        for name in ("key", "value", "key_scale", "value_scale")
+        if getattr(pool, name) is not None
+    }
+    out = []
+    for address, n, _ in segments:
+        for name, t in spans.items():
+            if t.base <= address and address + n <= t.base + t.flat.size:
+                out.append([name, address - t.base, n])
+                break
+        else:
+            raise AssertionError("segment outside pool")
+    return out
+
+
+@pytest.mark.parametrize("case", golden_json("segments.json"), ids=lambda c: f"{c['kind']}-{c['start']}-{c['end']}")
+def test_segments_and_partition_match_reference(case):
+    pool = oracle_pool(case["kind"], case["shape"])
+    assert pool.allocate("a", case["tokens"])
+    tables = pool.plane_block_tables("a")
+    assert [list(t) for t in tables] == case["tables"]
+    info = pool.info()
+    for key in ("block_bytes", "layer_bytes", "token_bytes"):
+        assert info[key] == case["geometry"][key]
+    if "scale" in case["geometry"]:
+        for key in ("block_bytes", "layer_bytes", "token_bytes"):
+            assert info["scale_region"][key] == case["geometry"]["scale"][key]
+    else:
+        assert info["scale_region"] is None
+    segs = list(ho.kv_segments(info, tables, case["start"], case["end"]))
+    assert named(pool, segs) == case["segments"]
+    parts = list(ho.partition_segments(segs, segs, case["byte_limit"], case["descriptor_limit"]))
+    assert [[named(pool, local), n] for local, _, n in parts] == case["partition"]
+    assert all(local == remote for local, remote, _ in parts)
+
+
+def test_segments_cover_exactly_the_valid_rows():
+    """The byte-set property the reference pins in tests/test_pd.py:56-87."""
+    for kind in ("f32", "fp8", "fp8_fixed"):
+        pool = oracle_pool(kind, (3, 2, 8, 24, 4, 4))
+        pool.allocate("a", 9)
+        tables = pool.plane_block_tables("a")
+        expected = set()
+        for table in tables:
+            for token in range(2, 9):
+                for layer in range(3):
+                    for t in pool.tensors():
+                        row = t.data.strides[2]
+                        start = t.base + table[token // 4] * t.data.strides[0] + layer * t.data.strides[1] + (token % 4) * row
+                        expected.update(range(start, start + row))
+        got = set()
+        for address, n, _ in ho.kv_segments(pool.info(), tables, 2, 9):
+            got.update(range(address, address + n))
+        assert got == expected
+
+
+def test_partition_known_answers():
+    data = golden_json("partition.json")
+    for case in data["cases"]:
+        src = [tuple(s) for s in case["source"]]
+        dst = [tuple(s) for s in case["target"]]
+        parts = list(ho.partition_segments(src, dst, case["byte_limit"], case["descriptor_limit"]))
+        got = [[[list(x) for x in l], [list(x) for x in r], n] for l, r, n in parts]
+        assert got == case["parts"]
+    assert data["length_mismatch_error"] == "incompatible source/target KV geometry"
+    with pytest.raises(ValueError, match="incompatible source/target KV geometry"):
+        list(ho.partition_segments([(0, 4, 0), (4, 4, 0)], [(0, 4, 1)], 100, 100))
+    with pytest.raises(ValueError, match="incompatible source/target KV geometry"):
+        list(ho.partition_segments([(0, 4, 0)], [(0, 8, 1)], 100, 100))
+
+
+def test_planner_errors_match_reference_messages():
+    pool = oracle_pool("bf16", (3, 2, 8, 24, 4, 4))
+    pool.allocate("a", 9)
+    info, tables = pool.info(), pool.plane_block_tables("a")
+    for start, end in [(-1, 3), (3, 3), (5, 2)]:
+        with pytest.raises(ValueError, match="invalid KV range"):
+            list(ho.kv_segments(info, tables, start, end))
+    with pytest.raises(ValueError, match="KV range exceeds allocation"):
+        list(ho.kv_segments(info, tables, 0, 13))
+    bad = ((0, 1, 99),) + tables[1:]
+    with pytest.raises(ValueError, match="physical block outside registered pool"):
+        list(ho.kv_segments(info, bad, 0, 9))
+
+
+def test_allocation_order_matches_reference():
+    for case in golden_json("allocation.json"):
+        pool = oracle_pool("f32", case["shape"])
+        for step in case["trace"]:
+            if step["op"] == "alloc":
+                assert pool.allocate(step["rid"], step["tokens"]) == step["ok"]
+                assert [list(t) for t in pool.plane_block_tables(step["rid"])] == step["tables"]
+            else:
+                pool.free(step["rid"])
+        assert len(pool._free) == case["free"]
+
+
+HANDOFF = golden_json("handoff.json")
+
+
+@pytest.mark.parametrize("case", HANDOFF, ids=lambda c: c["name"])
+def test_handoff_matches_reference_bytes(case):
+    arrays = golden_npz(case["name"])
+    P = oracle_pool(case["kind"], case["shape"], device=0)
+    D = oracle_pool(case["kind"], case["shape"], device=1, base=1 << 40)
+    P.shuffle_free_list(random.Random(case["free_src_seed"]))
+    D.shuffle_free_list(random.Random(case["free_dst_seed"]))
+    load_pool(P, arrays, "src_")
+    load_pool(D, arrays, "dst_before_")
+    packed = []
+    for i, req in enumerate(case["requests"]):
+        rid = f"r{i}"
+        assert P.allocate(rid, req["tokens"]) and D.allocate(rid, req["tokens"])
+        # the seeded shuffle + ascending pop reproduces the reference's tables
+        assert [list(t) for t in P.plane_block_tables(rid)] == req["src_tables"]
+        assert [list(t) for t in D.plane_block_tables(rid)] == req["dst_tables"]
+        moved = ho.handoff_reference(
+            P, D, P.plane_block_tables(rid), D.plane_block_tables(rid), req["start"], req["end"],
+            byte_limit=case["byte_limit"], descriptor_limit=case["descriptor_limit"],
+        )
+        assert moved == req["bytes"]
+        assert moved == ho.payload_bytes(P, req["end"] - req["start"], P.planes)
+        assert sum(len(p) for p in packed) == req["packed_offset"]
+        packed.append(ho.pack_rows(P, P.plane_block_tables(rid), req["start"], req["end"]))
+    assert pool_equal(D, arrays, "dst_after_")
+    assert np.array_equal(np.concatenate(packed), arrays["packed"])
+
+
+@pytest.mark.parametrize("case", HANDOFF, ids=lambda c: c["name"])
+def test_row_statement_equals_segment_statement(case):
+    """``handoff_rows`` (what the kernels are checked against) == the planner + write."""
+    arrays = golden_npz(case["name"])
+    P = oracle_pool(case["kind"], case["shape"])
+    D = oracle_pool(case["kind"], case["shape"], device=1, base=1 << 40)
+    load_pool(P, arrays, "src_")
+    load_pool(D, arrays, "dst_before_")
+    for req in case["requests"]:
+        moved = ho.handoff_rows(P, D, req["src_tables"], req["dst_tables"], req["start"], req["end"])
+        assert moved == req["bytes"]
+    assert pool_equal(D, arrays, "dst_after_")
+
+
+def test_block_copy_simulation_agrees_on_aligned_ranges():
+    """Cross-check with the whole-block loop of tests/test_stage_engine.py:118-126."""
+    rng = np.random.default_rng(3)
+    P = oracle_pool("bf16", (3, 2, 8, 64, 4, 4))
+    A = oracle_pool("bf16", (3, 2, 8, 64, 4, 4), device=1, base=1 << 40)
+    B = oracle_pool("bf16", (3, 2, 8, 64, 4, 4), device=1, base=1 << 40)
+    P.fill_random(rng)
+    for pool, seed in ((P, 1), (A, 2), (B, 2)):
+        pool.shuffle_free_list(random.Random(seed))
+        pool.allocate("r", 12)
+    ho.handoff_reference(P, A, P.plane_block_tables("r"), A.plane_block_tables("r"), 0, 12)
+    ho.handoff_blocks(P, B, P.plane_block_tables("r"), B.plane_block_tables("r"))
+    assert np.array_equal(A.key.data, B.key.data) and np.array_equal(A.value.data, B.value.data)
+
+
+FINALIZE = golden_json("finalize.json")
+
+
+@pytest.mark.parametrize("case", FINALIZE, ids=lambda c: c["name"])
+def test_finalize_and_exit_modes_match_reference(case):
+    arrays = golden_npz(case["name"])
+    shape = case["shape"]
+    P = oracle_pool(case["kind"], shape, recurrent_layers=case["recurrent_layers"])
+    load_pool(P, arrays, "src_before_")
+    for i, req in enumerate(case["requests"]):
+        P.tables[f"r{i}"] = tuple(tuple(t) for t in req["src_tables"])
+        for pos, e in enumerate(req["exit_planes"]):
+            P.finalize_token(f"r{i}", pos, e)
+    assert pool_equal(P, arrays, "src_after_")
+
+    def fresh_destination(planes=None):
+        s = list(shape)
+        if planes is not None:
+            s[5] = planes
+        D = oracle_pool(case["kind"], s, device=1, base=1 << 40)
+        D.fill_sentinel()
+        if D.fp8 and D.fixed_scale is not None:
+            for t in (D.key_scale, D.value_scale):
+                t.data[...] = np.full(t.data.shape[:-1] + (D.num_kv_heads,), D.fixed_scale, np.float32).view(np.uint8).reshape(t.data.shape)
+        return D
+
+    # all planes: the reference's own behaviour
+    D = fresh_destination()
+    for req in case["requests"]:
+        ho.handoff_reference(P, D, req["src_tables"], req["dst_tables"], 0, req["tokens"])
+    assert pool_equal(D, arrays, "dst_after_")
+    if case["recurrent_layers"] is not None:
+        return  # dedup over a layer subset is exercised by the dedicated layer-mask tests
+    # dedup: rebuilds the deeper planes from the exit plane; same destination bytes
+    D = fresh_destination()
+    for req in case["requests"]:
+        ho.handoff_rows(P, D, req["src_tables"], req["dst_tables"], 0, req["tokens"],
+                        mode=ho.MODE_DEDUP, exit_planes=req["exit_planes"])
+    assert pool_equal(D, arrays, "dst_after_")
+    # exit only: a single-plane destination holds, per token, the exit plane's rows
+    D1 = fresh_destination(planes=1)
+    full = fresh_destination()
+    load_pool(full, arrays, "dst_after_")
+    for req in case["requests"]:
+        one = (tuple(req["dst_tables"][0]),)
+        ho.handoff_rows(P, D1, req["src_tables"], one, 0, req["tokens"],
+                        mode=ho.MODE_EXIT_ONLY, exit_planes=req["exit_planes"])
+        for t, e in enumerate(req["exit_planes"]):
+            for a, b in zip(D1.tensors(), full.tensors()):
+                assert np.array_equal(
+                    a.data[one[0][t // D1.block_size], :, t % D1.block_size],
+                    b.data[req["dst_tables"][e][t // D1.block_size], :, t % D1.block_size],
+                )
