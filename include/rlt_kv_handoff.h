@@ -1,0 +1,237 @@
+/*
+ * C ABI of the B200 KV-handoff library (librlt_kv_handoff.so).
+ *
+ * The library moves paged KV-cache bytes from a prefill pool to a decode pool
+ * with hand-written sm_100a kernels. It is the data plane behind the
+ * reference's transfer connector: every entry point below names the reference
+ * interface it replaces (paths relative to the vllm-rlt project root).
+ *
+ * Conventions
+ *  - Plain C types only; no framework types cross this boundary.
+ *  - Every pointer inside RltPool / RltBatch is a DEVICE pointer valid on the
+ *    current device (a destination pool may be a peer mapping of another GPU).
+ *    The structs themselves are read on the host during the call.
+ *  - Calls are stream-ordered and never synchronise. The caller owns all
+ *    memory; unless stated otherwise the library allocates nothing.
+ *  - Return value: RLT_OK or a negative RLT_E_* code (argument errors are
+ *    detected on the host before any launch). Data-dependent errors found on
+ *    the device (a block id outside the pool, a token range outside the table)
+ *    are recorded in the optional status words and the offending rows are
+ *    skipped; the kernels never trap.
+ */
+#ifndef RLT_KV_HANDOFF_H
+#define RLT_KV_HANDOFF_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define RLT_API __attribute__((visibility("default")))
+#else
+#define RLT_API
+#endif
+
+/* cudaStream_t / CUstream, spelled without the CUDA headers. */
+typedef struct CUstream_st* rlt_stream_t;
+
+enum {
+  RLT_OK = 0,
+  RLT_E_INVALID = -1,  /* bad argument: null pointer, non-positive size, unknown mode          */
+  RLT_E_GEOMETRY = -2, /* pools are not dense, or source and destination geometry differ       */
+  RLT_E_LIMIT = -3,    /* a documented size limit of the entry point is exceeded               */
+  RLT_E_CUDA = -4,     /* a CUDA runtime call failed; rlt_last_cuda_error() has the code        */
+  RLT_E_ALIGN = -5     /* a pointer or size breaks the alignment rule of the entry point       */
+};
+
+/* Values written to status[0] by the kernels (0 = nothing to report). */
+enum {
+  RLT_STATUS_OK = 0,
+  RLT_STATUS_BAD_RANGE = 1,   /* token range negative or past the table: status[1] = request      */
+  RLT_STATUS_BAD_BLOCK = 2,   /* block id outside pool: [1] request, [2] logical block, [3] id    */
+  RLT_STATUS_BAD_PLANE = 3,   /* exit plane outside [0, planes): [1] request, [2] token, [3] value */
+  RLT_STATUS_TIMEOUT = 4      /* rlt_kv_wait gave up: [1] low 32 bits of the last value seen      */
+};
+#define RLT_STATUS_WORDS 4
+
+/* Which source plane feeds a destination plane (plane = zero-based loop depth). */
+enum {
+  RLT_MODE_ALL_PLANES = 0, /* plane p <- plane p; what the reference's PD path sends
+                              (vllm_rlt/pd/transport.py:40, "for table in tables")             */
+  RLT_MODE_DEDUP = 1,      /* plane p <- plane min(p, exit); equals ALL_PLANES on a source
+                              finalized by finalize_token (vllm_rlt/core/kv_cache_manager.py:1053-1076) */
+  RLT_MODE_EXIT_ONLY = 2   /* single destination plane <- the token's exit plane             */
+};
+
+/*
+ * One K/V tensor pair of a pool, as bytes. Same fields as the reference's
+ * _kv_region (vllm_rlt/pd/transport.py:18-26). The tensors must be dense:
+ * layer_bytes == block_size * token_bytes and block_bytes == num_layers *
+ * layer_bytes, which is what KVCacheManager allocates
+ * (vllm_rlt/core/kv_cache_manager.py:261-271).
+ */
+typedef struct RltRegion {
+  void* key;
+  void* value;
+  int64_t block_bytes;
+  int64_t layer_bytes;
+  int64_t token_bytes; /* bytes of one token row: kv_heads * head_dim * element size */
+} RltRegion;
+
+/*
+ * A paged KV pool: the codes (bf16/f16/f32 values or e4m3 bytes) and, for an
+ * FP8 pool with per-vector scales, the float32 scale tensors. scales.key ==
+ * NULL means no scale tensors travel (an unquantised pool, or a fixed-scale
+ * FP8 pool: vllm_rlt/pd/transport.py:132-137).
+ */
+typedef struct RltPool {
+  RltRegion codes;
+  RltRegion scales;
+  int32_t num_blocks;
+  int32_t block_size; /* tokens per block, 1..64 */
+  int32_t num_layers;
+  int32_t num_planes; /* block tables per request: max_loops (LAST_EXITED) or 1 (SHARED) */
+} RltPool;
+
+/*
+ * A batch of per-request handoffs. Tables are the reference's
+ * plane_block_tables (vllm_rlt/core/kv_cache_manager.py:550-557), padded to a
+ * common width. Token ranges are the [start, end) that queue_chunk passes to
+ * kv_segments (vllm_rlt/pd/connector.py:220-231), after its prefix skip.
+ */
+typedef struct RltBatch {
+  int32_t num_requests;        /* 1..RLT_MAX_REQUESTS                                          */
+  int32_t table_width;         /* entries per table row                                         */
+  const int32_t* src_tables;   /* [num_requests, src planes, table_width]                       */
+  const int32_t* dst_tables;   /* [num_requests, dst planes, table_width]                       */
+  const int32_t* tok_begin;    /* [num_requests]                                                */
+  const int32_t* tok_end;      /* [num_requests]; a request with end <= begin moves nothing     */
+  const int32_t* exit_planes;  /* NULL, or per-token zero-based exit plane (DEDUP / EXIT_ONLY)  */
+  const int64_t* exit_offsets; /* [num_requests]: index in exit_planes of the request's token 0 */
+} RltBatch;
+
+#define RLT_MAX_REQUESTS 4096
+
+typedef struct RltOptions {
+  int32_t mode;        /* RLT_MODE_*                                                            */
+  int32_t layer_begin; /* layer slice [layer_begin, layer_end) for layer-by-layer streaming    */
+  int32_t layer_end;   /* 0 means num_layers                                                    */
+  int32_t wire_planes; /* pack/scatter: planes on the wire; 0 = source planes (1 for EXIT_ONLY) */
+  int32_t* status;     /* NULL or device/mapped int32[RLT_STATUS_WORDS], zeroed by the caller   */
+  int32_t grid_limit;  /* 0 = one full wave of resident CTAs; else cap on CTAs launched        */
+  int32_t variant;     /* kernel variant: 0 = default; see rlt_kv_variants()                    */
+} RltOptions;
+
+/* --- information ---------------------------------------------------------------------------- */
+
+RLT_API int rlt_version(void);
+RLT_API const char* rlt_error_string(int code);
+/* Last cudaError_t seen by this thread inside the library (0 if none). */
+RLT_API int rlt_last_cuda_error(void);
+/* How many of this library's kernels the calling process has launched so far. */
+RLT_API int64_t rlt_kernel_launches(void);
+
+/* --- the handoff ---------------------------------------------------------------------------- */
+
+/*
+ * Pool-to-pool handoff driven by block tables: for every request, destination
+ * plane, token in [begin, end), layer in the slice and tensor (K, V, and the
+ * scale tensors when present) copy the token's row from the source block to
+ * the destination block. The destination may live on a peer GPU. No staging
+ * buffer is used and no other destination byte is written.
+ *
+ * Replaces, as one launch, the plan + write of PDStageConnector.queue_chunk /
+ * _submit_chunk (vllm_rlt/pd/connector.py:220-246, :444-455): kv_segments on
+ * both sides (vllm_rlt/pd/transport.py:29-63), partition_segments (:95-112) and
+ * NixlConnector.submit's WRITE (:182-201).
+ */
+RLT_API int rlt_kv_handoff(const RltPool* src, const RltPool* dst, const RltBatch* batch,
+                           const RltOptions* options, rlt_stream_t stream);
+
+/*
+ * Bytes of the packed wire image of a batch: total_tokens * planes * 2 *
+ * layers * (codes row + scales row). Host-side arithmetic only.
+ */
+RLT_API int64_t rlt_kv_packed_bytes(const RltPool* pool, int64_t total_tokens, int32_t wire_planes,
+                                    int32_t layers);
+
+/*
+ * Gather a batch into a contiguous buffer in the reference's segment order
+ * (vllm_rlt/pd/transport.py:40-63: plane, logical block, codes then scales, K
+ * then V, layer, token), requests back to back. batch->dst_tables is ignored.
+ * packed must be 16-byte aligned. RLT_MODE_DEDUP is not a pack mode.
+ */
+RLT_API int rlt_kv_pack(const RltPool* src, const RltBatch* batch, const RltOptions* options,
+                        void* packed, int64_t packed_bytes, rlt_stream_t stream);
+
+/*
+ * Inverse of rlt_kv_pack: write a packed image into the destination blocks
+ * named by batch->dst_tables (batch->src_tables is ignored). Writes only the
+ * rows of valid tokens.
+ */
+RLT_API int rlt_kv_scatter(const void* packed, int64_t packed_bytes, const RltPool* dst,
+                           const RltBatch* batch, const RltOptions* options, rlt_stream_t stream);
+
+/*
+ * Copy one contiguous range, typically a packed image into a buffer on the
+ * decode GPU through a peer pointer. Any alignment; 16-byte aligned ranges
+ * take the vector path.
+ */
+RLT_API int rlt_kv_push(const void* src, void* dst, int64_t nbytes, rlt_stream_t stream);
+
+/*
+ * Copy a list of (source address, destination address, byte count) triples
+ * held in device memory as int64[count][3], count <= RLT_MAX_SEGMENTS. This is
+ * the WRITE of one NixlConnector.submit call (vllm_rlt/pd/transport.py:182-201)
+ * for descriptor lists produced by partition_segments, so an unmodified
+ * PDStageConnector can drive this library.
+ */
+RLT_API int rlt_kv_copy_segments(const int64_t* segments, int32_t count, rlt_stream_t stream);
+#define RLT_MAX_SEGMENTS 4096
+
+/* --- completion ----------------------------------------------------------------------------- */
+
+/*
+ * Stream-ordered release store of value to *flag (device, peer or mapped host
+ * memory, 8-byte aligned). Issued after a handoff on the same stream it tells
+ * the receiver that every earlier write has landed; it takes the place of the
+ * notification NIXL delivers with each WRITE (vllm_rlt/pd/transport.py:186-195, :222-229).
+ */
+RLT_API int rlt_kv_signal(uint64_t* flag, uint64_t value, rlt_stream_t stream);
+
+/*
+ * Bounded device-side wait until *flag >= value. Gives up after timeout_ns
+ * (1 .. RLT_MAX_WAIT_NS), writing RLT_STATUS_TIMEOUT to status; the kernel
+ * always returns and the context stays usable. Never launch it on the GPU
+ * whose own later work is what sets the flag.
+ */
+RLT_API int rlt_kv_wait(const uint64_t* flag, uint64_t value, int64_t timeout_ns, int32_t* status,
+                        rlt_stream_t stream);
+#define RLT_MAX_WAIT_NS 2000000000LL
+
+/* --- peer memory ---------------------------------------------------------------------------- */
+
+/* Enable access from device `device` to memory of device `peer` (idempotent). */
+RLT_API int rlt_peer_enable(int device, int peer);
+/* 1 if `device` can map memory of `peer`, 0 if not, negative on error. */
+RLT_API int rlt_peer_can_access(int device, int peer);
+
+#define RLT_IPC_HANDLE_BYTES 64
+/*
+ * Export the allocation that contains ptr for another process on the same
+ * host: fills handle and the byte offset of ptr inside that allocation. This
+ * takes the place of the NIXL agent metadata in startup_info
+ * (vllm_rlt/pd/connector.py:96-98, vllm_rlt/pd/transport.py:140-154).
+ */
+RLT_API int rlt_ipc_export(const void* ptr, uint8_t handle[RLT_IPC_HANDLE_BYTES], int64_t* offset);
+/* Map an exported allocation into this process on the current device. */
+RLT_API int rlt_ipc_open(const uint8_t handle[RLT_IPC_HANDLE_BYTES], void** base);
+RLT_API int rlt_ipc_close(void* base);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* RLT_KV_HANDOFF_H */

@@ -1,0 +1,333 @@
+"""GPU parity: the CUDA kernels, called through the C ABI, against the CPU oracle and the golden fixtures.
+
+Bit-exact everywhere (the handoff is a byte mover). Every comparison is over the
+whole destination pool, which was pre-filled with a sentinel, so a stray write is
+caught as well as a missing one (the "no other byte changes" property pinned by
+tests/test_tensor_transfer.py:64-74 in the reference).
+"""
+
+import random
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import handoff_oracle as ho
+from tests.conftest import golden_json, golden_npz, load_pool, oracle_pool
+from tests.gpu_support import GpuPool, assert_pools_equal
+
+pytestmark = pytest.mark.gpu
+
+
+def kh():
+    from vllm_rlt_b200.kernels import kv_handoff
+
+    return kv_handoff
+
+
+def sentinel_destination(kind, shape, planes=None):
+    s = list(shape)
+    if planes is not None:
+        s[5] = planes
+    D = oracle_pool(kind, s, device=1, base=1 << 40)
+    fixed = [t.data.copy() for t in (D.key_scale, D.value_scale)] if D.fp8 and D.fixed_scale is not None else None
+    D.fill_sentinel()
+    if fixed is not None:
+        D.key_scale.data[...] = fixed[0]
+        D.value_scale.data[...] = fixed[1]
+    return D
+
+
+# ----------------------------------------------------------------------------- golden fixtures
+
+
+@pytest.mark.parametrize("case", golden_json("handoff.json"), ids=lambda c: c["name"])
+@pytest.mark.parametrize("batched", [True, False])
+def test_handoff_equals_reference_destination(case, batched):
+    k = kh()
+    arrays = golden_npz(case["name"])
+    P = oracle_pool(case["kind"], case["shape"])
+    D = oracle_pool(case["kind"], case["shape"], device=1, base=1 << 40)
+    load_pool(P, arrays, "src_")
+    load_pool(D, arrays, "dst_before_")
+    gp, gd = GpuPool(P), GpuPool(D)
+    reqs = case["requests"]
+    status = k.new_status()
+    groups = [reqs] if batched else [[r] for r in reqs]
+    for group in groups:
+        batch = k.HandoffBatch(
+            [r["src_tables"] for r in group], [r["dst_tables"] for r in group],
+            [(r["start"], r["end"]) for r in group], block_size=P.block_size,
+            src_blocks=P.num_blocks, dst_blocks=D.num_blocks,
+        )
+        k.kv_handoff(gp.view(), gd.view(), batch, status=status)
+    k.raise_for_status(status)
+    load_pool(D, arrays, "dst_after_")
+    assert_pools_equal(gd, D)
+
+
+@pytest.mark.parametrize("case", golden_json("handoff.json"), ids=lambda c: c["name"])
+def test_pack_equals_reference_wire_and_scatter_inverts_it(case):
+    k = kh()
+    arrays = golden_npz(case["name"])
+    P = oracle_pool(case["kind"], case["shape"])
+    D = oracle_pool(case["kind"], case["shape"], device=1, base=1 << 40)
+    load_pool(P, arrays, "src_")
+    load_pool(D, arrays, "dst_before_")
+    gp, gd = GpuPool(P), GpuPool(D)
+    reqs = case["requests"]
+    batch = k.HandoffBatch(
+        [r["src_tables"] for r in reqs], [r["dst_tables"] for r in reqs],
+        [(r["start"], r["end"]) for r in reqs], block_size=P.block_size,
+    )
+    size = k.packed_bytes(gp.view(), batch.total_tokens, P.planes)
+    assert size == arrays["packed"].size
+    packed = torch.full((size + 64,), 0x5A, dtype=torch.uint8, device="cuda")
+    status = k.new_status()
+    k.kv_pack(gp.view(), batch, packed[:size], status=status)
+    k.raise_for_status(status)
+    got = packed.cpu().numpy()
+    assert np.array_equal(got[:size], arrays["packed"])
+    assert (got[size:] == 0x5A).all()
+    k.kv_scatter(packed[:size], gd.view(), batch, status=status)
+    k.raise_for_status(status)
+    load_pool(D, arrays, "dst_after_")
+    assert_pools_equal(gd, D)
+
+
+@pytest.mark.parametrize("case", golden_json("finalize.json"), ids=lambda c: c["name"])
+def test_exit_plane_modes_on_reference_finalized_source(case):
+    k = kh()
+    arrays = golden_npz(case["name"])
+    P = oracle_pool(case["kind"], case["shape"], recurrent_layers=case["recurrent_layers"])
+    load_pool(P, arrays, "src_after_")
+    gp = GpuPool(P)
+    reqs = case["requests"]
+    ranges = [(0, r["tokens"]) for r in reqs]
+    exits = [r["exit_planes"] for r in reqs]
+    # all planes and dedup both reproduce the reference destination
+    for mode in (k.MODE_ALL_PLANES, k.MODE_DEDUP):
+        if mode == k.MODE_DEDUP and case["recurrent_layers"] is not None:
+            continue
+        D = sentinel_destination(case["kind"], case["shape"])
+        gd = GpuPool(D)
+        batch = k.HandoffBatch([r["src_tables"] for r in reqs], [r["dst_tables"] for r in reqs], ranges,
+                               block_size=P.block_size, exit_planes=exits)
+        status = k.new_status()
+        k.kv_handoff(gp.view(), gd.view(), batch, mode=mode, status=status)
+        k.raise_for_status(status)
+        load_pool(D, arrays, "dst_after_")
+        assert_pools_equal(gd, D)
+    if case["recurrent_layers"] is not None:
+        return
+    # exit only: single-plane destination, checked against the row-level oracle
+    D1 = sentinel_destination(case["kind"], case["shape"], planes=1)
+    gd1 = GpuPool(D1)
+    one = [[r["dst_tables"][0]] for r in reqs]
+    batch = k.HandoffBatch([r["src_tables"] for r in reqs], one, ranges, block_size=P.block_size, exit_planes=exits)
+    status = k.new_status()
+    k.kv_handoff(gp.view(), gd1.view(), batch, mode=k.MODE_EXIT_ONLY, status=status)
+    k.raise_for_status(status)
+    for r, tables in zip(reqs, one):
+        ho.handoff_rows(P, D1, r["src_tables"], tables, 0, r["tokens"], mode=ho.MODE_EXIT_ONLY, exit_planes=r["exit_planes"])
+    assert_pools_equal(gd1, D1)
+    # exit-only pack: the wire image is the row oracle's
+    size = k.packed_bytes(gp.view(), batch.total_tokens, 1)
+    packed = torch.zeros(size, dtype=torch.uint8, device="cuda")
+    k.kv_pack(gp.view(), batch, packed, mode=k.MODE_EXIT_ONLY, status=status)
+    k.raise_for_status(status)
+    want = np.concatenate([
+        ho.pack_rows(P, r["src_tables"], 0, r["tokens"], mode=ho.MODE_EXIT_ONLY, exit_planes=r["exit_planes"]) for r in reqs
+    ])
+    assert np.array_equal(packed.cpu().numpy(), want)
+
+
+# ----------------------------------------------------------------------------- seeded cases vs the oracle
+
+SHAPES = {
+    # name: (kind, (layers, kv_heads, head_dim, blocks, block_size, planes))
+    "ouro_bf16_small": ("bf16", (4, 16, 128, 96, 16, 4)),       # 4 KiB rows, vec16
+    "ouro_fp8_small": ("fp8", (4, 16, 128, 96, 16, 4)),         # 2 KiB code rows + 64 B scale rows
+    "huginn_rows": ("bf16", (3, 55, 96, 48, 16, 2)),            # 10,560 B rows: 16-B aligned, not a power of two
+    "huginn_fp8_rows": ("fp8", (2, 55, 96, 40, 16, 2)),         # 220 B scale rows: 4-byte path
+    "odd_rows": ("fp8", (3, 1, 3, 40, 8, 2)),                   # 3 B code rows (byte path), 4 B scale rows
+    "block32": ("bf16", (2, 2, 8, 40, 32, 3)),
+    "block1": ("bf16", (2, 2, 8, 64, 1, 2)),
+    "shared_single_plane": ("bf16", (3, 2, 16, 40, 16, 1)),
+}
+
+
+def random_requests(rng, pool_src, pool_dst, count, max_tokens):
+    reqs = []
+    for i in range(count):
+        tokens = rng.randint(1, max_tokens)
+        if not (pool_src.allocate(f"r{i}", tokens) and pool_dst.allocate(f"r{i}", tokens)):
+            break
+        start = rng.choice([0, 0, rng.randrange(tokens)])
+        end = rng.choice([tokens, tokens, rng.randint(start + 1, tokens)])
+        reqs.append((f"r{i}", tokens, start, end))
+    assert reqs
+    return reqs
+
+
+@pytest.mark.parametrize("name", list(SHAPES))
+@pytest.mark.parametrize("mode_name", ["all", "dedup", "exit_only"])
+def test_seeded_handoff_matches_oracle(name, mode_name):
+    k = kh()
+    kind, shape = SHAPES[name]
+    planes = shape[5]
+    seed = hash((name, mode_name)) & 0xFFFF
+    rng, nrng = random.Random(seed), np.random.default_rng(seed)
+    P = oracle_pool(kind, shape)
+    dst_planes = 1 if mode_name == "exit_only" else planes
+    D = sentinel_destination(kind, shape, planes=dst_planes)
+    P.fill_random(nrng)
+    P.shuffle_free_list(rng)
+    D.shuffle_free_list(rng)
+    per_request = shape[3] // (max(planes, 1) * 3)
+    reqs = random_requests(rng, P, D, 3, max(1, per_request * shape[4] - 1))
+    mode = {"all": ho.MODE_ALL_PLANES, "dedup": ho.MODE_DEDUP, "exit_only": ho.MODE_EXIT_ONLY}[mode_name]
+    exits = None
+    if mode != ho.MODE_ALL_PLANES:
+        exits = [[rng.randrange(planes) for _ in range(t)] for _, t, _, _ in reqs]
+        for (rid, t, _, _), e in zip(reqs, exits):
+            for pos in range(t):
+                P.finalize_token(rid, pos, e[pos])
+    gp, gd = GpuPool(P), GpuPool(D)
+    batch = k.HandoffBatch(
+        [P.plane_block_tables(r) for r, *_ in reqs], [D.plane_block_tables(r) for r, *_ in reqs],
+        [(s, e) for _, _, s, e in reqs], block_size=P.block_size, exit_planes=exits,
+        src_blocks=P.num_blocks, dst_blocks=D.num_blocks,
+    )
+    status = k.new_status()
+    k.kv_handoff(gp.view(), gd.view(), batch, mode=mode, status=status)
+    k.raise_for_status(status)
+    moved = 0
+    for i, (rid, _, s, e) in enumerate(reqs):
+        moved += ho.handoff_rows(P, D, P.plane_block_tables(rid), D.plane_block_tables(rid), s, e,
+                                 mode=mode, exit_planes=None if exits is None else exits[i])
+    assert moved == gp.view().payload_bytes(batch.total_tokens, dst_planes)
+    assert_pools_equal(gd, D)
+    if mode == ho.MODE_DEDUP:
+        # on a finalized source, dedup and all-planes agree (what makes dedup a valid wire saving)
+        D2 = sentinel_destination(kind, shape)
+        D2._free, D2.tables = [], dict(D.tables)
+        for rid, _, s, e in reqs:
+            ho.handoff_reference(P, D2, P.plane_block_tables(rid), D2.plane_block_tables(rid), s, e)
+        assert_pools_equal(gd, D2)
+
+
+@pytest.mark.parametrize("name", ["ouro_bf16_small", "ouro_fp8_small", "huginn_fp8_rows", "odd_rows"])
+def test_layer_slices_compose_to_the_full_handoff(name):
+    """Layer-by-layer streaming: slices [0,1), [1,3), [3,L) together equal one full handoff."""
+    k = kh()
+    kind, shape = SHAPES[name]
+    rng, nrng = random.Random(11), np.random.default_rng(11)
+    P = oracle_pool(kind, shape)
+    D = sentinel_destination(kind, shape)
+    P.fill_random(nrng)
+    P.shuffle_free_list(rng)
+    D.shuffle_free_list(rng)
+    reqs = random_requests(rng, P, D, 2, 3 * shape[4] + 5)
+    gp, gd = GpuPool(P), GpuPool(D)
+    batch = k.HandoffBatch(
+        [P.plane_block_tables(r) for r, *_ in reqs], [D.plane_block_tables(r) for r, *_ in reqs],
+        [(s, e) for _, _, s, e in reqs], block_size=P.block_size,
+    )
+    layers = shape[0]
+    cuts = sorted({0, 1, min(3, layers), layers})
+    status = k.new_status()
+    for lo, hi in zip(cuts, cuts[1:]):
+        k.kv_handoff(gp.view(), gd.view(), batch, layer_begin=lo, layer_end=hi, status=status)
+        for rid, _, s, e in reqs:
+            ho.handoff_rows(P, D, P.plane_block_tables(rid), D.plane_block_tables(rid), s, e, layer_begin=lo, layer_end=hi)
+        assert_pools_equal(gd, D)
+    k.raise_for_status(status)
+    # and the packed image of a slice is the oracle's
+    lo, hi = cuts[1], cuts[2] if len(cuts) > 2 else layers
+    if hi > lo:
+        size = k.packed_bytes(gp.view(), batch.total_tokens, P.planes, hi - lo)
+        packed = torch.zeros(size, dtype=torch.uint8, device="cuda")
+        k.kv_pack(gp.view(), batch, packed, layer_begin=lo, layer_end=hi, status=status)
+        k.raise_for_status(status)
+        want = np.concatenate([ho.pack_rows(P, P.plane_block_tables(r), s, e, layer_begin=lo, layer_end=hi) for r, _, s, e in reqs])
+        assert np.array_equal(packed.cpu().numpy(), want)
+
+
+def test_many_requests_cross_the_scan_tile():
+    """More requests than threads in a CTA, so the request prefix sums span several scan tiles."""
+    k = kh()
+    kind, shape = "bf16", (2, 2, 8, 2400, 4, 2)
+    rng, nrng = random.Random(5), np.random.default_rng(5)
+    P, D = oracle_pool(kind, shape), sentinel_destination(kind, shape)
+    P.fill_random(nrng)
+    P.shuffle_free_list(rng)
+    D.shuffle_free_list(rng)
+    reqs = []
+    for i in range(600):
+        tokens = rng.randint(1, 7)
+        assert P.allocate(f"r{i}", tokens) and D.allocate(f"r{i}", tokens)
+        start = rng.randrange(tokens)
+        reqs.append((f"r{i}", tokens, start, rng.randint(start + 1, tokens)))
+    gp, gd = GpuPool(P), GpuPool(D)
+    batch = k.HandoffBatch(
+        [P.plane_block_tables(r) for r, *_ in reqs], [D.plane_block_tables(r) for r, *_ in reqs],
+        [(s, e) for _, _, s, e in reqs], block_size=P.block_size,
+    )
+    status = k.new_status()
+    k.kv_handoff(gp.view(), gd.view(), batch, status=status)
+    k.raise_for_status(status)
+    for rid, _, s, e in reqs:
+        ho.handoff_rows(P, D, P.plane_block_tables(rid), D.plane_block_tables(rid), s, e)
+    assert_pools_equal(gd, D)
+    size = k.packed_bytes(gp.view(), batch.total_tokens, P.planes)
+    packed = torch.zeros(size, dtype=torch.uint8, device="cuda")
+    k.kv_pack(gp.view(), batch, packed, status=status)
+    k.raise_for_status(status)
+    want = np.concatenate([ho.pack_rows(P, P.plane_block_tables(r), s, e) for r, _, s, e in reqs])
+    assert np.array_equal(packed.cpu().numpy(), want)
+
+
+# ----------------------------------------------------------------------------- errors
+
+
+def test_bad_block_id_is_reported_and_skipped_not_written():
+    k = kh()
+    kind, shape = "bf16", (2, 2, 8, 16, 4, 2)
+    P, D = oracle_pool(kind, shape), sentinel_destination(kind, shape)
+    P.fill_random(np.random.default_rng(0))
+    P.allocate("a", 8)
+    D.allocate("a", 8)
+    gp, gd = GpuPool(P), GpuPool(D)
+    src = [list(t) for t in P.plane_block_tables("a")]
+    src[1][1] = 99  # outside the pool; host validation is bypassed by not passing src_blocks
+    batch = k.HandoffBatch([src], [D.plane_block_tables("a")], [(0, 8)], block_size=4)
+    status = k.new_status()
+    k.kv_handoff(gp.view(), gd.view(), batch, status=status)
+    with pytest.raises(ValueError, match="physical block outside registered pool"):
+        k.raise_for_status(status)
+    assert status.tolist()[:1] == [2] and status.tolist()[3] == 99
+    # every other row arrived; the rows of the bad block kept the sentinel
+    tables = P.plane_block_tables("a")
+    ho.handoff_rows(P, D, tables, D.plane_block_tables("a"), 0, 8)
+    bad_dst = D.plane_block_tables("a")[1][1]
+    for t in D.tensors():
+        t.data[bad_dst] = 0xA5
+    assert_pools_equal(gd, D)
+    with pytest.raises(ValueError, match="physical block outside registered pool"):
+        k.HandoffBatch([src], [D.plane_block_tables("a")], [(0, 8)], block_size=4, src_blocks=16)
+
+
+def test_host_validation_matches_reference_errors():
+    k = kh()
+    tables = [[[0, 1, 2]]]
+    for rng_ in [(-1, 3), (3, 3), (5, 2)]:
+        with pytest.raises(ValueError, match="invalid KV range"):
+            k.HandoffBatch(tables, tables, [rng_], block_size=4)
+    with pytest.raises(ValueError, match="KV range exceeds allocation"):
+        k.HandoffBatch(tables, tables, [(0, 13)], block_size=4)
+    P = oracle_pool("bf16", (2, 2, 8, 16, 4, 1))
+    D = oracle_pool("bf16", (2, 2, 16, 16, 4, 1))
+    batch = k.HandoffBatch(tables, tables, [(0, 12)], block_size=4)
+    with pytest.raises(ValueError, match="geometry"):
+        k.kv_handoff(GpuPool(P).view(), GpuPool(D).view(), batch)

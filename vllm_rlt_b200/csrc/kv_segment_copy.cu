@@ -1,0 +1,142 @@
+// Copies of explicit byte ranges: one range (push) or a device-resident list of
+// (source, destination, bytes) triples (copy_segments).
+//
+// copy_segments performs the WRITE of one NixlConnector.submit call
+// (vllm_rlt/pd/transport.py:182-201) for the descriptor lists that
+// partition_segments produces (:95-112): up to a few hundred ranges whose sizes
+// differ by orders of magnitude (a 1.5 MiB block next to a 4 KiB partial row).
+// Each CTA scans the per-range tile counts with warp-shuffle prefix sums in
+// shared memory, so tiles of all ranges form one flat index space that the
+// persistent grid strides over; no range is left to a single CTA.
+//
+// Roofline: one read and one write per byte. Local copies are HBM bound; a
+// destination on a peer GPU is bound by NVLink (one direction).
+
+#include "common.cuh"
+
+namespace rlt {
+namespace {
+
+constexpr long long kTileBytes = 64 * 1024;
+constexpr int kUnroll = 8;
+
+template <typename T>
+__device__ __forceinline__ void stream_range(const char* __restrict__ src, char* __restrict__ dst, long long n) {
+  const T* s = reinterpret_cast<const T*>(src);
+  T* d = reinterpret_cast<T*>(dst);
+  for (long long base = threadIdx.x; base < n; base += kThreads * kUnroll) {
+    T regs[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const long long i = base + u * kThreads;
+      if (i < n) regs[u] = ld_stream(s + i);
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const long long i = base + u * kThreads;
+      if (i < n) st_stream(d + i, regs[u]);
+    }
+  }
+}
+
+__device__ __forceinline__ void copy_tile(const char* src, char* dst, long long n) {
+  const unsigned long long bits = reinterpret_cast<unsigned long long>(src) |
+                                  reinterpret_cast<unsigned long long>(dst) | static_cast<unsigned long long>(n);
+  if ((bits & 15ull) == 0) {
+    stream_range<uint4>(src, dst, n >> 4);
+  } else if ((bits & 3ull) == 0) {
+    stream_range<uint32_t>(src, dst, n >> 2);
+  } else {
+    stream_range<uint8_t>(src, dst, n);
+  }
+}
+
+__global__ void __launch_bounds__(kThreads, 4) push_kernel(const char* src, char* dst, long long nbytes) {
+  const long long tiles = (nbytes + kTileBytes - 1) / kTileBytes;
+  for (long long t = blockIdx.x; t < tiles; t += gridDim.x) {
+    const long long at = t * kTileBytes;
+    copy_tile(src + at, dst + at, min(kTileBytes, nbytes - at));
+  }
+}
+
+__global__ void __launch_bounds__(kThreads, 4) segment_copy_kernel(const long long* __restrict__ segments, int count) {
+  extern __shared__ int tile_off[];  // [count + 1] exclusive scan of tiles per segment
+  __shared__ int warp_sum[kThreads / 32];
+  __shared__ int carry;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (threadIdx.x == 0) {
+    carry = 0;
+    tile_off[0] = 0;
+  }
+  __syncthreads();
+  for (int base = 0; base < count; base += kThreads) {
+    const int s = base + threadIdx.x;
+    int tiles = 0;
+    if (s < count) {
+      const long long n = segments[3ll * s + 2];
+      tiles = n > 0 ? static_cast<int>((n + kTileBytes - 1) / kTileBytes) : 0;
+    }
+    const int inc = warp_inclusive_scan(tiles);
+    if (lane == 31) warp_sum[warp] = inc;
+    __syncthreads();
+    if (warp == 0) {
+      const int v = lane < kThreads / 32 ? warp_sum[lane] : 0;
+      const int iv = warp_inclusive_scan(v);
+      if (lane < kThreads / 32) warp_sum[lane] = iv - v;
+    }
+    __syncthreads();
+    if (s < count) tile_off[s + 1] = carry + warp_sum[warp] + inc;
+    __syncthreads();
+    if (threadIdx.x == kThreads - 1) carry += warp_sum[warp] + inc;
+    __syncthreads();
+  }
+  const int total = tile_off[count];
+  for (int t = blockIdx.x; t < total; t += gridDim.x) {
+    int lo = 0, hi = count;
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (tile_off[mid] <= t) lo = mid; else hi = mid;
+    }
+    const long long at = static_cast<long long>(t - tile_off[lo]) * kTileBytes;
+    const long long n = segments[3ll * lo + 2];
+    copy_tile(reinterpret_cast<const char*>(segments[3ll * lo]) + at,
+              reinterpret_cast<char*>(segments[3ll * lo + 1]) + at, min(kTileBytes, n - at));
+  }
+}
+
+}  // namespace
+}  // namespace rlt
+
+extern "C" {
+
+int rlt_kv_push(const void* src, void* dst, int64_t nbytes, rlt_stream_t stream) {
+  if (nbytes == 0) return RLT_OK;
+  if (src == nullptr || dst == nullptr || nbytes < 0) return RLT_E_INVALID;
+  int sms = 0;
+  const int rc = rlt::sm_count(&sms);
+  if (rc != RLT_OK) return rc;
+  const long long tiles = (nbytes + rlt::kTileBytes - 1) / rlt::kTileBytes;
+  const int grid = static_cast<int>(tiles < sms * 4ll ? tiles : sms * 4ll);
+  rlt::push_kernel<<<grid, rlt::kThreads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      static_cast<const char*>(src), static_cast<char*>(dst), nbytes);
+  RLT_CUDA_TRY(cudaGetLastError());
+  rlt::g_launches.fetch_add(1, std::memory_order_relaxed);
+  return RLT_OK;
+}
+
+int rlt_kv_copy_segments(const int64_t* segments, int32_t count, rlt_stream_t stream) {
+  if (count == 0) return RLT_OK;
+  if (segments == nullptr || count < 0) return RLT_E_INVALID;
+  if (count > RLT_MAX_SEGMENTS) return RLT_E_LIMIT;
+  int sms = 0;
+  const int rc = rlt::sm_count(&sms);
+  if (rc != RLT_OK) return rc;
+  const size_t smem = (static_cast<size_t>(count) + 1) * sizeof(int);
+  rlt::segment_copy_kernel<<<sms * 4, rlt::kThreads, smem, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const long long*>(segments), count);
+  RLT_CUDA_TRY(cudaGetLastError());
+  rlt::g_launches.fetch_add(1, std::memory_order_relaxed);
+  return RLT_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,481 @@
+// Block-table driven KV copy: pool -> pool (handoff), pool -> packed (pack) and
+// packed -> pool (scatter), one persistent kernel for all three.
+//
+// What it replaces in the reference: the Python walk of kv_segments over the
+// source and the peer tables (vllm_rlt/pd/transport.py:29-63), the
+// coalesce/partition step (:66-112) and the WRITE that NIXL performs with the
+// resulting descriptors (:182-201). Here the walk runs on the GPU: each CTA
+// derives its own slice of the (request, plane, block, tensor, layer) space
+// from the block tables, so no descriptor list is ever built.
+//
+// Work decomposition
+//   unit  = (request, logical block, destination plane, region, K|V, layer chunk)
+//   row   = one token's bytes of one layer inside a unit (token_bytes long)
+// A unit holds at most kMaxRows rows. For each unit the CTA first writes the
+// source and destination byte offset of every row to shared memory (this is
+// where block tables and per-token exit planes are read), then streams the
+// unit as a flat array of 16-byte vectors: thread t handles vectors t, t+256,
+// ... with kUnroll loads in flight before the first store. Row boundaries do
+// not matter to the flat loop, so 64-byte scale rows use every lane just like
+// 4 KiB code rows.
+//
+// Ragged requests: every CTA computes, with warp-shuffle prefix sums, the
+// exclusive scan of per-request block counts (and token counts, for packed
+// offsets) into shared memory, and finds a unit's request by binary search.
+//
+// HBM roofline: the kernel reads and writes each payload byte once; tables add
+// 4 bytes per (request, plane, block). Algorithmic bytes per token per plane
+// are 2 * layers * kv_heads * (head_dim * elt + scale) read and the same written.
+
+#include "common.cuh"
+
+namespace rlt {
+namespace {
+
+struct RegionParams {
+  const char* src_key;
+  const char* src_value;
+  char* dst_key;
+  char* dst_value;
+  long long block_bytes;
+  long long layer_bytes;
+  long long token_bytes;
+  int vec_bytes;        // 16, 4 or 1
+  int row_vecs;         // token_bytes / vec_bytes
+  unsigned row_magic;   // div_magic(row_vecs)
+  int layers_per_unit;  // layers one unit covers
+  int chunks;           // ceil(layers in slice / layers_per_unit)
+};
+
+struct TableCopyParams {
+  RegionParams region[2];
+  int num_regions;
+  int num_requests;
+  int table_width;
+  int src_planes;
+  int dst_planes;   // planes iterated: destination planes, or wire planes for pack
+  int block_size;
+  int src_blocks;
+  int dst_blocks;
+  const int* src_tables;
+  const int* dst_tables;
+  const int* tok_begin;
+  const int* tok_end;
+  const int* exit_planes;
+  const long long* exit_offsets;
+  int plane_bias;   // 0: source plane = min(p, exit); src_planes: source plane = exit
+  int layer_begin;
+  int layer_end;
+  int src_packed;   // source is the packed image (scatter)
+  int dst_packed;   // destination is the packed image (pack)
+  long long packed_token_bytes;  // 2 * layers in slice * (codes row + scales row)
+  long long packed_bytes;        // size of the packed image; rows past it are skipped
+  int* status;
+};
+
+template <typename T, int kUnroll>
+__device__ __forceinline__ void stream_rows(const char* __restrict__ src, char* __restrict__ dst,
+                                            const long long* __restrict__ src_off,
+                                            const long long* __restrict__ dst_off, int total_vecs,
+                                            int row_vecs, unsigned row_magic) {
+  // A skipped row has -1 in both offset tables. Row and offset are recomputed for the
+  // stores instead of being kept live, which keeps the kernel at 64 registers.
+  for (int base = threadIdx.x; base < total_vecs; base += kThreads * kUnroll) {
+    T regs[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const int i = base + u * kThreads;
+      if (i < total_vecs) {
+        const int row = static_cast<int>(__umulhi(static_cast<unsigned>(i), row_magic));
+        const long long so = src_off[row];
+        if (so >= 0) regs[u] = ld_stream(reinterpret_cast<const T*>(src + so) + (i - row * row_vecs));
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const int i = base + u * kThreads;
+      if (i < total_vecs) {
+        const int row = static_cast<int>(__umulhi(static_cast<unsigned>(i), row_magic));
+        const long long to = dst_off[row];
+        if (to >= 0) st_stream(reinterpret_cast<T*>(dst + to) + (i - row * row_vecs), regs[u]);
+      }
+    }
+  }
+}
+
+// Exclusive scans of per-request block counts and token counts, into shared memory.
+__device__ void scan_requests(const TableCopyParams& p, int* blk_off, int* tok_off) {
+  __shared__ int warp_sum[2][kThreads / 32];
+  __shared__ int carry[2];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (threadIdx.x == 0) {
+    carry[0] = carry[1] = 0;
+    blk_off[0] = tok_off[0] = 0;
+  }
+  __syncthreads();
+  for (int tile = 0; tile < p.num_requests; tile += kThreads) {
+    const int r = tile + threadIdx.x;
+    int nb = 0, nt = 0;
+    if (r < p.num_requests) {
+      const int b = p.tok_begin[r], e = p.tok_end[r];
+      if (e > b) {
+        const bool ok = b >= 0 && e <= p.table_width * p.block_size;
+        if (ok) {
+          nb = (e - 1) / p.block_size - b / p.block_size + 1;
+        } else {
+          report(p.status, RLT_STATUS_BAD_RANGE, r, b, e);
+        }
+        nt = e - b;  // a skipped request still owns its slot in the packed image
+      }
+    }
+    const int sb = warp_inclusive_scan(nb), st = warp_inclusive_scan(nt);
+    if (lane == 31) {
+      warp_sum[0][warp] = sb;
+      warp_sum[1][warp] = st;
+    }
+    __syncthreads();
+    if (warp == 0) {
+      const int vb = lane < kThreads / 32 ? warp_sum[0][lane] : 0;
+      const int vt = lane < kThreads / 32 ? warp_sum[1][lane] : 0;
+      const int ib = warp_inclusive_scan(vb), it = warp_inclusive_scan(vt);
+      if (lane < kThreads / 32) {
+        warp_sum[0][lane] = ib - vb;
+        warp_sum[1][lane] = it - vt;
+      }
+    }
+    __syncthreads();
+    if (r < p.num_requests) {
+      blk_off[r + 1] = carry[0] + warp_sum[0][warp] + sb;
+      tok_off[r + 1] = carry[1] + warp_sum[1][warp] + st;
+    }
+    __syncthreads();
+    if (threadIdx.x == kThreads - 1) {
+      carry[0] += warp_sum[0][warp] + sb;
+      carry[1] += warp_sum[1][warp] + st;
+    }
+    __syncthreads();
+  }
+}
+
+template <int kUnroll>
+__global__ void __launch_bounds__(kThreads, 4) table_copy_kernel(const TableCopyParams p) {
+  extern __shared__ int dyn_smem[];
+  int* blk_off = dyn_smem;                       // [num_requests + 1]
+  int* tok_off = dyn_smem + p.num_requests + 1;  // [num_requests + 1]
+  __shared__ long long row_src[2][kMaxRows];
+  __shared__ long long row_dst[2][kMaxRows];
+
+  scan_requests(p, blk_off, tok_off);
+
+  int units_per_plane = 0;
+  for (int g = 0; g < p.num_regions; ++g) units_per_plane += 2 * p.region[g].chunks;
+  const int units_per_block = units_per_plane * p.dst_planes;
+  const long long total_units = static_cast<long long>(blk_off[p.num_requests]) * units_per_block;
+  const int slice_layers = p.layer_end - p.layer_begin;
+
+  int parity = 0;
+  for (long long w = blockIdx.x; w < total_units; w += gridDim.x, parity ^= 1) {
+    const int blk_idx = static_cast<int>(w / units_per_block);
+    int sub = static_cast<int>(w - static_cast<long long>(blk_idx) * units_per_block);
+    const int plane = sub / units_per_plane;
+    sub -= plane * units_per_plane;
+    int g = 0;
+    if (sub >= 2 * p.region[0].chunks) {
+      g = 1;
+      sub -= 2 * p.region[0].chunks;
+    }
+    const RegionParams& rg = p.region[g];
+    const int kv = sub / rg.chunks;
+    const int chunk = sub - kv * rg.chunks;
+
+    // Request that owns block blk_idx: last r with blk_off[r] <= blk_idx.
+    int lo_r = 0, hi_r = p.num_requests;
+    while (hi_r - lo_r > 1) {
+      const int mid = (lo_r + hi_r) >> 1;
+      if (blk_off[mid] <= blk_idx) lo_r = mid; else hi_r = mid;
+    }
+    const int r = lo_r;
+    const int begin = p.tok_begin[r], end = p.tok_end[r];
+    const int logical = begin / p.block_size + (blk_idx - blk_off[r]);
+    const int tok_lo = max(begin, logical * p.block_size);
+    const int tok_hi = min(end, (logical + 1) * p.block_size);
+    const int n_tok = tok_hi - tok_lo;
+    const int layer0 = p.layer_begin + chunk * rg.layers_per_unit;
+    const int n_layers = min(rg.layers_per_unit, p.layer_end - layer0);
+    const int rows = n_layers * n_tok;
+
+    long long* rs = row_src[parity];
+    long long* rd = row_dst[parity];
+    if (threadIdx.x < rows) {
+      const int l_rel = threadIdx.x / n_tok;
+      const int tok = threadIdx.x - l_rel * n_tok;
+      const int t_abs = tok_lo + tok;
+      const int layer = layer0 + l_rel;
+      long long so = -1, dof = -1;
+      // Packed image: request, plane, block, region, tensor, layer, token (reference walk order).
+      long long packed = 0;
+      if (p.src_packed | p.dst_packed) {
+        const long long n_req = end - begin;
+        packed = (static_cast<long long>(tok_off[r]) * p.dst_planes + static_cast<long long>(plane) * n_req +
+                  (tok_lo - begin)) * p.packed_token_bytes;
+        if (g == 1) packed += 2ll * slice_layers * n_tok * p.region[0].token_bytes;
+        packed += (static_cast<long long>(kv) * slice_layers * n_tok +
+                   static_cast<long long>(layer - p.layer_begin) * n_tok + tok) * rg.token_bytes;
+      }
+      bool ok = true;
+      if ((p.src_packed | p.dst_packed) && packed + rg.token_bytes > p.packed_bytes) {
+        report(p.status, RLT_STATUS_BAD_RANGE, r, begin, end);
+        ok = false;
+      }
+      if (p.src_packed) {
+        so = packed;
+      } else {
+        int exit_plane = p.src_planes - 1;
+        if (p.exit_planes != nullptr) {
+          exit_plane = p.exit_planes[p.exit_offsets[r] + t_abs];
+          if (exit_plane < 0 || exit_plane >= p.src_planes) {
+            report(p.status, RLT_STATUS_BAD_PLANE, r, t_abs, exit_plane);
+            ok = false;
+            exit_plane = 0;
+          }
+        }
+        const int sp = min(plane + p.plane_bias, exit_plane);
+        const int sb = p.src_tables[(static_cast<long long>(r) * p.src_planes + sp) * p.table_width + logical];
+        if (sb < 0 || sb >= p.src_blocks) {
+          report(p.status, RLT_STATUS_BAD_BLOCK, r, logical, sb);
+          ok = false;
+        }
+        so = sb * rg.block_bytes + layer * rg.layer_bytes + (t_abs - logical * p.block_size) * rg.token_bytes;
+      }
+      if (p.dst_packed) {
+        dof = packed;
+      } else {
+        const int db = p.dst_tables[(static_cast<long long>(r) * p.dst_planes + plane) * p.table_width + logical];
+        if (db < 0 || db >= p.dst_blocks) {
+          report(p.status, RLT_STATUS_BAD_BLOCK, r, logical, db);
+          ok = false;
+        }
+        dof = db * rg.block_bytes + layer * rg.layer_bytes + (t_abs - logical * p.block_size) * rg.token_bytes;
+      }
+      rs[threadIdx.x] = ok ? so : -1;
+      rd[threadIdx.x] = ok ? dof : -1;
+    }
+    __syncthreads();  // one barrier per unit: the offset tables are double buffered
+
+    const char* src = p.src_packed ? rg.src_key : (kv ? rg.src_value : rg.src_key);
+    char* dst = p.dst_packed ? rg.dst_key : (kv ? rg.dst_value : rg.dst_key);
+    const int total_vecs = rows * rg.row_vecs;
+    if (rg.vec_bytes == 16) {
+      stream_rows<uint4, kUnroll>(src, dst, rs, rd, total_vecs, rg.row_vecs, rg.row_magic);
+    } else if (rg.vec_bytes == 4) {
+      stream_rows<uint32_t, kUnroll>(src, dst, rs, rd, total_vecs, rg.row_vecs, rg.row_magic);
+    } else {
+      stream_rows<uint8_t, kUnroll>(src, dst, rs, rd, total_vecs, rg.row_vecs, rg.row_magic);
+    }
+  }
+}
+
+bool dense(const RltRegion& r, const RltPool& pool) {
+  return r.token_bytes > 0 && r.layer_bytes == r.token_bytes * pool.block_size &&
+         r.block_bytes == r.layer_bytes * pool.num_layers;
+}
+
+int vector_width(const void* a, const void* b, const void* c, const void* d, long long token_bytes) {
+  const uintptr_t bits = reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) |
+                         reinterpret_cast<uintptr_t>(c) | reinterpret_cast<uintptr_t>(d) |
+                         static_cast<uintptr_t>(token_bytes);
+  if ((bits & 15u) == 0) return 16;
+  if ((bits & 3u) == 0) return 4;
+  return 1;
+}
+
+enum Direction { kDirect, kPack, kScatter };
+
+int launch_table_copy(Direction dir, const RltPool* src, const RltPool* dst, const RltBatch* batch,
+                      const RltOptions* opt, void* packed, long long packed_bytes, cudaStream_t stream) {
+  if (batch == nullptr || opt == nullptr) return RLT_E_INVALID;
+  const RltPool* any = dir == kScatter ? dst : src;
+  if (any == nullptr || (dir == kDirect && dst == nullptr)) return RLT_E_INVALID;
+  if (batch->num_requests < 1 || batch->table_width < 1 || batch->tok_begin == nullptr ||
+      batch->tok_end == nullptr)
+    return RLT_E_INVALID;
+  if (batch->num_requests > RLT_MAX_REQUESTS) return RLT_E_LIMIT;
+  if (any->block_size < 1 || any->block_size > kMaxBlockSize) return RLT_E_LIMIT;
+  if (any->num_layers < 1 || any->num_planes < 1 || any->num_blocks < 1) return RLT_E_INVALID;
+  if (dir != kScatter && batch->src_tables == nullptr) return RLT_E_INVALID;
+  if (dir != kPack && batch->dst_tables == nullptr) return RLT_E_INVALID;
+  if (opt->mode < RLT_MODE_ALL_PLANES || opt->mode > RLT_MODE_EXIT_ONLY) return RLT_E_INVALID;
+  if (opt->mode != RLT_MODE_ALL_PLANES && dir != kScatter &&
+      (batch->exit_planes == nullptr || batch->exit_offsets == nullptr))
+    return RLT_E_INVALID;
+  if (dir == kPack && opt->mode == RLT_MODE_DEDUP) return RLT_E_INVALID;
+
+  const int layer_begin = opt->layer_begin;
+  const int layer_end = opt->layer_end == 0 ? any->num_layers : opt->layer_end;
+  if (layer_begin < 0 || layer_end <= layer_begin || layer_end > any->num_layers) return RLT_E_INVALID;
+
+  const bool scales = any->scales.key != nullptr;
+  if (scales && any->scales.value == nullptr) return RLT_E_INVALID;
+  if (any->codes.key == nullptr || any->codes.value == nullptr) return RLT_E_INVALID;
+  if (!dense(any->codes, *any) || (scales && !dense(any->scales, *any))) return RLT_E_GEOMETRY;
+  if (dir == kDirect) {
+    if (dst->codes.key == nullptr || dst->codes.value == nullptr) return RLT_E_INVALID;
+    if ((dst->scales.key != nullptr) != scales) return RLT_E_GEOMETRY;
+    if (scales && dst->scales.value == nullptr) return RLT_E_INVALID;
+    if (dst->block_size != src->block_size || dst->num_layers != src->num_layers ||
+        dst->codes.token_bytes != src->codes.token_bytes || !dense(dst->codes, *dst) ||
+        dst->num_blocks < 1 || dst->num_planes < 1)
+      return RLT_E_GEOMETRY;
+    if (scales && (dst->scales.token_bytes != src->scales.token_bytes || !dense(dst->scales, *dst)))
+      return RLT_E_GEOMETRY;
+  }
+
+  TableCopyParams p{};
+  p.num_regions = scales ? 2 : 1;
+  p.num_requests = batch->num_requests;
+  p.table_width = batch->table_width;
+  p.block_size = any->block_size;
+  p.src_tables = batch->src_tables;
+  p.dst_tables = batch->dst_tables;
+  p.tok_begin = batch->tok_begin;
+  p.tok_end = batch->tok_end;
+  p.exit_planes = opt->mode == RLT_MODE_ALL_PLANES ? nullptr : batch->exit_planes;
+  p.exit_offsets = reinterpret_cast<const long long*>(batch->exit_offsets);
+  p.layer_begin = layer_begin;
+  p.layer_end = layer_end;
+  p.status = opt->status;
+  p.src_packed = dir == kScatter;
+  p.dst_packed = dir == kPack;
+
+  int wire_planes = opt->wire_planes;
+  if (dir == kDirect) {
+    p.src_planes = src->num_planes;
+    p.dst_planes = dst->num_planes;
+    p.src_blocks = src->num_blocks;
+    p.dst_blocks = dst->num_blocks;
+    if (opt->mode == RLT_MODE_EXIT_ONLY) {
+      if (dst->num_planes != 1) return RLT_E_GEOMETRY;
+    } else if (dst->num_planes != src->num_planes) {
+      return RLT_E_GEOMETRY;
+    }
+  } else if (dir == kPack) {
+    if (wire_planes == 0) wire_planes = opt->mode == RLT_MODE_EXIT_ONLY ? 1 : src->num_planes;
+    if (opt->mode == RLT_MODE_EXIT_ONLY ? wire_planes != 1 : wire_planes != src->num_planes)
+      return RLT_E_GEOMETRY;
+    p.src_planes = src->num_planes;
+    p.dst_planes = wire_planes;
+    p.src_blocks = src->num_blocks;
+  } else {
+    if (wire_planes == 0) wire_planes = dst->num_planes;
+    if (wire_planes != dst->num_planes) return RLT_E_GEOMETRY;
+    p.src_planes = wire_planes;
+    p.dst_planes = dst->num_planes;
+    p.dst_blocks = dst->num_blocks;
+    p.exit_planes = nullptr;
+  }
+  p.plane_bias = opt->mode == RLT_MODE_EXIT_ONLY ? p.src_planes : 0;
+
+  const int slice_layers = layer_end - layer_begin;
+  const long long row_total = any->codes.token_bytes + (scales ? any->scales.token_bytes : 0);
+  p.packed_token_bytes = 2ll * slice_layers * row_total;
+  if (dir != kDirect) {
+    if (packed == nullptr) return RLT_E_INVALID;
+    if (reinterpret_cast<uintptr_t>(packed) & 15u) return RLT_E_ALIGN;
+    if (packed_bytes < 0) return RLT_E_INVALID;
+    p.packed_bytes = packed_bytes;
+  }
+
+  const int unit_kib = (opt->variant >> 4) & 0xff;
+  const long long unit_target = unit_kib ? unit_kib * 16384ll : 131072ll;
+  for (int g = 0; g < p.num_regions; ++g) {
+    const RltRegion& s = g == 0 ? any->codes : any->scales;
+    RegionParams& rg = p.region[g];
+    rg.block_bytes = s.block_bytes;
+    rg.layer_bytes = s.layer_bytes;
+    rg.token_bytes = s.token_bytes;
+    if (dir == kScatter) {
+      rg.src_key = rg.src_value = static_cast<const char*>(packed);
+    } else {
+      const RltRegion& sr = g == 0 ? src->codes : src->scales;
+      rg.src_key = static_cast<const char*>(sr.key);
+      rg.src_value = static_cast<const char*>(sr.value);
+    }
+    if (dir == kPack) {
+      rg.dst_key = rg.dst_value = static_cast<char*>(packed);
+    } else {
+      const RltRegion& dr = g == 0 ? dst->codes : dst->scales;
+      rg.dst_key = static_cast<char*>(dr.key);
+      rg.dst_value = static_cast<char*>(dr.value);
+    }
+    // The packed offset of a scale row is a multiple of the scale row size plus a multiple of
+    // the code row size, so both row sizes bound the vector width of a packed-side region.
+    long long align_bytes = s.token_bytes;
+    if (dir != kDirect && scales) align_bytes |= any->codes.token_bytes | any->scales.token_bytes;
+    rg.vec_bytes = vector_width(rg.src_key, rg.src_value, rg.dst_key, rg.dst_value, align_bytes);
+    rg.row_vecs = static_cast<int>(s.token_bytes / rg.vec_bytes);
+    rg.row_magic = div_magic(static_cast<uint32_t>(rg.row_vecs));
+    long long lpu = unit_target / (s.token_bytes * any->block_size);
+    if (lpu < 1) lpu = 1;
+    if (lpu > slice_layers) lpu = slice_layers;
+    if (lpu * any->block_size > kMaxRows) lpu = kMaxRows / any->block_size;
+    // __umulhi row split is exact while (vector index) * row_vecs < 2^32.
+    while (lpu > 1 && lpu * any->block_size * rg.row_vecs * static_cast<long long>(rg.row_vecs) >= (1ll << 32)) --lpu;
+    if (lpu * any->block_size * rg.row_vecs * static_cast<long long>(rg.row_vecs) >= (1ll << 32)) return RLT_E_LIMIT;
+    rg.layers_per_unit = static_cast<int>(lpu);
+    rg.chunks = (slice_layers + rg.layers_per_unit - 1) / rg.layers_per_unit;
+  }
+  if (p.num_regions == 1) p.region[1].chunks = 0;
+
+  int sms = 0;
+  const int rc = sm_count(&sms);
+  if (rc != RLT_OK) return rc;
+  int per_sm = (opt->variant >> 12) & 0xf;
+  if (per_sm == 0) per_sm = 4;
+  int grid = sms * per_sm;
+  if (opt->grid_limit > 0 && grid > opt->grid_limit) grid = opt->grid_limit;
+  const size_t smem = 2 * (static_cast<size_t>(batch->num_requests) + 1) * sizeof(int);
+  switch (opt->variant & 0xf) {
+    case 0:
+      table_copy_kernel<8><<<grid, kThreads, smem, stream>>>(p);
+      break;
+    case 1:
+      table_copy_kernel<4><<<grid, kThreads, smem, stream>>>(p);
+      break;
+    default:
+      return RLT_E_INVALID;
+  }
+  RLT_CUDA_TRY(cudaGetLastError());
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return RLT_OK;
+}
+
+}  // namespace
+}  // namespace rlt
+
+extern "C" {
+
+int rlt_kv_handoff(const RltPool* src, const RltPool* dst, const RltBatch* batch,
+                   const RltOptions* options, rlt_stream_t stream) {
+  return rlt::launch_table_copy(rlt::kDirect, src, dst, batch, options, nullptr, 0,
+                                reinterpret_cast<cudaStream_t>(stream));
+}
+
+int64_t rlt_kv_packed_bytes(const RltPool* pool, int64_t total_tokens, int32_t wire_planes, int32_t layers) {
+  if (pool == nullptr || total_tokens < 0 || wire_planes < 1 || layers < 1) return RLT_E_INVALID;
+  const int64_t row = pool->codes.token_bytes + (pool->scales.key != nullptr ? pool->scales.token_bytes : 0);
+  return total_tokens * wire_planes * 2 * layers * row;
+}
+
+int rlt_kv_pack(const RltPool* src, const RltBatch* batch, const RltOptions* options, void* packed,
+                int64_t packed_bytes, rlt_stream_t stream) {
+  return rlt::launch_table_copy(rlt::kPack, src, nullptr, batch, options, packed, packed_bytes,
+                                reinterpret_cast<cudaStream_t>(stream));
+}
+
+int rlt_kv_scatter(const void* packed, int64_t packed_bytes, const RltPool* dst, const RltBatch* batch,
+                   const RltOptions* options, rlt_stream_t stream) {
+  return rlt::launch_table_copy(rlt::kScatter, nullptr, dst, batch, options, const_cast<void*>(packed),
+                                packed_bytes, reinterpret_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

@@ -1,0 +1,347 @@
+"""Python face of the KV-handoff kernels: argument checking and the C-ABI calls.
+
+These wrappers play the role that ``vllm_rlt/kernels/activation.py`` plays for
+the reference's one native op: validate on the host, then launch on the
+caller's current CUDA stream without synchronising. There is no fallback: if
+the native library is not built, or no CUDA device is present, the calls raise.
+
+Reference behaviour that is kept: bad ranges and tables raise ``ValueError``
+with the messages of ``kv_segments`` (vllm_rlt/pd/transport.py:29-47).
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass, field
+from typing import Sequence
+
+import numpy as np
+import torch
+
+from .. import _lib
+from .._lib import MODE_ALL_PLANES, MODE_DEDUP, MODE_EXIT_ONLY  # noqa: F401  (re-exported)
+
+
+def _stream_ptr(stream) -> int:
+    if stream is None:
+        return torch.cuda.current_stream().cuda_stream
+    if isinstance(stream, int):
+        return stream
+    return stream.cuda_stream
+
+
+# --------------------------------------------------------------------------- pools
+
+
+@dataclass(frozen=True)
+class Region:
+    """One K/V tensor pair as raw pointers and byte strides (``_kv_region``, vllm_rlt/pd/transport.py:18-26)."""
+
+    key_ptr: int
+    value_ptr: int
+    block_bytes: int
+    layer_bytes: int
+    token_bytes: int
+
+    @classmethod
+    def of(cls, key: torch.Tensor, value: torch.Tensor) -> "Region":
+        if key.shape != value.shape or key.dtype != value.dtype or key.device != value.device:
+            raise ValueError("key and value tensors must agree in shape, dtype and device")
+        if key.dim() < 4 or not key.is_contiguous() or not value.is_contiguous():
+            raise ValueError("pool tensors must be contiguous [blocks, layers, block_size, ...]")
+        e = key.element_size()
+        return cls(key.data_ptr(), value.data_ptr(), key.stride(0) * e, key.stride(1) * e, key.stride(2) * e)
+
+    def rebased(self, key_ptr: int, value_ptr: int) -> "Region":
+        return Region(key_ptr, value_ptr, self.block_bytes, self.layer_bytes, self.token_bytes)
+
+    def as_struct(self) -> _lib.RltRegion:
+        return _lib.RltRegion(self.key_ptr, self.value_ptr, self.block_bytes, self.layer_bytes, self.token_bytes)
+
+
+_NO_REGION = _lib.RltRegion(None, None, 0, 0, 0)
+
+
+@dataclass(frozen=True)
+class PoolView:
+    """Geometry and addresses of one paged KV pool, local or mapped from a peer GPU.
+
+    ``scales`` is set only when scale tensors travel: a dynamic-scale FP8 pool.
+    A fixed-scale FP8 pool keeps its (constant) scale tensors out of the handoff,
+    as the reference does (vllm_rlt/pd/transport.py:132-137).
+    """
+
+    codes: Region
+    scales: Region | None
+    num_blocks: int
+    block_size: int
+    num_layers: int
+    num_planes: int
+    device: int
+    keepalive: tuple = field(default=(), compare=False, repr=False)
+
+    @classmethod
+    def from_tensors(cls, key, value, num_planes, key_scale=None, value_scale=None) -> "PoolView":
+        if not key.is_cuda:
+            raise ValueError("KV pools must live on a CUDA device: the handoff has no CPU path")
+        codes = Region.of(key, value)
+        scales = None
+        keep = (key, value)
+        if key_scale is not None:
+            if key_scale.shape != key.shape[:-1] or key_scale.dtype != torch.float32:
+                raise ValueError("scale tensors must be float32 [blocks, layers, block_size, kv_heads]")
+            scales = Region.of(key_scale, value_scale)
+            keep += (key_scale, value_scale)
+        return cls(codes, scales, key.shape[0], key.shape[2], key.shape[1], int(num_planes), key.device.index, keep)
+
+    @classmethod
+    def from_cache(cls, cache) -> "PoolView":
+        """From a ``KVCacheManager``-shaped object (vllm_rlt/core/kv_cache_manager.py:261-271)."""
+        dynamic = cache.key_scale is not None and cache.fp8_scale is None
+        return cls.from_tensors(
+            cache.key_cache,
+            cache.value_cache,
+            cache.storage_depths,
+            cache.key_scale if dynamic else None,
+            cache.value_scale if dynamic else None,
+        )
+
+    def as_struct(self) -> _lib.RltPool:
+        return _lib.RltPool(
+            self.codes.as_struct(),
+            self.scales.as_struct() if self.scales is not None else _NO_REGION,
+            self.num_blocks,
+            self.block_size,
+            self.num_layers,
+            self.num_planes,
+        )
+
+    @property
+    def row_bytes(self) -> int:
+        return self.codes.token_bytes + (self.scales.token_bytes if self.scales is not None else 0)
+
+    def payload_bytes(self, tokens: int, planes: int, layers: int | None = None) -> int:
+        """Algorithmic payload of ``tokens`` tokens over ``planes`` planes."""
+        return 2 * (self.num_layers if layers is None else layers) * self.row_bytes * tokens * planes
+
+
+# --------------------------------------------------------------------------- batches
+
+
+class HandoffBatch:
+    """Per-request tables and ranges, staged in pinned memory and copied to the device once.
+
+    ``src_tables[r]`` / ``dst_tables[r]`` are the per-plane block tables of request
+    ``r`` (``plane_block_tables``); ``ranges[r]`` is its token range; ``exit_planes[r]``
+    (optional) holds one zero-based exit plane per token position of the request.
+    Validation mirrors ``kv_segments``: same conditions, same messages.
+    """
+
+    def __init__(
+        self,
+        src_tables: Sequence[Sequence[Sequence[int]]] | None,
+        dst_tables: Sequence[Sequence[Sequence[int]]] | None,
+        ranges: Sequence[tuple[int, int]],
+        *,
+        block_size: int,
+        exit_planes: Sequence[Sequence[int]] | None = None,
+        src_blocks: int | None = None,
+        dst_blocks: int | None = None,
+        device=None,
+        stream=None,
+    ):
+        n = len(ranges)
+        if n < 1:
+            raise ValueError("a handoff batch needs at least one request")
+        if n > _lib.MAX_REQUESTS:
+            raise ValueError(f"a handoff batch holds at most {_lib.MAX_REQUESTS} requests")
+        self.num_requests = n
+        self.block_size = block_size
+        self.ranges = [(int(s), int(e)) for s, e in ranges]
+        for s, e in self.ranges:
+            if not 0 <= s < e:
+                raise ValueError("invalid KV range")
+        self.total_tokens = sum(e - s for s, e in self.ranges)
+        sides = []
+        width = 1
+        for tables, limit in ((src_tables, src_blocks), (dst_tables, dst_blocks)):
+            if tables is None:
+                sides.append(None)
+                continue
+            if len(tables) != n:
+                raise ValueError("one table set per request is required")
+            planes = len(tables[0])
+            for req, (s, e) in zip(tables, self.ranges):
+                if len(req) != planes:
+                    raise ValueError("requests of one batch must have the same number of planes")
+                for table in req:
+                    if e > len(table) * block_size:
+                        raise ValueError("KV range exceeds allocation")
+                    width = max(width, len(table))
+            sides.append((tables, planes, limit))
+        self.table_width = width
+        arrays = []
+        for side in sides:
+            if side is None:
+                arrays.append(None)
+                continue
+            tables, planes, limit = side
+            a = np.zeros((n, planes, width), np.int32)
+            for r, req in enumerate(tables):
+                for p, table in enumerate(req):
+                    a[r, p, : len(table)] = table
+                s, e = self.ranges[r]
+                used = a[r, :, s // block_size : (e - 1) // block_size + 1]
+                if used.min() < 0 or (limit is not None and used.max() >= limit):
+                    raise ValueError("physical block outside registered pool")
+            arrays.append(a)
+        self.src_planes = arrays[0].shape[1] if arrays[0] is not None else 0
+        self.dst_planes = arrays[1].shape[1] if arrays[1] is not None else 0
+        begin = np.array([s for s, _ in self.ranges], np.int32)
+        end = np.array([e for _, e in self.ranges], np.int32)
+        exits = offsets = None
+        if exit_planes is not None:
+            if len(exit_planes) != n:
+                raise ValueError("one exit-plane array per request is required")
+            offsets = np.zeros(n, np.int64)
+            parts, at = [], 0
+            for r, (e_r, (s, e)) in enumerate(zip(exit_planes, self.ranges)):
+                e_r = np.asarray(e_r, np.int32)
+                if e_r.ndim != 1 or len(e_r) < e:
+                    raise ValueError("exit planes must cover every token position up to the range end")
+                offsets[r] = at
+                at += len(e_r)
+                parts.append(e_r)
+            exits = np.concatenate(parts)
+        # One pinned staging buffer, one host-to-device copy; int64 data first for alignment.
+        pieces = [("exit_offsets", offsets), ("src_tables", arrays[0]), ("dst_tables", arrays[1]),
+                  ("tok_begin", begin), ("tok_end", end), ("exit_planes", exits)]
+        layout, size = {}, 0
+        for name, a in pieces:
+            if a is None:
+                continue
+            size = (size + 15) & ~15
+            layout[name] = (size, a)
+            size += a.nbytes
+        self.metadata_bytes = size
+        device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        self._host = torch.empty(size, dtype=torch.uint8, pin_memory=True)
+        host = self._host.numpy()
+        for name, (at, a) in layout.items():
+            host[at : at + a.nbytes] = a.reshape(-1).view(np.uint8)
+        self._dev = torch.empty(size, dtype=torch.uint8, device=device)
+        if stream is None:
+            self._dev.copy_(self._host, non_blocking=True)
+        else:
+            with torch.cuda.stream(stream):
+                self._dev.copy_(self._host, non_blocking=True)
+        base = self._dev.data_ptr()
+        self._ptr = {name: base + at for name, (at, _) in layout.items()}
+        self.has_exit = exits is not None
+
+    def as_struct(self) -> _lib.RltBatch:
+        g = self._ptr.get
+        return _lib.RltBatch(
+            self.num_requests, self.table_width, g("src_tables"), g("dst_tables"),
+            g("tok_begin"), g("tok_end"), g("exit_planes"), g("exit_offsets"),
+        )
+
+
+def new_status(device=None) -> torch.Tensor:
+    """A zeroed int32 status word array the kernels report data errors into."""
+    return torch.zeros(_lib.STATUS_WORDS, dtype=torch.int32, device=device or "cuda")
+
+
+_STATUS_TEXT = {
+    _lib.STATUS_BAD_RANGE: "KV range exceeds allocation",
+    _lib.STATUS_BAD_BLOCK: "physical block outside registered pool",
+    _lib.STATUS_BAD_PLANE: "exit plane outside the pool's planes",
+    _lib.STATUS_TIMEOUT: "timed out waiting for the peer's completion flag",
+}
+
+
+def raise_for_status(status: torch.Tensor) -> None:
+    """Synchronising read of a status array; raises like the reference's planner would have."""
+    words = status.tolist()
+    if words[0] == _lib.STATUS_OK:
+        return
+    text = _STATUS_TEXT.get(words[0], f"device status {words[0]}")
+    if words[0] == _lib.STATUS_TIMEOUT:
+        raise TimeoutError(f"{text} (last value {words[1]})")
+    raise ValueError(f"{text} (request {words[1]}, detail {words[2]}, {words[3]})")
+
+
+def _options(mode, layer_begin, layer_end, wire_planes, status, grid_limit, variant) -> _lib.RltOptions:
+    return _lib.RltOptions(
+        int(mode), int(layer_begin), int(layer_end), int(wire_planes),
+        status.data_ptr() if status is not None else None, int(grid_limit), int(variant),
+    )
+
+
+# --------------------------------------------------------------------------- ops
+
+
+def kv_handoff(src: PoolView, dst: PoolView, batch: HandoffBatch, *, mode=MODE_ALL_PLANES,
+               layer_begin=0, layer_end=0, status=None, stream=None, grid_limit=0, variant=0) -> None:
+    """Pool-to-pool handoff of a batch, straight from source blocks to destination blocks."""
+    lib = _lib.load()
+    s, d, b = src.as_struct(), dst.as_struct(), batch.as_struct()
+    o = _options(mode, layer_begin, layer_end, 0, status, grid_limit, variant)
+    _lib.check(lib.rlt_kv_handoff(C.byref(s), C.byref(d), C.byref(b), C.byref(o), _stream_ptr(stream)), "rlt_kv_handoff")
+
+
+def packed_bytes(pool: PoolView, total_tokens: int, wire_planes: int, layers: int | None = None) -> int:
+    lib = _lib.load()
+    s = pool.as_struct()
+    n = lib.rlt_kv_packed_bytes(C.byref(s), total_tokens, wire_planes, pool.num_layers if layers is None else layers)
+    if n < 0:
+        _lib.check(int(n), "rlt_kv_packed_bytes")
+    return int(n)
+
+
+def kv_pack(src: PoolView, batch: HandoffBatch, out: torch.Tensor, *, mode=MODE_ALL_PLANES, layer_begin=0,
+            layer_end=0, wire_planes=0, status=None, stream=None, grid_limit=0, variant=0) -> None:
+    """Gather a batch into ``out`` (uint8, contiguous) in the reference's segment order."""
+    if out.dtype != torch.uint8 or not out.is_contiguous() or not out.is_cuda:
+        raise ValueError("packed buffer must be a contiguous CUDA uint8 tensor")
+    lib = _lib.load()
+    s, b = src.as_struct(), batch.as_struct()
+    o = _options(mode, layer_begin, layer_end, wire_planes, status, grid_limit, variant)
+    _lib.check(lib.rlt_kv_pack(C.byref(s), C.byref(b), C.byref(o), out.data_ptr(), out.numel(), _stream_ptr(stream)), "rlt_kv_pack")
+
+
+def kv_scatter(packed: torch.Tensor, dst: PoolView, batch: HandoffBatch, *, layer_begin=0, layer_end=0,
+               wire_planes=0, status=None, stream=None, grid_limit=0, variant=0) -> None:
+    """Write a packed image into the destination blocks of a batch."""
+    if packed.dtype != torch.uint8 or not packed.is_contiguous() or not packed.is_cuda:
+        raise ValueError("packed buffer must be a contiguous CUDA uint8 tensor")
+    lib = _lib.load()
+    d, b = dst.as_struct(), batch.as_struct()
+    o = _options(MODE_ALL_PLANES, layer_begin, layer_end, wire_planes, status, grid_limit, variant)
+    _lib.check(lib.rlt_kv_scatter(packed.data_ptr(), packed.numel(), C.byref(d), C.byref(b), C.byref(o), _stream_ptr(stream)), "rlt_kv_scatter")
+
+
+def kv_push(src_ptr: int, dst_ptr: int, nbytes: int, *, stream=None) -> None:
+    """Copy one byte range; ``dst_ptr`` may be a peer mapping."""
+    _lib.check(_lib.load().rlt_kv_push(src_ptr, dst_ptr, nbytes, _stream_ptr(stream)), "rlt_kv_push")
+
+
+def kv_copy_segments(segments: torch.Tensor, *, stream=None) -> None:
+    """Copy ``int64 [n, 3]`` (source address, destination address, bytes) triples held on the device."""
+    if segments.dtype != torch.int64 or segments.dim() != 2 or segments.shape[1] != 3 or not segments.is_contiguous():
+        raise ValueError("segments must be a contiguous int64 [n, 3] tensor")
+    if not segments.is_cuda:
+        raise ValueError("segments must live on the device")
+    _lib.check(_lib.load().rlt_kv_copy_segments(segments.data_ptr(), segments.shape[0], _stream_ptr(stream)), "rlt_kv_copy_segments")
+
+
+def kv_signal(flag_ptr: int, value: int, *, stream=None) -> None:
+    _lib.check(_lib.load().rlt_kv_signal(flag_ptr, value, _stream_ptr(stream)), "rlt_kv_signal")
+
+
+def kv_wait(flag_ptr: int, value: int, timeout_ns: int, status: torch.Tensor, *, stream=None) -> None:
+    _lib.check(_lib.load().rlt_kv_wait(flag_ptr, value, timeout_ns, status.data_ptr(), _stream_ptr(stream)), "rlt_kv_wait")
+
+
+def kernel_launches() -> int:
+    return int(_lib.load().rlt_kernel_launches())
