@@ -1,0 +1,163 @@
+"""GPU parity for the descriptor-list copy, the range push, the completion flags and the torch ops."""
+
+import random
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import handoff_oracle as ho
+from tests.conftest import golden_json, golden_npz, load_pool, oracle_pool
+from tests.gpu_support import GpuPool, assert_pools_equal
+
+pytestmark = pytest.mark.gpu
+
+
+def kh():
+    from vllm_rlt_b200.kernels import kv_handoff
+
+    return kv_handoff
+
+
+def device_address(oracle, gpu, address):
+    """Oracle synthetic address -> address of the same byte in the GPU copy of the pool."""
+    names = ["key", "value", "key_scale", "value_scale"]
+    tensors = dict(zip(["key", "value", "key_scale", "value_scale"], [gpu.key_cache, gpu.value_cache, gpu.key_scale, gpu.value_scale]))
+    for name in names:
+        t = getattr(oracle, name)
+        if t is not None and t.base <= address < t.base + t.flat.size:
+            return tensors[name].data_ptr() + (address - t.base)
+    raise AssertionError("address outside pool")
+
+
+@pytest.mark.parametrize("case", golden_json("handoff.json"), ids=lambda c: c["name"])
+def test_descriptor_lists_of_the_reference_planner_are_written_exactly(case):
+    """Drive the copy with the (local, remote) lists partition_segments yields, like NixlConnector.submit."""
+    k = kh()
+    arrays = golden_npz(case["name"])
+    P = oracle_pool(case["kind"], case["shape"])
+    D = oracle_pool(case["kind"], case["shape"], device=1, base=1 << 40)
+    load_pool(P, arrays, "src_")
+    load_pool(D, arrays, "dst_before_")
+    gp, gd = GpuPool(P), GpuPool(D)
+    submissions = 0
+    for req in case["requests"]:
+        source = ho.kv_segments(P.info(), req["src_tables"], req["start"], req["end"])
+        target = ho.kv_segments(D.info(), req["dst_tables"], req["start"], req["end"])
+        for local, remote, size in ho.partition_segments(source, target, case["byte_limit"], case["descriptor_limit"]):
+            rows = [(device_address(P, gp, a), device_address(D, gd, b), n) for (a, n, _), (b, _, _) in zip(local, remote)]
+            assert sum(r[2] for r in rows) == size
+            k.kv_copy_segments(torch.tensor(rows, dtype=torch.int64, device="cuda"))
+            submissions += 1
+    assert submissions >= len(case["requests"])
+    load_pool(D, arrays, "dst_after_")
+    assert_pools_equal(gd, D)
+
+
+def test_segments_of_any_alignment_and_size():
+    k = kh()
+    rng = random.Random(9)
+    n = 3 << 20
+    src = torch.randint(0, 256, (n,), dtype=torch.uint8, device="cuda")
+    dst = torch.full((n,), 0xA5, dtype=torch.uint8, device="cuda")
+    want = np.full(n, 0xA5, np.uint8)
+    host = src.cpu().numpy()
+    rows, at = [], 0
+    for size in [1, 3, 15, 16, 17, 64, 100, 4096, 4099, 65536, 65537, 200_000, 0, 1 << 20]:
+        s_off = rng.randrange(0, n - size - 1)
+        at += rng.choice([0, 1, 4, 16, 3])
+        rows.append((src.data_ptr() + s_off, dst.data_ptr() + at, size))
+        want[at : at + size] = host[s_off : s_off + size]
+        at += size
+    k.kv_copy_segments(torch.tensor(rows, dtype=torch.int64, device="cuda"))
+    assert np.array_equal(dst.cpu().numpy(), want)
+
+
+def test_more_segments_than_threads():
+    k = kh()
+    count, size = 1500, 48
+    src = torch.randint(0, 256, (count * size,), dtype=torch.uint8, device="cuda")
+    dst = torch.zeros(count * size, dtype=torch.uint8, device="cuda")
+    perm = list(range(count))
+    random.Random(2).shuffle(perm)
+    rows = [(src.data_ptr() + i * size, dst.data_ptr() + j * size, size) for i, j in enumerate(perm)]
+    k.kv_copy_segments(torch.tensor(rows, dtype=torch.int64, device="cuda"))
+    want = src.cpu().numpy().reshape(count, size)
+    got = dst.cpu().numpy().reshape(count, size)
+    assert np.array_equal(got[perm], want)
+
+
+@pytest.mark.parametrize("size", [0, 1, 15, 16, 4099, (1 << 20) + 5, 5 << 20])
+@pytest.mark.parametrize("shift", [(0, 0), (1, 0), (0, 4), (16, 16)])
+def test_push_copies_exactly_the_range(size, shift):
+    k = kh()
+    src = torch.randint(0, 256, (size + 64,), dtype=torch.uint8, device="cuda")
+    dst = torch.full((size + 64,), 0xA5, dtype=torch.uint8, device="cuda")
+    k.kv_push(src.data_ptr() + shift[0], dst.data_ptr() + shift[1], size)
+    want = np.full(size + 64, 0xA5, np.uint8)
+    want[shift[1] : shift[1] + size] = src.cpu().numpy()[shift[0] : shift[0] + size]
+    assert np.array_equal(dst.cpu().numpy(), want)
+
+
+def test_signal_then_wait_and_a_wait_that_runs_out():
+    k = kh()
+    flag = torch.zeros(1, dtype=torch.int64, device="cuda")
+    status = k.new_status()
+    k.kv_signal(flag.data_ptr(), 7)
+    k.kv_wait(flag.data_ptr(), 7, 50_000_000, status)
+    k.raise_for_status(status)
+    assert flag.item() == 7
+    # nothing ever sets 8: the wait gives up after 2 ms and reports it; the context stays usable
+    k.kv_wait(flag.data_ptr(), 8, 2_000_000, status)
+    with pytest.raises(TimeoutError, match="last value 7"):
+        k.raise_for_status(status)
+    assert torch.ones(4, device="cuda").sum().item() == 4
+
+
+def test_torch_ops_match_the_c_abi_path():
+    from vllm_rlt_b200 import _build
+
+    torch.ops.load_library(str(_build.PACKAGE / _build.OPS_NAME))
+    ops = torch.ops.vllm_rlt
+    case = golden_json("handoff.json")[1]  # fp8 with travelling scales
+    arrays = golden_npz(case["name"])
+    P = oracle_pool(case["kind"], case["shape"])
+    D = oracle_pool(case["kind"], case["shape"], device=1, base=1 << 40)
+    load_pool(P, arrays, "src_")
+    load_pool(D, arrays, "dst_before_")
+    gp, gd, gd2 = GpuPool(P), GpuPool(D), GpuPool(D)
+    reqs = case["requests"]
+    width = max(len(t) for r in reqs for t in r["src_tables"])
+
+    def table_tensor(key):
+        a = np.zeros((len(reqs), P.planes, width), np.int32)
+        for i, r in enumerate(reqs):
+            for p, t in enumerate(r[key]):
+                a[i, p, : len(t)] = t
+        return torch.from_numpy(a).cuda()
+
+    st, dt = table_tensor("src_tables"), table_tensor("dst_tables")
+    begin = torch.tensor([r["start"] for r in reqs], dtype=torch.int32, device="cuda")
+    end = torch.tensor([r["end"] for r in reqs], dtype=torch.int32, device="cuda")
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    ops.kv_handoff(gp.key_cache, gp.value_cache, gp.key_scale, gp.value_scale, gd.key_cache, gd.value_cache,
+                   gd.key_scale, gd.value_scale, st, dt, begin, end, None, None, 0, 0, 0, status)
+    assert status.tolist() == [0, 0, 0, 0]
+    load_pool(D, arrays, "dst_after_")
+    assert_pools_equal(gd, D)
+    packed = torch.zeros(arrays["packed"].size, dtype=torch.uint8, device="cuda")
+    ops.kv_pack(gp.key_cache, gp.value_cache, gp.key_scale, gp.value_scale, st, begin, end, None, None, 0, 0, 0, packed, status)
+    assert np.array_equal(packed.cpu().numpy(), arrays["packed"])
+    ops.kv_scatter(packed, dt, begin, end, 0, 0, gd2.key_cache, gd2.value_cache, gd2.key_scale, gd2.value_scale, status)
+    assert_pools_equal(gd2, D)
+    # same-device "peer" form: destination given as raw addresses
+    gd3 = GpuPool(oracle_pool(case["kind"], case["shape"], device=1, base=1 << 40))
+    for t, name in zip(gd3.tensors(), ["key", "value", "key_scale", "value_scale"]):
+        t.view(torch.uint8).copy_(torch.from_numpy(arrays["dst_before_" + name].reshape(-1)).cuda().view(t.view(torch.uint8).shape))
+    ops.kv_handoff_peer(gp.key_cache, gp.value_cache, gp.key_scale, gp.value_scale, gd3.key_cache.data_ptr(),
+                        gd3.value_cache.data_ptr(), gd3.key_scale.data_ptr(), gd3.value_scale.data_ptr(),
+                        D.num_blocks, D.planes, st, dt, begin, end, None, None, 0, 0, 0, status)
+    assert_pools_equal(gd3, D)
+    with pytest.raises(RuntimeError, match="contiguous"):
+        ops.kv_handoff(gp.key_cache.transpose(0, 1), gp.value_cache, None, None, gd.key_cache, gd.value_cache,
+                       None, None, st, dt, begin, end, None, None, 0, 0, 0, None)

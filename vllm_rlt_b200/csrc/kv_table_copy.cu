@@ -80,13 +80,14 @@ __device__ __forceinline__ void stream_rows(const char* __restrict__ src, char* 
                                             int row_vecs, unsigned row_magic) {
   // A skipped row has -1 in both offset tables. Row and offset are recomputed for the
   // stores instead of being kept live, which keeps the kernel at 64 registers.
+  // row_magic == 0 marks one-vector rows, for which no 32-bit multiplier exists.
   for (int base = threadIdx.x; base < total_vecs; base += kThreads * kUnroll) {
     T regs[kUnroll];
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
       const int i = base + u * kThreads;
       if (i < total_vecs) {
-        const int row = static_cast<int>(__umulhi(static_cast<unsigned>(i), row_magic));
+        const int row = row_magic ? static_cast<int>(__umulhi(static_cast<unsigned>(i), row_magic)) : i;
         const long long so = src_off[row];
         if (so >= 0) regs[u] = ld_stream(reinterpret_cast<const T*>(src + so) + (i - row * row_vecs));
       }
@@ -95,7 +96,7 @@ __device__ __forceinline__ void stream_rows(const char* __restrict__ src, char* 
     for (int u = 0; u < kUnroll; ++u) {
       const int i = base + u * kThreads;
       if (i < total_vecs) {
-        const int row = static_cast<int>(__umulhi(static_cast<unsigned>(i), row_magic));
+        const int row = row_magic ? static_cast<int>(__umulhi(static_cast<unsigned>(i), row_magic)) : i;
         const long long to = dst_off[row];
         if (to >= 0) st_stream(reinterpret_cast<T*>(dst + to) + (i - row * row_vecs), regs[u]);
       }
@@ -413,7 +414,7 @@ int launch_table_copy(Direction dir, const RltPool* src, const RltPool* dst, con
     if (dir != kDirect && scales) align_bytes |= any->codes.token_bytes | any->scales.token_bytes;
     rg.vec_bytes = vector_width(rg.src_key, rg.src_value, rg.dst_key, rg.dst_value, align_bytes);
     rg.row_vecs = static_cast<int>(s.token_bytes / rg.vec_bytes);
-    rg.row_magic = div_magic(static_cast<uint32_t>(rg.row_vecs));
+    rg.row_magic = rg.row_vecs == 1 ? 0u : div_magic(static_cast<uint32_t>(rg.row_vecs));
     long long lpu = unit_target / (s.token_bytes * any->block_size);
     if (lpu < 1) lpu = 1;
     if (lpu > slice_layers) lpu = slice_layers;
