@@ -1,0 +1,84 @@
+"""The multi-rank metadata exchange on CPU: two gloo ranks, decode tables and handles reach the prefill rank."""
+
+import os
+import socket
+
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+from vllm_rlt_b200.pd import exchange
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, out):
+    import torch.distributed as dist
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        is_prefill, index, partners = exchange.pairing(rank, world)
+        lengths, planes, width, page = [9, 16, 3], 2, 4, 4
+        tables_msg = torch.zeros((len(lengths), planes, width), dtype=torch.int32)
+        handles_msg = torch.zeros((2, exchange.HANDLE_ROW), dtype=torch.uint8)
+        if not is_prefill:
+            tables = [[[10 * r + p + j for j in range(-(-n // page))] for p in range(planes)] for r, n in enumerate(lengths)]
+            tables_msg.copy_(exchange.encode_tables(tables, planes, width))
+            exported = [{"handle": bytes([rank, k] * 32).hex(), "offset": 4096 * k + 48} for k in range(2)]
+            handles_msg.copy_(exchange.encode_handles(exported))
+        all_tables, all_handles = exchange.all_gather_metadata(tables_msg, handles_msg)
+        if is_prefill:
+            got_tables = exchange.decode_tables(all_tables[partners[0]], lengths, page)
+            got_handles = exchange.decode_handles(all_handles[partners[0]])
+            out.put((rank, got_tables, got_handles))
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_rank_exchange_delivers_tables_and_handles():
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, out)) for r in range(2)]
+    for p in procs:
+        p.start()
+    rank, tables, handles = out.get(timeout=120)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert rank == 0
+    assert tables == [[[0, 1, 2], [1, 2, 3]], [[10, 11, 12, 13], [11, 12, 13, 14]], [[20], [21]]]
+    assert handles == [{"handle": bytes([1, 0] * 32).hex(), "offset": 48}, {"handle": bytes([1, 1] * 32).hex(), "offset": 4144}]
+
+
+def test_pairing_for_even_and_uneven_splits():
+    assert exchange.pairing(0, 2) == (True, 0, [1])
+    assert exchange.pairing(1, 2) == (False, 0, [0])
+    assert [exchange.pairing(r, 8)[2] for r in range(8)] == [[4], [5], [6], [7], [0], [1], [2], [3]]
+    # 2P:6D - each prefill rank feeds three decode ranks; 6P:2D - three prefill ranks share one decode rank
+    assert exchange.pairing(0, 8, 2) == (True, 0, [2, 4, 6])
+    assert exchange.pairing(1, 8, 2) == (True, 1, [3, 5, 7])
+    assert exchange.pairing(5, 8, 2) == (False, 3, [1])
+    assert exchange.pairing(7, 8, 6) == (False, 1, [1, 3, 5])
+    assert exchange.pairing(4, 8, 6) == (True, 4, [6])
+    with pytest.raises(ValueError):
+        exchange.pairing(0, 1)
+    with pytest.raises(ValueError):
+        exchange.pairing(0, 4, 4)
+
+
+def test_table_codec_round_trip_and_errors():
+    tables = [[[5, 6, 7], [8, 9, 1]], [[2], [3]]]
+    msg = exchange.encode_tables(tables, 2, 3)
+    assert msg.dtype == torch.int32 and tuple(msg.shape) == (2, 2, 3)
+    assert exchange.decode_tables(msg, [12, 4], 4) == tables
+    with pytest.raises(ValueError):
+        exchange.encode_tables(tables, 3, 3)
+    with pytest.raises(ValueError):
+        exchange.encode_tables(tables, 2, 2)
