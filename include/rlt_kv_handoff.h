@@ -212,6 +212,16 @@ RLT_API int rlt_kv_wait(const uint64_t* flag, uint64_t value, int64_t timeout_ns
                         rlt_stream_t stream);
 #define RLT_MAX_WAIT_NS 2000000000LL
 
+/*
+ * Stream-ordered post of a 64-byte message into a mailbox slot (device, peer or
+ * registered host memory, 16-byte aligned): bytes 8..63 are written first, then
+ * the 8-byte stamp at offset 0 with release semantics at system scope, so a
+ * reader that sees the stamp also sees the body and every earlier write of the
+ * stream. Carries the (transfer id, sequence) notification that NIXL attaches
+ * to each WRITE (vllm_rlt/pd/transport.py:186, :222-229).
+ */
+RLT_API int rlt_kv_post(void* slot, const uint8_t body[56], uint64_t stamp, rlt_stream_t stream);
+
 /* --- peer memory ---------------------------------------------------------------------------- */
 
 /* Enable access from device `device` to memory of device `peer` (idempotent). */
@@ -230,6 +240,15 @@ RLT_API int rlt_ipc_export(const void* ptr, uint8_t handle[RLT_IPC_HANDLE_BYTES]
 /* Map an exported allocation into this process on the current device. */
 RLT_API int rlt_ipc_open(const uint8_t handle[RLT_IPC_HANDLE_BYTES], void** base);
 RLT_API int rlt_ipc_close(void* base);
+
+/*
+ * Make a range of ordinary host memory (for instance a POSIX shared-memory
+ * mapping that another process polls) writable from kernels on the current
+ * device; returns the device-side address. The receiver of a handoff keeps its
+ * mailbox in such memory so that it can poll without any CUDA call.
+ */
+RLT_API int rlt_host_register(void* host, size_t bytes, void** device_ptr);
+RLT_API int rlt_host_unregister(void* host);
 
 #ifdef __cplusplus
 }

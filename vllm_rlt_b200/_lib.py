@@ -84,6 +84,9 @@ SIGNATURES = {
     "rlt_kv_copy_segments": (C.c_int, [C.c_void_p, C.c_int32, C.c_void_p]),
     "rlt_kv_signal": (C.c_int, [C.c_void_p, C.c_uint64, C.c_void_p]),
     "rlt_kv_wait": (C.c_int, [C.c_void_p, C.c_uint64, C.c_int64, C.c_void_p, C.c_void_p]),
+    "rlt_kv_post": (C.c_int, [C.c_void_p, C.c_void_p, C.c_uint64, C.c_void_p]),
+    "rlt_host_register": (C.c_int, [C.c_void_p, C.c_size_t, C.POINTER(C.c_void_p)]),
+    "rlt_host_unregister": (C.c_int, [C.c_void_p]),
     "rlt_peer_enable": (C.c_int, [C.c_int, C.c_int]),
     "rlt_peer_can_access": (C.c_int, [C.c_int, C.c_int]),
     "rlt_ipc_export": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(C.c_int64)]),

@@ -9,6 +9,8 @@
 // The wait never spins without a limit: it watches %globaltimer and gives up
 // after the caller's timeout, recording what it last saw.
 
+#include <cstring>
+
 #include "common.cuh"
 
 namespace rlt {
@@ -18,6 +20,19 @@ __global__ void signal_kernel(unsigned long long* flag, unsigned long long value
   if (threadIdx.x == 0 && blockIdx.x == 0) {
     __threadfence_system();
     asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(flag), "l"(value) : "memory");
+  }
+}
+
+struct PostBody {
+  unsigned long long words[7];
+};
+
+__global__ void post_kernel(unsigned long long* slot, const PostBody body, unsigned long long stamp) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) {
+#pragma unroll
+    for (int i = 0; i < 7; ++i) slot[1 + i] = body.words[i];
+    __threadfence_system();
+    asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(slot), "l"(stamp) : "memory");
   }
 }
 
@@ -52,6 +67,18 @@ int rlt_kv_signal(uint64_t* flag, uint64_t value, rlt_stream_t stream) {
   if (reinterpret_cast<uintptr_t>(flag) & 7u) return RLT_E_ALIGN;
   rlt::signal_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       reinterpret_cast<unsigned long long*>(flag), value);
+  RLT_CUDA_TRY(cudaGetLastError());
+  rlt::g_launches.fetch_add(1, std::memory_order_relaxed);
+  return RLT_OK;
+}
+
+int rlt_kv_post(void* slot, const uint8_t body[56], uint64_t stamp, rlt_stream_t stream) {
+  if (slot == nullptr || body == nullptr) return RLT_E_INVALID;
+  if (reinterpret_cast<uintptr_t>(slot) & 15u) return RLT_E_ALIGN;
+  rlt::PostBody b;
+  std::memcpy(b.words, body, sizeof(b.words));
+  rlt::post_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      static_cast<unsigned long long*>(slot), b, stamp);
   RLT_CUDA_TRY(cudaGetLastError());
   rlt::g_launches.fetch_add(1, std::memory_order_relaxed);
   return RLT_OK;

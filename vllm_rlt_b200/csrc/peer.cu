@@ -77,4 +77,21 @@ int rlt_ipc_close(void* base) {
   return RLT_OK;
 }
 
+int rlt_host_register(void* host, size_t bytes, void** device_ptr) {
+  if (host == nullptr || bytes == 0 || device_ptr == nullptr) return RLT_E_INVALID;
+  RLT_CUDA_TRY(cudaHostRegister(host, bytes, cudaHostRegisterPortable | cudaHostRegisterMapped));
+  const cudaError_t e = cudaHostGetDevicePointer(device_ptr, host, 0);
+  if (e != cudaSuccess) {
+    (void)cudaHostUnregister(host);
+    return rlt::cuda_fail(e);
+  }
+  return RLT_OK;
+}
+
+int rlt_host_unregister(void* host) {
+  if (host == nullptr) return RLT_E_INVALID;
+  RLT_CUDA_TRY(cudaHostUnregister(host));
+  return RLT_OK;
+}
+
 }  // extern "C"
