@@ -18,8 +18,7 @@ def make_pair(config=None, **cache_kw):
     pc.key_cache.view(torch.uint8).random_(0, 256)
     pc.value_cache.view(torch.uint8).random_(0, 256)
     p = tr.B200Transport("p0", pc, torch.zeros(2, 16), config, backend=FakeBackend())
-    d = tr.B200Transport("d0", dc, torch.zeros(2, 16), config, backend=FakeBackend())
-    d.info["device"] = 1  # two workers never share a device (PDConfig enforces distinct devices)
+    d = tr.B200Transport("d0", dc, torch.zeros(2, 16), config, backend=FakeBackend(), lane=1)
     p.connect(d.info)
     d.connect(p.info)
     return p, d
@@ -113,7 +112,7 @@ def test_descriptor_outside_registered_memory_is_rejected():
 @pytest.mark.parametrize("key", ["block_size", "num_layers", "depths", "hidden_bytes", "kv_dtype", "token_bytes"])
 def test_handshake_rejects_geometry_mismatch(key):
     p, d = make_pair()
-    peer = dict(d.info, agent="d1", device=2)
+    peer = dict(d.info, agent="d1", metadata=dict(d.info["metadata"], lane=2))
     peer[key] = "x" if key == "kv_dtype" else peer[key] + 1
     with pytest.raises(ValueError, match=f"PD KV geometry mismatch: {key}"):
         p.connect(peer)
@@ -128,12 +127,12 @@ def test_handshake_rejects_scale_mismatch():
     assert a.info["scale_region"] is not None and b.info["scale_region"] is None
     assert len(a.storage) == 5 and len(b.storage) == 3  # dynamic scales are registered, fixed ones are not
     with pytest.raises(ValueError, match="same calibrated FP8 scale"):
-        a.connect(dict(b.info, device=1))
+        a.connect(b.info)
     with pytest.raises(ValueError, match="same calibrated FP8 scale"):
-        b.connect(dict(c.info, device=1))
-    b.connect(dict(b.info, agent="b2", device=1))
-    with pytest.raises(ValueError, match="shares device"):
-        b.connect(dict(b.info, agent="b3", device=1))
+        b.connect(c.info)
+    b.connect(dict(b.info, agent="b2", metadata=dict(b.info["metadata"], lane=1)))
+    with pytest.raises(ValueError, match="shares mailbox lane"):
+        b.connect(dict(b.info, agent="b3", metadata=dict(b.info["metadata"], lane=1)))
     for t in (a, b, c):
         t.close()
 

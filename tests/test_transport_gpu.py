@@ -85,9 +85,7 @@ def test_descriptor_and_table_paths_write_the_same_bytes(fp8, two_gpus):
         hidden_p = torch.arange(4 * 64, dtype=torch.bfloat16, device=dev_p).reshape(4, 64)
         hidden_d = torch.zeros(4, 64, dtype=torch.bfloat16, device=dev_d)
         p = B200Transport("p0", P, hidden_p, config)
-        d = B200Transport("d0", D, hidden_d, config)
-        if not two_gpus:
-            d.info["device"] = 9  # one GPU plays both workers; lanes are keyed by the advertised device
+        d = B200Transport("d0", D, hidden_d, config, lane=9)  # one GPU may play both workers: distinct lanes
         p.connect(d.info)
         d.connect(p.info)
         want = expected_destination(P, D, requests)
@@ -146,8 +144,7 @@ def test_notification_is_only_visible_after_the_bytes():
     assert P.allocate("a", 4096) and D.reserve_transfer("a", 4096) is not None
     cfg = PDConfig()
     p = B200Transport("p0", P, torch.zeros(1, 8, device="cuda:0"), cfg)
-    d = B200Transport("d0", D, torch.zeros(1, 8, device="cuda:0"), cfg)
-    d.info["device"] = 9
+    d = B200Transport("d0", D, torch.zeros(1, 8, device="cuda:0"), cfg, lane=9)
     p.connect(d.info)
     d.connect(p.info)
     source = list(ho.kv_segments(p.info, P.plane_block_tables("a"), 0, 4096))

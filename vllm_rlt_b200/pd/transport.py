@@ -245,7 +245,7 @@ def _pid() -> int:
 
 
 class B200Transport:
-    def __init__(self, name, cache, hidden, config, *, backend=None):
+    def __init__(self, name, cache, hidden, config, *, backend=None, lane=None):
         self.config = config
         self.name = name
         self.cache = cache
@@ -262,7 +262,8 @@ class B200Transport:
         self.info = dict(
             **_kv_region(k, cache.value_cache),
             agent=name,
-            metadata=dict(tensors=[self.backend.export(t) for t in self.storage], mailbox=self.mailbox.name, pid=_pid()),
+            metadata=dict(tensors=[self.backend.export(t) for t in self.storage], mailbox=self.mailbox.name, pid=_pid(),
+                          lane=None),
             hidden_ptr=hidden.data_ptr(),
             hidden_bytes=hidden.stride(0) * hidden.element_size(),
             device=k.device.index if k.device.index is not None else 0,
@@ -274,6 +275,9 @@ class B200Transport:
             fp8_scale=cache.fp8_scale,
             scale_region=scale_region,
         )
+        # Mailbox lane this worker writes on at every receiver: its device index unless told otherwise
+        # (workers of one deployment never share a device, vllm_rlt/pd/config.py:31-33).
+        self.info["metadata"]["lane"] = Mailbox.lane_of(self.info["device"] if lane is None else lane)
         self.peers: dict[str, dict] = {}
         self._lane_agent: dict[int, str] = {}
         self._writer: dict[str, dict] = {}  # per peer: translate fn, mailbox, next stamp
@@ -297,9 +301,9 @@ class B200Transport:
         if (mine is None) != (theirs is None) or (mine is not None and any(mine[k] != theirs[k] for k in strides)):
             raise ValueError("PD KV scale geometry mismatch")
         name = peer["agent"]
-        lane = Mailbox.lane_of(peer["device"])
+        lane = peer["metadata"]["lane"]
         if self._lane_agent.get(lane, name) != name:
-            raise ValueError(f"peer {name!r} shares device {peer['device']} with another connected worker")
+            raise ValueError(f"peer {name!r} shares mailbox lane {lane} with another connected worker")
         self._lane_agent[lane] = name
         self.peers[name] = peer
 
@@ -310,7 +314,7 @@ class B200Transport:
             box, box_ptr = self.backend.mailbox_pointer(peer["metadata"]["mailbox"])
             state = self._writer[peer_name] = dict(
                 translate=self.backend.translator(peer), box=box, box_ptr=box_ptr,
-                lane=Mailbox.lane_of(self.info["device"]), stamp=0,
+                lane=self.info["metadata"]["lane"], stamp=0,
             )
         return state
 
