@@ -52,8 +52,27 @@ class FakeBackend:
         self.copies.append(list(triples))
         return ()
 
-    def handoff(self, *a, **k):
-        raise RuntimeError("the table-driven handoff needs a GPU")
+    def handoff(self, cache, peer_info, translate, requests, *, mode=0, layer_begin=0, layer_end=0,
+                exit_planes=None, status=None):
+        """Row-by-row statement of the table-driven launch over host tensors (all-planes mode only)."""
+        assert mode == 0 and exit_planes is None
+        page, layers = cache.block_size, cache.num_layers
+        layer_end = layer_end or layers
+        pairs = [(cache.key_cache, "key_ptr", peer_info), (cache.value_cache, "value_ptr", peer_info)]
+        if peer_info.get("scale_region") is not None:
+            pairs += [(cache.key_scale, "key_ptr", peer_info["scale_region"]), (cache.value_scale, "value_ptr", peer_info["scale_region"])]
+        for source, target, start, end in requests:
+            for src_table, dst_table in zip(source, target, strict=True):
+                for t in range(start, end):
+                    for tensor, key, region in pairs:
+                        row = tensor.stride(2) * tensor.element_size()
+                        for layer in range(layer_begin, layer_end):
+                            off = layer * region["layer_bytes"] + (t % page) * region["token_bytes"]
+                            src = tensor.data_ptr() + src_table[t // page] * region["block_bytes"] + off
+                            dst = translate(region[key] + dst_table[t // page] * region["block_bytes"] + off, row)
+                            ctypes.memmove(dst, src, row)
+        self.copies.append(("tables", list(requests)))
+        return ()
 
     def post(self, slot_ptr, body, stamp):
         box = list(self.boxes.values())[slot_ptr // self.STRIDE]
@@ -87,3 +106,75 @@ def cpu_cache(num_layers=3, heads=2, dim=8, blocks=24, page=4, planes=4, dtype=t
         ns.key_scale = torch.full(shape[:-1], fill)
         ns.value_scale = torch.full(shape[:-1], fill)
     return ns
+
+
+class FakeRequest:
+    def __init__(self, request_id, tokens, phase):
+        self.request_id = request_id
+        self.prompt_token_ids = list(tokens)
+        self.num_prefilled_tokens = 0
+        self.hidden_state = None
+        self.phase = phase
+        self.compute_released = False
+
+
+class FakeEngine:
+    """The handful of stage-engine hooks the connector calls, over a ``KVPool`` on the CPU.
+
+    Mirrors the contracts of ``StageEngine.reserve_transfer / accept_import / release_transfer_compute /
+    release_transfer / suspend_transfer`` (vllm_rlt/engine/stage_engine.py:679-775): identity checks on
+    the request object, a lease taken at reservation, KV freed only when the lease is dropped.
+    """
+
+    def __init__(self, role, pool, *, max_num_seqs=4, hidden_size=16):
+        self.cache_manager = pool
+        pool.layout = "last_exited"
+        pool.attention_info = {"backend": "torch"}
+        self.scheduler = SimpleNamespace(requests={}, config=SimpleNamespace(max_num_seqs=max_num_seqs, wavefront_chunked_prefill=False))
+        self.stage_config = SimpleNamespace(role=role, produces_tokens=role != "prefill", accepts_prompt=role != "decode", stage_id=f"{role}-0")
+        self.model = SimpleNamespace(config=SimpleNamespace(hidden_size=hidden_size))
+        self.imported = {}
+        self.suspended = []
+
+    def reserve_transfer(self, tid, tokens, params, *, receiving, trace_id=None):
+        if tid in self.scheduler.requests:
+            raise ValueError("duplicate request")
+        if self.cache_manager.reserve_transfer(tid, len(tokens)) is None:
+            return None
+        request = FakeRequest(tid, tokens, "RECEIVING" if receiving else "WAITING")
+        self.scheduler.requests[tid] = request
+        return request
+
+    def accept_import(self, request, hidden, *, cached_tokens=0):
+        if self.scheduler.requests.get(request.request_id) is not request:
+            return False
+        self.cache_manager.mark_imported_prefix(request.request_id, len(request.prompt_token_ids), start=cached_tokens)
+        self.imported[request.request_id] = hidden.clone()
+        return True
+
+    def admit(self, tid):
+        """What the scheduler does when it grants the imported request a compute slot."""
+        request = self.scheduler.requests[tid]
+        self.cache_manager.unpin_transfer(tid, tid)
+        request.phase = "CODA"
+
+    def release_transfer_compute(self, request, *, ready_event=None):
+        if self.scheduler.requests.get(request.request_id) is not request:
+            return False
+        if ready_event is not None and not ready_event.query():
+            return False
+        request.hidden_state = None
+        request.compute_released = True
+        return True
+
+    def release_transfer(self, request):
+        if self.scheduler.requests.get(request.request_id) is not request:
+            return False
+        del self.scheduler.requests[request.request_id]
+        self.cache_manager.unpin_transfer(request.request_id, request.request_id)
+        self.cache_manager.free(request.request_id)
+        return True
+
+    def suspend_transfer(self, request):
+        self.suspended.append(request.request_id)
+        request.phase = "TRANSFERRING"

@@ -1,0 +1,255 @@
+"""Connector + transport, prefill worker and decode worker in one process, on CPU tensors.
+
+The whole control sequence of a handoff (vllm_rlt/pd/engine.py:197-240 drives it in a deployment):
+reserve on D -> prefill on P -> chunks -> commit -> received -> ack -> released, with the messages
+relayed by hand the way the coordinator relays them. Destination bytes are compared with the oracle.
+"""
+
+from contextlib import nullcontext
+from types import SimpleNamespace
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import handoff_oracle as ho
+from tests.fakes import FakeBackend, FakeEngine, FakeEvent
+from vllm_rlt_b200.core.kv_pool import KVPool
+from vllm_rlt_b200.pd.config import PDConfig
+from vllm_rlt_b200.pd.connector import PDStageConnector, TableChunk
+from vllm_rlt_b200.pd.transport import B200Transport
+
+
+@pytest.fixture(autouse=True)
+def no_cuda(monkeypatch):
+    monkeypatch.setattr(torch.cuda, "current_stream", lambda device=None: SimpleNamespace(wait_event=lambda e: None))
+    monkeypatch.setattr(torch.cuda, "stream", lambda stream: nullcontext())
+
+    class ReadyEvent(FakeEvent):
+        def record(self, stream=None):
+            pass
+
+    monkeypatch.setattr(torch.cuda, "Event", ReadyEvent)
+
+
+class Worker:
+    def __init__(self, role, config, lane, *, blocks=64, fp8=False, seed=0):
+        self.pool = KVPool(3, 2, 8, blocks, 4, 2, device="cpu", kv_cache_dtype="fp8_e4m3" if fp8 else "auto")
+        gen = torch.Generator().manual_seed(seed)
+        for t in (self.pool.key_cache, self.pool.value_cache):
+            raw = t.view(torch.uint8)
+            raw.copy_(torch.randint(0, 256, raw.shape, dtype=torch.uint8, generator=gen) if role == "prefill" else torch.full_like(raw, 0xA5))
+        if fp8:
+            for t in (self.pool.key_scale, self.pool.value_scale):
+                t.copy_(torch.rand(t.shape, generator=gen) if role == "prefill" else torch.full_like(t, -1.0))
+        import random
+
+        random.Random(seed).shuffle(self.pool._free_blocks)
+        self.engine = FakeEngine(role, self.pool)
+        self.messages = []
+        hidden = torch.zeros(6, 16)
+        self.transport = B200Transport(f"{role}-0", self.pool, hidden, config, backend=FakeBackend(), lane=lane)
+        self.connector = PDStageConnector(self.engine, hidden, self.transport, config,
+                                          notify=lambda kind, **f: self.messages.append(dict(kind=kind, **f)))
+
+    def take(self, kind):
+        hits = [m for m in self.messages if m["kind"] == kind]
+        self.messages = [m for m in self.messages if m["kind"] != kind]
+        return hits
+
+
+def make_pair(config=None, **kw):
+    config = config or PDConfig()
+    p, d = Worker("prefill", config, 0, seed=1, **kw), Worker("decode", config, 1, seed=2, **kw)
+    assert p.connector.command(dict(kind="connect", peers=[d.transport.info]))
+    assert d.connector.command(dict(kind="connect", peers=[p.transport.info]))
+    assert p.take("connected") and d.take("connected")
+    return p, d
+
+
+def pool_rows(pool, tables, start, end):
+    out = []
+    tensors = [pool.key_cache, pool.value_cache] + ([pool.key_scale, pool.value_scale] if pool.key_scale is not None else [])
+    for table in tables:
+        for t in range(start, end):
+            for x in tensors:
+                out.append(x[table[t // 4], :, t % 4].contiguous().view(torch.uint8).reshape(-1))
+    return torch.cat(out)
+
+
+def run_handoff(p, d, tid, tokens, *, chunks=((0, None),), params=SimpleNamespace(max_tokens=4)):
+    """Relay the control messages by hand; returns the source request."""
+    from dataclasses import dataclass
+
+    @dataclass
+    class Params:
+        max_tokens: int = 4
+
+    prompt = list(range(1, tokens + 1))
+    d.connector.command(dict(kind="reserve", tid=tid, tokens=prompt, params=Params(), peer="prefill-0"))
+    (reserved,) = d.take("reserved")
+    p.connector.command(dict(kind="prefill", tid=tid, tokens=prompt, params=Params(), peer="decode-0",
+                             tables=reserved["tables"], slot=reserved["slot"], cached_tokens=reserved["cached_tokens"]))
+    assert p.take("prefill_started")
+    request = p.engine.scheduler.requests[tid]
+    assert p.connector.exports(request)
+    done = 0
+    for start, end in chunks:
+        end = tokens if end is None else end
+        request.num_prefilled_tokens = end
+        final = end == tokens
+        if final:
+            request.hidden_state = torch.full((16,), float(len(tid)))
+        progress = SimpleNamespace(chunk_complete=True, prompt_complete=final)
+        p.connector.prefill_submitted(request, phase="PREFILLING_RECURRENT", start=start, progress=progress, event=None, stream=None)
+        done = end
+        p.connector.progress()
+        d.connector.progress()
+    assert done == tokens
+    return request, reserved
+
+
+@pytest.mark.parametrize("fp8", [False, True])
+def test_full_handoff_sequence_moves_exactly_the_prompt_kv(fp8):
+    p, d = make_pair(fp8=fp8)
+    before = [t.clone() for t in (d.pool.key_cache, d.pool.value_cache)]
+    request, reserved = run_handoff(p, d, "req-1", 10, chunks=((0, 6), (6, None)))
+    (commit,) = p.take("commit")
+    assert commit["count"] == 2  # two prefill chunks, each under the byte limit: two submissions
+    (complete,) = p.take("prefill_complete")
+    assert complete["boundaries"] == ((0, 6), (6, 10), 2)
+    assert request.compute_released
+    # the coordinator relays the commit to D; D has already seen both notifications
+    d.connector.command(dict(kind="commit", tid="req-1", count=commit["count"]))
+    d.connector.progress()
+    assert d.take("received") == [dict(kind="received", tid="req-1")]
+    st, dt = p.pool.plane_block_tables("req-1"), reserved["tables"]
+    assert torch.equal(pool_rows(p.pool, st, 0, 10), pool_rows(d.pool, dt, 0, 10))
+    assert torch.equal(d.engine.imported["req-1"], torch.full((16,), 5.0))
+    # nothing outside the request's rows changed on D: rows of other blocks still hold the sentinel
+    used = {b for table in dt for b in table}
+    for t, old in zip((d.pool.key_cache, d.pool.value_cache), before):
+        for block in set(range(d.pool.num_blocks)) - used:
+            assert torch.equal(t[block].view(torch.uint8), old[block].view(torch.uint8))
+        tail_block = dt[0][2]  # tokens 8..9 live here; offsets 2..3 were never written
+        assert (t[tail_block, :, 2:].view(torch.uint8) == 0xA5).all()
+    # activation and retirement
+    d.engine.admit("req-1")
+    d.connector.progress()
+    assert d.take("activated")
+    p.connector.command(dict(kind="ack", tid="req-1"))
+    p.connector.progress()
+    assert p.take("released") == [dict(kind="released", tid="req-1", role="prefill")]
+    assert p.pool.num_used_blocks == 0 and not p.connector.transfers
+    del d.engine.scheduler.requests["req-1"]
+    d.connector.output_finished("req-1")
+    assert d.take("released")
+    assert not d.connector.has_pending
+    metrics = p.connector.close()
+    assert metrics["transfers"] == 2 and metrics["prefill_tokens"] == 10
+    assert metrics["bytes_sent"] == 10 * 2 * 2 * 3 * (2 * 8 * (1 if fp8 else 2) + (2 * 4 if fp8 else 0)) + 16 * 4
+    d.connector.close()
+
+
+def test_chunks_respect_the_byte_limit_and_sequence_numbers_are_dense():
+    per_token = 2 * 3 * 2 * 8 * 2 * 2  # K,V x layers x heads x dim x bf16 x planes = 384 B
+    config = PDConfig(transfer_chunk_bytes=3 * per_token + 10, max_inflight_bytes=1 << 20)
+    p, d = make_pair(config)
+    run_handoff(p, d, "r", 12)
+    (commit,) = p.take("commit")
+    assert commit["count"] == 5  # 12 tokens in pieces of 3 -> 4 full KV chunks, and the hidden row alone in a fifth
+    d.connector.command(dict(kind="commit", tid="r", count=5))
+    d.connector.progress()
+    assert d.take("received")
+    kinds = [c[0] if isinstance(c, tuple) else "segments" for c in p.transport.backend.copies]
+    assert kinds.count("tables") == 4
+    assert torch.equal(pool_rows(p.pool, p.pool.plane_block_tables("r"), 0, 12),
+                       pool_rows(d.pool, d.pool.plane_block_tables("r"), 0, 12))
+    run_handoff(p, d, "s", 11)  # last piece has room for the hidden row: it rides along
+    assert p.take("commit")[0]["count"] == 4
+
+
+def test_prefix_already_on_the_decode_side_is_skipped():
+    p, d = make_pair()
+    prompt = list(range(8))
+    from dataclasses import dataclass
+
+    @dataclass
+    class Params:
+        max_tokens: int = 4
+
+    d.connector.command(dict(kind="reserve", tid="r", tokens=prompt, params=Params(), peer="prefill-0"))
+    (reserved,) = d.take("reserved")
+    d.pool._allocations["r"].prefix = 4  # the decode side found the first block in its prefix cache
+    p.connector.command(dict(kind="prefill", tid="r", tokens=prompt, params=Params(), peer="decode-0",
+                             tables=reserved["tables"], slot=reserved["slot"], cached_tokens=4))
+    request = p.engine.scheduler.requests["r"]
+    request.num_prefilled_tokens, request.hidden_state = 8, torch.ones(16)
+    p.connector.prefill_submitted(request, phase="PREFILLING_RECURRENT", start=0,
+                                  progress=SimpleNamespace(chunk_complete=True, prompt_complete=True), event=None, stream=None)
+    chunk = p.connector.transfers["r"].chunks[0]
+    assert isinstance(chunk, TableChunk) and (chunk.start, chunk.end) == (4, 8)
+    p.connector.progress()
+    assert p.take("prefill_complete")[0]["boundaries"] == ((4, 8), (4, 8), 1)
+    d.connector.transfers["r"].cached_tokens = 4
+    d.connector.command(dict(kind="commit", tid="r", count=p.take("commit")[0]["count"]))
+    d.connector.progress()
+    assert d.take("received")
+    dt = reserved["tables"]
+    assert torch.equal(pool_rows(p.pool, p.pool.plane_block_tables("r"), 4, 8), pool_rows(d.pool, dt, 4, 8))
+    assert (d.pool.key_cache[dt[0][0]].view(torch.uint8) == 0xA5).all()  # the cached block was not rewritten
+
+
+def test_backpressure_and_cancellation_keep_resources_until_safe():
+    config = PDConfig(transfer_chunk_bytes=400, max_inflight_bytes=400)
+    p, d = make_pair(config)
+    p.transport.backend.complete_immediately = False
+    request, _ = run_handoff(p, d, "r", 6)
+    t = p.connector.transfers["r"]
+    assert p.transport.inflight_bytes > 0 and t.chunks  # one chunk on the wire, the rest waits for budget
+    assert not p.connector.can_schedule(request)
+    p.connector.command(dict(kind="cancel", tid="r"))
+    assert not t.chunks and p.engine.suspended == ["r"]
+    p.connector.progress()
+    assert "r" in p.connector.transfers  # still on the wire: the slot and the KV stay
+    for ev in p.transport.backend.events:
+        ev.done = True
+    p.connector.progress()
+    assert p.take("released") and p.pool.num_used_blocks == 0
+    # the decode side drops the import only after the coordinator confirms the writer stopped
+    d.connector.command(dict(kind="cancel", tid="r"))
+    d.connector.progress()
+    assert "r" in d.connector.transfers
+    p.connector.cancel_safe("missing")  # unknown generations are ignored
+    d.connector.transfers["r"].cancelled = False
+    with pytest.raises(RuntimeError, match="unexpected cancellation acknowledgement"):
+        d.connector.cancel_safe("r")
+    d.connector.transfers["r"].cancelled = True
+    d.connector.command(dict(kind="cancel_safe", tid="r"))
+    assert d.take("released") and d.pool.num_used_blocks == 0
+
+
+def test_rejection_when_the_decode_pool_is_full_and_protocol_errors():
+    p, d = make_pair(blocks=8)
+    from dataclasses import dataclass
+
+    @dataclass
+    class Params:
+        max_tokens: int = 4
+
+    d.connector.command(dict(kind="reserve", tid="ok", tokens=list(range(12)), params=Params(), peer="prefill-0"))
+    assert d.take("reserved")
+    d.connector.command(dict(kind="reserve", tid="big", tokens=list(range(8)), params=Params(), peer="prefill-0"))
+    assert d.take("rejected") == [dict(kind="rejected", tid="big", role="decode")]
+    assert "big" not in d.connector.transfers and len(d.connector.free_slots) == 5
+    with pytest.raises(RuntimeError, match="duplicate transfer generation"):
+        d.connector.reserve("ok", [1], Params(), receiving=True, peer="prefill-0")
+    with pytest.raises(RuntimeError, match="invalid transfer commit"):
+        d.connector.commit("ok", 0)
+    with pytest.raises(RuntimeError, match="acknowledgement requires an outgoing transfer"):
+        d.connector.acknowledge("ok")
+    with pytest.raises(ValueError, match="cancellation protocol"):
+        d.connector.command(dict(kind="abort", request_id="ok"))
+    assert d.connector.command(dict(kind="stats")) is False
+    with pytest.raises(RuntimeError, match="pending transfers"):
+        d.connector.close()

@@ -105,9 +105,7 @@ def test_descriptor_and_table_paths_write_the_same_bytes(fp8, two_gpus):
                     sent += size
                     seq += 1
             else:
-                with torch.cuda.device(dev_p):
-                    batch = kh.HandoffBatch([P.plane_block_tables(rid)], [D.plane_block_tables(rid)], [(start, end)],
-                                            block_size=16, device=dev_p)
+                batch = [(P.plane_block_tables(rid), D.plane_block_tables(rid), start, end)]
                 size = kh.PoolView.from_cache(P).payload_bytes(end - start, 2)
                 hb = p.info["hidden_bytes"]
                 extra = [(p.info["hidden_ptr"] + 1 * hb, d.info["hidden_ptr"] + 2 * hb, hb)]

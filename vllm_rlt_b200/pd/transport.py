@@ -202,11 +202,27 @@ class CudaBackend:
                 keep.append(dev)
         return (host, *keep)
 
-    def handoff(self, src_view, dst_view, batch, **kw):
+    def handoff(self, cache, peer_info, translate, requests, *, mode=0, layer_begin=0, layer_end=0,
+                exit_planes=None, status=None):
+        """One table-driven launch for ``requests`` = [(source tables, target tables, start, end), ...]."""
         from ..kernels import kv_handoff as kh
 
+        src = kh.PoolView.from_cache(cache)
+        codes = src.codes.rebased(translate(peer_info["key_ptr"], 1), translate(peer_info["value_ptr"], 1))
+        scales = None
+        if src.scales is not None:
+            sr = peer_info["scale_region"]
+            scales = src.scales.rebased(translate(sr["key_ptr"], 1), translate(sr["value_ptr"], 1))
+        planes = 1 if mode == kh.MODE_EXIT_ONLY else peer_info["depths"]
+        dst = kh.PoolView(codes, scales, peer_info["num_blocks"], peer_info["block_size"], peer_info["num_layers"],
+                          planes, peer_info["device"])
         with self.torch.cuda.device(self.device):
-            kh.kv_handoff(src_view, dst_view, batch, **kw)
+            batch = kh.HandoffBatch(
+                [r[0] for r in requests], [r[1] for r in requests], [(r[2], r[3]) for r in requests],
+                block_size=src.block_size, exit_planes=exit_planes, src_blocks=src.num_blocks,
+                dst_blocks=dst.num_blocks, device=self.device)
+            kh.kv_handoff(src, dst, batch, mode=mode, layer_begin=layer_begin, layer_end=layer_end, status=status)
+        return (batch,)
 
     def post(self, slot_ptr: int, body: bytes, stamp: int):
         import ctypes as C
@@ -353,26 +369,18 @@ class B200Transport:
         keep = self.backend.copy_segments(triples) if triples else ()
         return self._finish_submit(state, transfer_id, sequence, size, keep)
 
-    def submit_tables(self, transfer_id, sequence, peer, batch, size, *, mode=0, layer_begin=0, layer_end=0,
-                      extra=(), status=None):
-        """Table-driven form of ``submit``: the GPU walks the tables; ``extra`` holds plain ranges (the hidden row)."""
-        from ..kernels.kv_handoff import PoolView
-
+    def submit_tables(self, transfer_id, sequence, peer, requests, size, *, mode=0, layer_begin=0, layer_end=0,
+                      exit_planes=None, extra=(), status=None):
+        """Table-driven form of ``submit``: ``requests`` is a list of ``(source tables, target tables,
+        start, end)`` and the GPU walks the tables itself; ``extra`` holds plain ``(source address,
+        peer address, bytes)`` ranges that ride along (the final hidden-state row)."""
         state = self._writer_state(peer)
         if not self._admit(size, state):
             return False
-        info = self.peers[peer]
         translate = state["translate"]
-        src = PoolView.from_cache(self.cache)
-        codes = src.codes.rebased(translate(info["key_ptr"], 1), translate(info["value_ptr"], 1))
-        scales = None
-        if src.scales is not None:
-            sr = info["scale_region"]
-            scales = src.scales.rebased(translate(sr["key_ptr"], 1), translate(sr["value_ptr"], 1))
-        dst = PoolView(codes, scales, info["num_blocks"], info["block_size"], info["num_layers"],
-                       info["depths"] if mode != 2 else 1, info["device"])
-        self.backend.handoff(src, dst, batch, mode=mode, layer_begin=layer_begin, layer_end=layer_end, status=status)
-        keep = (batch,)
+        keep = tuple(self.backend.handoff(self.cache, self.peers[peer], translate, requests, mode=mode,
+                                          layer_begin=layer_begin, layer_end=layer_end, exit_planes=exit_planes,
+                                          status=status))
         if extra:
             keep += tuple(self.backend.copy_segments([(s, translate(d, n), n) for s, d, n in extra]))
         return self._finish_submit(state, transfer_id, sequence, size, keep)
