@@ -53,7 +53,8 @@ enum {
   RLT_STATUS_BAD_RANGE = 1,   /* token range negative or past the table: status[1] = request      */
   RLT_STATUS_BAD_BLOCK = 2,   /* block id outside pool: [1] request, [2] logical block, [3] id    */
   RLT_STATUS_BAD_PLANE = 3,   /* exit plane outside [0, planes): [1] request, [2] token, [3] value */
-  RLT_STATUS_TIMEOUT = 4      /* rlt_kv_wait gave up: [1] low 32 bits of the last value seen      */
+  RLT_STATUS_TIMEOUT = 4,     /* rlt_kv_wait gave up: [1] low 32 bits of the last value seen      */
+  RLT_STATUS_STALL = 5        /* a bulk copy never landed within the wait limit: [1] CTA, [2] warp */
 };
 #define RLT_STATUS_WORDS 4
 

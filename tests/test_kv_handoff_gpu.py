@@ -18,6 +18,9 @@ from tests.gpu_support import GpuPool, assert_pools_equal
 
 pytestmark = pytest.mark.gpu
 
+# kernel flavours: 0 = register path (16-byte loads/stores), 3 and 4 = cp.async.bulk rings of 8 x 4 KiB / 4 x 8 KiB
+VARIANTS = [0, 3, 4]
+
 
 def kh():
     from vllm_rlt_b200.kernels import kv_handoff
@@ -43,7 +46,8 @@ def sentinel_destination(kind, shape, planes=None):
 
 @pytest.mark.parametrize("case", golden_json("handoff.json"), ids=lambda c: c["name"])
 @pytest.mark.parametrize("batched", [True, False])
-def test_handoff_equals_reference_destination(case, batched):
+@pytest.mark.parametrize("variant", VARIANTS)
+def test_handoff_equals_reference_destination(case, batched, variant):
     k = kh()
     arrays = golden_npz(case["name"])
     P = oracle_pool(case["kind"], case["shape"])
@@ -60,14 +64,15 @@ def test_handoff_equals_reference_destination(case, batched):
             [(r["start"], r["end"]) for r in group], block_size=P.block_size,
             src_blocks=P.num_blocks, dst_blocks=D.num_blocks,
         )
-        k.kv_handoff(gp.view(), gd.view(), batch, status=status)
+        k.kv_handoff(gp.view(), gd.view(), batch, status=status, variant=variant)
     k.raise_for_status(status)
     load_pool(D, arrays, "dst_after_")
     assert_pools_equal(gd, D)
 
 
 @pytest.mark.parametrize("case", golden_json("handoff.json"), ids=lambda c: c["name"])
-def test_pack_equals_reference_wire_and_scatter_inverts_it(case):
+@pytest.mark.parametrize("variant", VARIANTS)
+def test_pack_equals_reference_wire_and_scatter_inverts_it(case, variant):
     k = kh()
     arrays = golden_npz(case["name"])
     P = oracle_pool(case["kind"], case["shape"])
@@ -84,12 +89,12 @@ def test_pack_equals_reference_wire_and_scatter_inverts_it(case):
     assert size == arrays["packed"].size
     packed = torch.full((size + 64,), 0x5A, dtype=torch.uint8, device="cuda")
     status = k.new_status()
-    k.kv_pack(gp.view(), batch, packed[:size], status=status)
+    k.kv_pack(gp.view(), batch, packed[:size], status=status, variant=variant)
     k.raise_for_status(status)
     got = packed.cpu().numpy()
     assert np.array_equal(got[:size], arrays["packed"])
     assert (got[size:] == 0x5A).all()
-    k.kv_scatter(packed[:size], gd.view(), batch, status=status)
+    k.kv_scatter(packed[:size], gd.view(), batch, status=status, variant=variant)
     k.raise_for_status(status)
     load_pool(D, arrays, "dst_after_")
     assert_pools_equal(gd, D)
@@ -172,7 +177,8 @@ def random_requests(rng, pool_src, pool_dst, count, max_tokens):
 
 @pytest.mark.parametrize("name", list(SHAPES))
 @pytest.mark.parametrize("mode_name", ["all", "dedup", "exit_only"])
-def test_seeded_handoff_matches_oracle(name, mode_name):
+@pytest.mark.parametrize("variant", VARIANTS)
+def test_seeded_handoff_matches_oracle(name, mode_name, variant):
     k = kh()
     kind, shape = SHAPES[name]
     planes = shape[5]
@@ -200,7 +206,7 @@ def test_seeded_handoff_matches_oracle(name, mode_name):
         src_blocks=P.num_blocks, dst_blocks=D.num_blocks,
     )
     status = k.new_status()
-    k.kv_handoff(gp.view(), gd.view(), batch, mode=mode, status=status)
+    k.kv_handoff(gp.view(), gd.view(), batch, mode=mode, status=status, variant=variant)
     k.raise_for_status(status)
     moved = 0
     for i, (rid, _, s, e) in enumerate(reqs):
@@ -218,7 +224,8 @@ def test_seeded_handoff_matches_oracle(name, mode_name):
 
 
 @pytest.mark.parametrize("name", ["ouro_bf16_small", "ouro_fp8_small", "huginn_fp8_rows", "odd_rows"])
-def test_layer_slices_compose_to_the_full_handoff(name):
+@pytest.mark.parametrize("variant", VARIANTS)
+def test_layer_slices_compose_to_the_full_handoff(name, variant):
     """Layer-by-layer streaming: slices [0,1), [1,3), [3,L) together equal one full handoff."""
     k = kh()
     kind, shape = SHAPES[name]
@@ -238,7 +245,7 @@ def test_layer_slices_compose_to_the_full_handoff(name):
     cuts = sorted({0, 1, min(3, layers), layers})
     status = k.new_status()
     for lo, hi in zip(cuts, cuts[1:]):
-        k.kv_handoff(gp.view(), gd.view(), batch, layer_begin=lo, layer_end=hi, status=status)
+        k.kv_handoff(gp.view(), gd.view(), batch, layer_begin=lo, layer_end=hi, status=status, variant=variant)
         for rid, _, s, e in reqs:
             ho.handoff_rows(P, D, P.plane_block_tables(rid), D.plane_block_tables(rid), s, e, layer_begin=lo, layer_end=hi)
         assert_pools_equal(gd, D)
@@ -248,13 +255,14 @@ def test_layer_slices_compose_to_the_full_handoff(name):
     if hi > lo:
         size = k.packed_bytes(gp.view(), batch.total_tokens, P.planes, hi - lo)
         packed = torch.zeros(size, dtype=torch.uint8, device="cuda")
-        k.kv_pack(gp.view(), batch, packed, layer_begin=lo, layer_end=hi, status=status)
+        k.kv_pack(gp.view(), batch, packed, layer_begin=lo, layer_end=hi, status=status, variant=variant)
         k.raise_for_status(status)
         want = np.concatenate([ho.pack_rows(P, P.plane_block_tables(r), s, e, layer_begin=lo, layer_end=hi) for r, _, s, e in reqs])
         assert np.array_equal(packed.cpu().numpy(), want)
 
 
-def test_many_requests_cross_the_scan_tile():
+@pytest.mark.parametrize("variant", VARIANTS)
+def test_many_requests_cross_the_scan_tile(variant):
     """More requests than threads in a CTA, so the request prefix sums span several scan tiles."""
     k = kh()
     kind, shape = "bf16", (2, 2, 8, 2400, 4, 2)
@@ -275,14 +283,14 @@ def test_many_requests_cross_the_scan_tile():
         [(s, e) for _, _, s, e in reqs], block_size=P.block_size,
     )
     status = k.new_status()
-    k.kv_handoff(gp.view(), gd.view(), batch, status=status)
+    k.kv_handoff(gp.view(), gd.view(), batch, status=status, variant=variant)
     k.raise_for_status(status)
     for rid, _, s, e in reqs:
         ho.handoff_rows(P, D, P.plane_block_tables(rid), D.plane_block_tables(rid), s, e)
     assert_pools_equal(gd, D)
     size = k.packed_bytes(gp.view(), batch.total_tokens, P.planes)
     packed = torch.zeros(size, dtype=torch.uint8, device="cuda")
-    k.kv_pack(gp.view(), batch, packed, status=status)
+    k.kv_pack(gp.view(), batch, packed, status=status, variant=variant)
     k.raise_for_status(status)
     want = np.concatenate([ho.pack_rows(P, P.plane_block_tables(r), s, e) for r, _, s, e in reqs])
     assert np.array_equal(packed.cpu().numpy(), want)

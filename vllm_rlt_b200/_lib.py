@@ -15,7 +15,7 @@ LIB_PATH = PACKAGE / "librlt_kv_handoff.so"
 
 RLT_OK = 0
 RLT_E_INVALID, RLT_E_GEOMETRY, RLT_E_LIMIT, RLT_E_CUDA, RLT_E_ALIGN = -1, -2, -3, -4, -5
-STATUS_OK, STATUS_BAD_RANGE, STATUS_BAD_BLOCK, STATUS_BAD_PLANE, STATUS_TIMEOUT = 0, 1, 2, 3, 4
+STATUS_OK, STATUS_BAD_RANGE, STATUS_BAD_BLOCK, STATUS_BAD_PLANE, STATUS_TIMEOUT, STATUS_STALL = 0, 1, 2, 3, 4, 5
 STATUS_WORDS = 4
 MODE_ALL_PLANES, MODE_DEDUP, MODE_EXIT_ONLY = 0, 1, 2
 MAX_REQUESTS = 4096

@@ -73,7 +73,7 @@ struct TableCopyParams {
   int* status;
 };
 
-template <typename T, int kUnroll>
+template <typename T, int kUnroll, bool kStreaming>
 __device__ __forceinline__ void stream_rows(const char* __restrict__ src, char* __restrict__ dst,
                                             const long long* __restrict__ src_off,
                                             const long long* __restrict__ dst_off, int total_vecs,
@@ -89,7 +89,10 @@ __device__ __forceinline__ void stream_rows(const char* __restrict__ src, char* 
       if (i < total_vecs) {
         const int row = row_magic ? static_cast<int>(__umulhi(static_cast<unsigned>(i), row_magic)) : i;
         const long long so = src_off[row];
-        if (so >= 0) regs[u] = ld_stream(reinterpret_cast<const T*>(src + so) + (i - row * row_vecs));
+        if (so >= 0) {
+          const T* from = reinterpret_cast<const T*>(src + so) + (i - row * row_vecs);
+          regs[u] = kStreaming ? ld_stream(from) : *from;
+        }
       }
     }
 #pragma unroll
@@ -98,14 +101,19 @@ __device__ __forceinline__ void stream_rows(const char* __restrict__ src, char* 
       if (i < total_vecs) {
         const int row = row_magic ? static_cast<int>(__umulhi(static_cast<unsigned>(i), row_magic)) : i;
         const long long to = dst_off[row];
-        if (to >= 0) st_stream(reinterpret_cast<T*>(dst + to) + (i - row * row_vecs), regs[u]);
+        if (to >= 0) {
+          T* at = reinterpret_cast<T*>(dst + to) + (i - row * row_vecs);
+          if (kStreaming) st_stream(at, regs[u]); else *at = regs[u];
+        }
       }
     }
   }
 }
 
 // Exclusive scans of per-request block counts and token counts, into shared memory.
+template <int kBlock>
 __device__ void scan_requests(const TableCopyParams& p, int* blk_off, int* tok_off) {
+  constexpr int kThreads = kBlock;  // shadows the file-wide constant: this routine serves CTAs of either size
   __shared__ int warp_sum[2][kThreads / 32];
   __shared__ int carry[2];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -158,7 +166,126 @@ __device__ void scan_requests(const TableCopyParams& p, int* blk_off, int* tok_o
   }
 }
 
-template <int kUnroll>
+// One work unit, decoded from its flat index.
+struct Unit {
+  int r, plane, g, kv, logical;
+  int begin, end;      // token range of the request
+  int tok_lo, n_tok;   // tokens of this block that lie in the range
+  int layer0, n_layers;
+  int rows;            // n_layers * n_tok
+};
+
+__device__ __forceinline__ int units_per_plane(const TableCopyParams& p) {
+  int n = 0;
+  for (int g = 0; g < p.num_regions; ++g) n += 2 * p.region[g].chunks;
+  return n;
+}
+
+__device__ __forceinline__ Unit decode_unit(const TableCopyParams& p, const int* blk_off, long long w,
+                                            int per_plane, int per_block) {
+  Unit u;
+  const int blk_idx = static_cast<int>(w / per_block);
+  int sub = static_cast<int>(w - static_cast<long long>(blk_idx) * per_block);
+  u.plane = sub / per_plane;
+  sub -= u.plane * per_plane;
+  u.g = 0;
+  if (sub >= 2 * p.region[0].chunks) {
+    u.g = 1;
+    sub -= 2 * p.region[0].chunks;
+  }
+  const RegionParams& rg = p.region[u.g];
+  u.kv = sub / rg.chunks;
+  const int chunk = sub - u.kv * rg.chunks;
+  // Request that owns block blk_idx: last r with blk_off[r] <= blk_idx.
+  int lo_r = 0, hi_r = p.num_requests;
+  while (hi_r - lo_r > 1) {
+    const int mid = (lo_r + hi_r) >> 1;
+    if (blk_off[mid] <= blk_idx) lo_r = mid; else hi_r = mid;
+  }
+  u.r = lo_r;
+  u.begin = p.tok_begin[u.r];
+  u.end = p.tok_end[u.r];
+  u.logical = u.begin / p.block_size + (blk_idx - blk_off[u.r]);
+  u.tok_lo = max(u.begin, u.logical * p.block_size);
+  u.n_tok = min(u.end, (u.logical + 1) * p.block_size) - u.tok_lo;
+  u.layer0 = p.layer_begin + chunk * rg.layers_per_unit;
+  u.n_layers = min(rg.layers_per_unit, p.layer_end - u.layer0);
+  u.rows = u.n_layers * u.n_tok;
+  return u;
+}
+
+// Byte offsets (from the unit's source and destination tensor bases) of row `row` of a unit.
+// This is where block tables and exit planes are read. A row that must be skipped gets -1 / -1.
+__device__ __forceinline__ void row_offsets(const TableCopyParams& p, const Unit& u, const int* tok_off, int row,
+                                            long long* src_off, long long* dst_off) {
+  const RegionParams& rg = p.region[u.g];
+  const int l_rel = row / u.n_tok;
+  const int tok = row - l_rel * u.n_tok;
+  const int t_abs = u.tok_lo + tok;
+  const int layer = u.layer0 + l_rel;
+  const int slice_layers = p.layer_end - p.layer_begin;
+  long long so = -1, dof = -1;
+  // Packed image: request, plane, block, region, tensor, layer, token (reference walk order).
+  long long packed = 0;
+  bool ok = true;
+  if (p.src_packed | p.dst_packed) {
+    const long long n_req = u.end - u.begin;
+    packed = (static_cast<long long>(tok_off[u.r]) * p.dst_planes + static_cast<long long>(u.plane) * n_req +
+              (u.tok_lo - u.begin)) * p.packed_token_bytes;
+    if (u.g == 1) packed += 2ll * slice_layers * u.n_tok * p.region[0].token_bytes;
+    packed += (static_cast<long long>(u.kv) * slice_layers * u.n_tok +
+               static_cast<long long>(layer - p.layer_begin) * u.n_tok + tok) * rg.token_bytes;
+    if (packed + rg.token_bytes > p.packed_bytes) {
+      report(p.status, RLT_STATUS_BAD_RANGE, u.r, u.begin, u.end);
+      ok = false;
+    }
+  }
+  const long long in_block = layer * rg.layer_bytes + (t_abs - u.logical * p.block_size) * rg.token_bytes;
+  if (p.src_packed) {
+    so = packed;
+  } else {
+    int exit_plane = p.src_planes - 1;
+    if (p.exit_planes != nullptr) {
+      exit_plane = p.exit_planes[p.exit_offsets[u.r] + t_abs];
+      if (exit_plane < 0 || exit_plane >= p.src_planes) {
+        report(p.status, RLT_STATUS_BAD_PLANE, u.r, t_abs, exit_plane);
+        ok = false;
+        exit_plane = 0;
+      }
+    }
+    const int sp = min(u.plane + p.plane_bias, exit_plane);
+    const int sb = p.src_tables[(static_cast<long long>(u.r) * p.src_planes + sp) * p.table_width + u.logical];
+    if (sb < 0 || sb >= p.src_blocks) {
+      report(p.status, RLT_STATUS_BAD_BLOCK, u.r, u.logical, sb);
+      ok = false;
+    }
+    so = sb * rg.block_bytes + in_block;
+  }
+  if (p.dst_packed) {
+    dof = packed;
+  } else {
+    const int db = p.dst_tables[(static_cast<long long>(u.r) * p.dst_planes + u.plane) * p.table_width + u.logical];
+    if (db < 0 || db >= p.dst_blocks) {
+      report(p.status, RLT_STATUS_BAD_BLOCK, u.r, u.logical, db);
+      ok = false;
+    }
+    dof = db * rg.block_bytes + in_block;
+  }
+  *src_off = ok ? so : -1;
+  *dst_off = ok ? dof : -1;
+}
+
+__device__ __forceinline__ const char* unit_src(const TableCopyParams& p, const Unit& u) {
+  const RegionParams& rg = p.region[u.g];
+  return p.src_packed ? rg.src_key : (u.kv ? rg.src_value : rg.src_key);
+}
+
+__device__ __forceinline__ char* unit_dst(const TableCopyParams& p, const Unit& u) {
+  const RegionParams& rg = p.region[u.g];
+  return p.dst_packed ? rg.dst_key : (u.kv ? rg.dst_value : rg.dst_key);
+}
+
+template <int kUnroll, bool kStreaming>
 __global__ void __launch_bounds__(kThreads, 4) table_copy_kernel(const TableCopyParams p) {
   extern __shared__ int dyn_smem[];
   int* blk_off = dyn_smem;                       // [num_requests + 1]
@@ -166,113 +293,236 @@ __global__ void __launch_bounds__(kThreads, 4) table_copy_kernel(const TableCopy
   __shared__ long long row_src[2][kMaxRows];
   __shared__ long long row_dst[2][kMaxRows];
 
-  scan_requests(p, blk_off, tok_off);
+  scan_requests<kThreads>(p, blk_off, tok_off);
 
-  int units_per_plane = 0;
-  for (int g = 0; g < p.num_regions; ++g) units_per_plane += 2 * p.region[g].chunks;
-  const int units_per_block = units_per_plane * p.dst_planes;
-  const long long total_units = static_cast<long long>(blk_off[p.num_requests]) * units_per_block;
-  const int slice_layers = p.layer_end - p.layer_begin;
+  const int per_plane = units_per_plane(p);
+  const int per_block = per_plane * p.dst_planes;
+  const long long total_units = static_cast<long long>(blk_off[p.num_requests]) * per_block;
 
   int parity = 0;
   for (long long w = blockIdx.x; w < total_units; w += gridDim.x, parity ^= 1) {
-    const int blk_idx = static_cast<int>(w / units_per_block);
-    int sub = static_cast<int>(w - static_cast<long long>(blk_idx) * units_per_block);
-    const int plane = sub / units_per_plane;
-    sub -= plane * units_per_plane;
-    int g = 0;
-    if (sub >= 2 * p.region[0].chunks) {
-      g = 1;
-      sub -= 2 * p.region[0].chunks;
-    }
-    const RegionParams& rg = p.region[g];
-    const int kv = sub / rg.chunks;
-    const int chunk = sub - kv * rg.chunks;
-
-    // Request that owns block blk_idx: last r with blk_off[r] <= blk_idx.
-    int lo_r = 0, hi_r = p.num_requests;
-    while (hi_r - lo_r > 1) {
-      const int mid = (lo_r + hi_r) >> 1;
-      if (blk_off[mid] <= blk_idx) lo_r = mid; else hi_r = mid;
-    }
-    const int r = lo_r;
-    const int begin = p.tok_begin[r], end = p.tok_end[r];
-    const int logical = begin / p.block_size + (blk_idx - blk_off[r]);
-    const int tok_lo = max(begin, logical * p.block_size);
-    const int tok_hi = min(end, (logical + 1) * p.block_size);
-    const int n_tok = tok_hi - tok_lo;
-    const int layer0 = p.layer_begin + chunk * rg.layers_per_unit;
-    const int n_layers = min(rg.layers_per_unit, p.layer_end - layer0);
-    const int rows = n_layers * n_tok;
-
+    const Unit u = decode_unit(p, blk_off, w, per_plane, per_block);
+    const RegionParams& rg = p.region[u.g];
     long long* rs = row_src[parity];
     long long* rd = row_dst[parity];
-    if (threadIdx.x < rows) {
-      const int l_rel = threadIdx.x / n_tok;
-      const int tok = threadIdx.x - l_rel * n_tok;
-      const int t_abs = tok_lo + tok;
-      const int layer = layer0 + l_rel;
-      long long so = -1, dof = -1;
-      // Packed image: request, plane, block, region, tensor, layer, token (reference walk order).
-      long long packed = 0;
-      if (p.src_packed | p.dst_packed) {
-        const long long n_req = end - begin;
-        packed = (static_cast<long long>(tok_off[r]) * p.dst_planes + static_cast<long long>(plane) * n_req +
-                  (tok_lo - begin)) * p.packed_token_bytes;
-        if (g == 1) packed += 2ll * slice_layers * n_tok * p.region[0].token_bytes;
-        packed += (static_cast<long long>(kv) * slice_layers * n_tok +
-                   static_cast<long long>(layer - p.layer_begin) * n_tok + tok) * rg.token_bytes;
-      }
-      bool ok = true;
-      if ((p.src_packed | p.dst_packed) && packed + rg.token_bytes > p.packed_bytes) {
-        report(p.status, RLT_STATUS_BAD_RANGE, r, begin, end);
-        ok = false;
-      }
-      if (p.src_packed) {
-        so = packed;
-      } else {
-        int exit_plane = p.src_planes - 1;
-        if (p.exit_planes != nullptr) {
-          exit_plane = p.exit_planes[p.exit_offsets[r] + t_abs];
-          if (exit_plane < 0 || exit_plane >= p.src_planes) {
-            report(p.status, RLT_STATUS_BAD_PLANE, r, t_abs, exit_plane);
-            ok = false;
-            exit_plane = 0;
-          }
-        }
-        const int sp = min(plane + p.plane_bias, exit_plane);
-        const int sb = p.src_tables[(static_cast<long long>(r) * p.src_planes + sp) * p.table_width + logical];
-        if (sb < 0 || sb >= p.src_blocks) {
-          report(p.status, RLT_STATUS_BAD_BLOCK, r, logical, sb);
-          ok = false;
-        }
-        so = sb * rg.block_bytes + layer * rg.layer_bytes + (t_abs - logical * p.block_size) * rg.token_bytes;
-      }
-      if (p.dst_packed) {
-        dof = packed;
-      } else {
-        const int db = p.dst_tables[(static_cast<long long>(r) * p.dst_planes + plane) * p.table_width + logical];
-        if (db < 0 || db >= p.dst_blocks) {
-          report(p.status, RLT_STATUS_BAD_BLOCK, r, logical, db);
-          ok = false;
-        }
-        dof = db * rg.block_bytes + layer * rg.layer_bytes + (t_abs - logical * p.block_size) * rg.token_bytes;
-      }
-      rs[threadIdx.x] = ok ? so : -1;
-      rd[threadIdx.x] = ok ? dof : -1;
-    }
+    if (threadIdx.x < u.rows) row_offsets(p, u, tok_off, threadIdx.x, &rs[threadIdx.x], &rd[threadIdx.x]);
     __syncthreads();  // one barrier per unit: the offset tables are double buffered
 
-    const char* src = p.src_packed ? rg.src_key : (kv ? rg.src_value : rg.src_key);
-    char* dst = p.dst_packed ? rg.dst_key : (kv ? rg.dst_value : rg.dst_key);
-    const int total_vecs = rows * rg.row_vecs;
+    const char* src = unit_src(p, u);
+    char* dst = unit_dst(p, u);
+    const int total_vecs = u.rows * rg.row_vecs;
     if (rg.vec_bytes == 16) {
-      stream_rows<uint4, kUnroll>(src, dst, rs, rd, total_vecs, rg.row_vecs, rg.row_magic);
+      stream_rows<uint4, kUnroll, kStreaming>(src, dst, rs, rd, total_vecs, rg.row_vecs, rg.row_magic);
     } else if (rg.vec_bytes == 4) {
-      stream_rows<uint32_t, kUnroll>(src, dst, rs, rd, total_vecs, rg.row_vecs, rg.row_magic);
+      stream_rows<uint32_t, kUnroll, kStreaming>(src, dst, rs, rd, total_vecs, rg.row_vecs, rg.row_magic);
     } else {
-      stream_rows<uint8_t, kUnroll>(src, dst, rs, rd, total_vecs, rg.row_vecs, rg.row_magic);
+      stream_rows<uint8_t, kUnroll, kStreaming>(src, dst, rs, rd, total_vecs, rg.row_vecs, rg.row_magic);
     }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Bulk-copy flavour: the same walk, but rows move global -> shared -> global with cp.async.bulk
+// (the TMA unit's untiled copy), tracked by mbarriers, instead of through registers.
+//
+// Every warp is an independent worker with a private ring of kBulkStages shared-memory stages.
+// All 32 lanes decode units and compute row offsets (32 rows at a time); lane 0 merges rows that
+// are adjacent on both sides into jobs of at most kBulkStageBytes and drives the ring:
+//     load(job k) ... wait full[k - kBulkLag] ; store(job k - kBulkLag)
+// so kBulkLag loads are in flight per warp while earlier stores drain. A stage is reused only
+// after cp.async.bulk.wait_group.read has confirmed that the store which last used it has read
+// it. Regions whose rows are too small or not 16-byte multiples (scale rows) are copied by the
+// warp with ordinary loads and stores. No multicast qualifier is used anywhere, and every wait
+// on an mbarrier is bounded: if a load never lands the warp records RLT_STATUS_STALL and stops.
+constexpr int kBulkWarps = 6;
+constexpr int kBulkThreads = kBulkWarps * 32;
+constexpr int kBulkMinRow = 512;
+constexpr int kBulkWarpBytes = 32768;  // shared memory of one warp's ring: stages x stage bytes
+constexpr size_t kBulkStageTotal = static_cast<size_t>(kBulkWarps) * kBulkWarpBytes;
+
+template <int kBulkStages>
+struct BulkRing {
+  unsigned long long full[kBulkStages];  // mbarriers: "the load into this stage has landed"
+  unsigned long long dst[kBulkStages];   // destination address of the job parked in the stage
+  int bytes[kBulkStages];
+  int pad[kBulkStages];
+};
+
+__device__ __forceinline__ unsigned smem_addr(const void* p) {
+  return static_cast<unsigned>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ void mbar_init(unsigned long long* bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(count) : "memory");
+}
+
+__device__ __forceinline__ void mbar_expect_tx(unsigned long long* bar, int bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
+}
+
+// Bounded wait for the phase with the given parity; false if it never completed.
+__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, int parity) {
+  const unsigned addr = smem_addr(bar);
+  for (int spin = 0; spin < (1 << 22); ++spin) {
+    unsigned done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(addr), "r"(parity)
+        : "memory");
+    if (done) return true;
+  }
+  return false;
+}
+
+__device__ __forceinline__ void bulk_load(void* smem_dst, const void* gmem_src, int bytes, unsigned long long* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   smem_addr(smem_dst)),
+               "l"(gmem_src), "r"(bytes), "r"(smem_addr(bar))
+               : "memory");
+}
+
+__device__ __forceinline__ void bulk_store(void* gmem_dst, const void* smem_src, int bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gmem_dst), "r"(smem_addr(smem_src)),
+               "r"(bytes)
+               : "memory");
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+
+template <int kBulkStages>
+struct BulkWorker {
+  static constexpr int kBulkStageBytes = kBulkWarpBytes / kBulkStages;
+  static constexpr int kBulkLag = kBulkStages - 2;
+  BulkRing<kBulkStages>* ring;
+  unsigned char* stages;  // kBulkStages * kBulkStageBytes of this warp
+  long long issued = 0;   // jobs whose load was issued
+  bool dead = false;
+
+  __device__ __forceinline__ unsigned char* stage(int s) const { return stages + static_cast<size_t>(s) * kBulkStageBytes; }
+
+  // Complete job k: its load has landed, send it on.
+  __device__ __forceinline__ void finish(long long k) {
+    const int s = static_cast<int>(k % kBulkStages);
+    if (!mbar_wait(&ring->full[s], static_cast<int>((k / kBulkStages) & 1))) {
+      dead = true;
+      return;
+    }
+    bulk_store(reinterpret_cast<void*>(ring->dst[s]), stage(s), ring->bytes[s]);
+  }
+
+  __device__ __forceinline__ void emit(const char* src, char* dst, int bytes) {
+    if (dead) return;
+    const int s = static_cast<int>(issued % kBulkStages);
+    if (issued >= kBulkStages) {
+      // The store of job issued - kBulkStages must have read the stage; one younger store may still be pending.
+      asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(kBulkStages - kBulkLag - 1) : "memory");
+    }
+    ring->dst[s] = reinterpret_cast<unsigned long long>(dst);
+    ring->bytes[s] = bytes;
+    mbar_expect_tx(&ring->full[s], bytes);
+    bulk_load(stage(s), src, bytes, &ring->full[s]);
+    ++issued;
+    if (issued > kBulkLag) finish(issued - 1 - kBulkLag);
+  }
+
+  __device__ __forceinline__ void drain() {
+    const long long first = issued > kBulkLag ? issued - kBulkLag : 0;
+    for (long long k = first; k < issued && !dead; ++k) finish(k);
+    asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+  }
+};
+
+template <typename T>
+__device__ __forceinline__ void warp_copy_rows(const char* src, char* dst, long long so, long long dof, int count,
+                                               int row_vecs, unsigned row_magic) {
+  // Lane j holds the offsets of row j; the warp streams the count rows as one flat vector array.
+  const int lane = threadIdx.x & 31;
+  const int total = count * row_vecs;
+  for (int i = lane; i < total + 31 - (total + 31) % 32; i += 32) {  // uniform trip count: shuffles need every lane
+    const bool in = i < total;
+    const int row = in ? (row_magic ? static_cast<int>(__umulhi(static_cast<unsigned>(i), row_magic)) : i) : 0;
+    const long long s = __shfl_sync(0xffffffffu, so, row);
+    const long long d = __shfl_sync(0xffffffffu, dof, row);
+    if (in && s >= 0) {
+      const int off = i - row * row_vecs;
+      reinterpret_cast<T*>(dst + d)[off] = reinterpret_cast<const T*>(src + s)[off];
+    }
+  }
+}
+
+template <int kBulkStages>
+__global__ void __launch_bounds__(kBulkThreads, 1) table_bulk_kernel(const TableCopyParams p) {
+  constexpr int kBulkStageBytes = kBulkWarpBytes / kBulkStages;
+  extern __shared__ __align__(128) unsigned char bulk_smem[];
+  BulkRing<kBulkStages>* rings = reinterpret_cast<BulkRing<kBulkStages>*>(bulk_smem + kBulkStageTotal);
+  int* blk_off = reinterpret_cast<int*>(rings + kBulkWarps);
+  int* tok_off = blk_off + p.num_requests + 1;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+
+  BulkWorker<kBulkStages> worker;
+  worker.ring = &rings[warp];
+  worker.stages = bulk_smem + static_cast<size_t>(warp) * kBulkWarpBytes;
+  if (lane == 0) {
+    for (int s = 0; s < kBulkStages; ++s) mbar_init(&worker.ring->full[s], 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  scan_requests<kBulkThreads>(p, blk_off, tok_off);  // ends with __syncthreads: barriers are initialised for everyone
+
+  const int per_plane = units_per_plane(p);
+  const int per_block = per_plane * p.dst_planes;
+  const long long total_units = static_cast<long long>(blk_off[p.num_requests]) * per_block;
+  const long long first = static_cast<long long>(blockIdx.x) * kBulkWarps + warp;
+  const long long stride = static_cast<long long>(gridDim.x) * kBulkWarps;
+
+  for (long long w = first; w < total_units; w += stride) {
+    const Unit u = decode_unit(p, blk_off, w, per_plane, per_block);
+    const RegionParams& rg = p.region[u.g];
+    const char* src = unit_src(p, u);
+    char* dst = unit_dst(p, u);
+    const bool bulk = rg.vec_bytes == 16 && rg.token_bytes >= kBulkMinRow;
+    const int row_bytes = static_cast<int>(rg.token_bytes);
+    long long run_s = 0, run_d = 0;
+    int run_n = 0;
+    for (int base = 0; base < u.rows; base += 32) {
+      long long so = -1, dof = -1;
+      if (base + lane < u.rows) row_offsets(p, u, tok_off, base + lane, &so, &dof);
+      const int count = min(32, u.rows - base);
+      if (!bulk) {
+        if (rg.vec_bytes == 16) {
+          warp_copy_rows<uint4>(src, dst, so, dof, count, rg.row_vecs, rg.row_magic);
+        } else if (rg.vec_bytes == 4) {
+          warp_copy_rows<uint32_t>(src, dst, so, dof, count, rg.row_vecs, rg.row_magic);
+        } else {
+          warp_copy_rows<uint8_t>(src, dst, so, dof, count, rg.row_vecs, rg.row_magic);
+        }
+        continue;
+      }
+      for (int j = 0; j < count; ++j) {
+        const long long s_j = __shfl_sync(0xffffffffu, so, j);
+        const long long d_j = __shfl_sync(0xffffffffu, dof, j);
+        if (s_j < 0 || lane != 0) continue;
+        for (int off = 0; off < row_bytes; off += kBulkStageBytes) {
+          const int n = min(kBulkStageBytes, row_bytes - off);
+          if (run_n > 0 && s_j + off == run_s + run_n && d_j + off == run_d + run_n && run_n + n <= kBulkStageBytes) {
+            run_n += n;
+          } else {
+            if (run_n > 0) worker.emit(src + run_s, dst + run_d, run_n);
+            run_s = s_j + off;
+            run_d = d_j + off;
+            run_n = n;
+          }
+        }
+      }
+    }
+    if (lane == 0 && run_n > 0) worker.emit(src + run_s, dst + run_d, run_n);
+    if (__shfl_sync(0xffffffffu, static_cast<int>(worker.dead), 0)) break;
+  }
+  if (lane == 0) {
+    worker.drain();
+    if (worker.dead) report(p.status, RLT_STATUS_STALL, static_cast<int>(blockIdx.x), warp, 0);
   }
 }
 
@@ -437,11 +687,31 @@ int launch_table_copy(Direction dir, const RltPool* src, const RltPool* dst, con
   const size_t smem = 2 * (static_cast<size_t>(batch->num_requests) + 1) * sizeof(int);
   switch (opt->variant & 0xf) {
     case 0:
-      table_copy_kernel<8><<<grid, kThreads, smem, stream>>>(p);
+      table_copy_kernel<8, true><<<grid, kThreads, smem, stream>>>(p);
       break;
     case 1:
-      table_copy_kernel<4><<<grid, kThreads, smem, stream>>>(p);
+      table_copy_kernel<4, true><<<grid, kThreads, smem, stream>>>(p);
       break;
+    case 2:
+      table_copy_kernel<8, false><<<grid, kThreads, smem, stream>>>(p);
+      break;
+    case 3:
+    case 4: {
+      // 3: eight 4 KiB stages per warp (six loads in flight); 4: four 8 KiB stages (two in flight).
+      const size_t bulk_smem_bytes = kBulkStageTotal + kBulkWarps * sizeof(BulkRing<8>) + smem;
+      // Opting in to large dynamic shared memory is per device; the call is cheap, so it is simply repeated.
+      const int want = static_cast<int>(bulk_smem_bytes);
+      RLT_CUDA_TRY(cudaFuncSetAttribute(table_bulk_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, want));
+      RLT_CUDA_TRY(cudaFuncSetAttribute(table_bulk_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, want));
+      int bulk_grid = sms;  // one CTA of kBulkWarps pipelines per SM
+      if (opt->grid_limit > 0 && bulk_grid > opt->grid_limit) bulk_grid = opt->grid_limit;
+      if ((opt->variant & 0xf) == 3) {
+        table_bulk_kernel<8><<<bulk_grid, kBulkThreads, bulk_smem_bytes, stream>>>(p);
+      } else {
+        table_bulk_kernel<4><<<bulk_grid, kBulkThreads, bulk_smem_bytes, stream>>>(p);
+      }
+      break;
+    }
     default:
       return RLT_E_INVALID;
   }

@@ -257,6 +257,7 @@ _STATUS_TEXT = {
     _lib.STATUS_BAD_BLOCK: "physical block outside registered pool",
     _lib.STATUS_BAD_PLANE: "exit plane outside the pool's planes",
     _lib.STATUS_TIMEOUT: "timed out waiting for the peer's completion flag",
+    _lib.STATUS_STALL: "a bulk copy did not complete within the wait limit",
 }
 
 
@@ -266,6 +267,8 @@ def raise_for_status(status: torch.Tensor) -> None:
     if words[0] == _lib.STATUS_OK:
         return
     text = _STATUS_TEXT.get(words[0], f"device status {words[0]}")
+    if words[0] == _lib.STATUS_STALL:
+        raise RuntimeError(f"{text} (CTA {words[1]}, warp {words[2]})")
     if words[0] == _lib.STATUS_TIMEOUT:
         raise TimeoutError(f"{text} (last value {words[1]})")
     raise ValueError(f"{text} (request {words[1]}, detail {words[2]}, {words[3]})")
