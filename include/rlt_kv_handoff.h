@@ -123,7 +123,10 @@ typedef struct RltOptions {
   int32_t wire_planes; /* pack/scatter: planes on the wire; 0 = source planes (1 for EXIT_ONLY) */
   int32_t* status;     /* NULL or device/mapped int32[RLT_STATUS_WORDS], zeroed by the caller   */
   int32_t grid_limit;  /* 0 = one full wave of resident CTAs; else cap on CTAs launched        */
-  int32_t variant;     /* kernel variant: 0 = default; see rlt_kv_variants()                    */
+  int32_t variant;     /* low 4 bits pick the kernel flavour: 0 register path (default), 3 and 4
+                          cp.async.bulk rings; the other bits are tuning knobs and may stay 0       */
+  void* workspace;     /* device scratch; needed only by pack/scatter in RLT_MODE_DEDUP          */
+  int64_t workspace_bytes; /* at least rlt_kv_dedup_workspace_bytes(...) for those calls          */
 } RltOptions;
 
 /* --- information ---------------------------------------------------------------------------- */
@@ -160,10 +163,23 @@ RLT_API int64_t rlt_kv_packed_bytes(const RltPool* pool, int64_t total_tokens, i
                                     int32_t layers);
 
 /*
+ * Scratch bytes that rlt_kv_pack / rlt_kv_scatter need in RLT_MODE_DEDUP for a
+ * batch of this shape (planes = source planes). The scratch holds the wire
+ * plan: where each (request, plane, block) starts when every token carries only
+ * the planes up to its exit plane. After the call (stream-ordered) its first 8
+ * bytes hold, as int64, the number of (token, plane) pairs on the wire; the
+ * wire image is that count times 2 * layers * (codes row + scales row) bytes.
+ */
+RLT_API int64_t rlt_kv_dedup_workspace_bytes(int32_t num_requests, int32_t table_width, int32_t planes);
+
+/*
  * Gather a batch into a contiguous buffer in the reference's segment order
  * (vllm_rlt/pd/transport.py:40-63: plane, logical block, codes then scales, K
  * then V, layer, token), requests back to back. batch->dst_tables is ignored.
- * packed must be 16-byte aligned. RLT_MODE_DEDUP is not a pack mode.
+ * packed must be 16-byte aligned. In RLT_MODE_DEDUP the image holds the same
+ * walk with the rows of planes deeper than a token's exit plane left out
+ * (they are copies, vllm_rlt/core/kv_cache_manager.py:1053-1076); this needs
+ * options->workspace.
  */
 RLT_API int rlt_kv_pack(const RltPool* src, const RltBatch* batch, const RltOptions* options,
                         void* packed, int64_t packed_bytes, rlt_stream_t stream);
@@ -171,7 +187,10 @@ RLT_API int rlt_kv_pack(const RltPool* src, const RltBatch* batch, const RltOpti
 /*
  * Inverse of rlt_kv_pack: write a packed image into the destination blocks
  * named by batch->dst_tables (batch->src_tables is ignored). Writes only the
- * rows of valid tokens.
+ * rows of valid tokens. In RLT_MODE_DEDUP (exit planes and workspace needed)
+ * the image is a dedup image and every destination plane deeper than a
+ * token's exit plane receives a copy of the exit plane's row, which is what
+ * finalize_token had left in the source.
  */
 RLT_API int rlt_kv_scatter(const void* packed, int64_t packed_bytes, const RltPool* dst,
                            const RltBatch* batch, const RltOptions* options, rlt_stream_t stream);

@@ -339,3 +339,77 @@ def test_host_validation_matches_reference_errors():
     batch = k.HandoffBatch(tables, tables, [(0, 12)], block_size=4)
     with pytest.raises(ValueError, match="geometry"):
         k.kv_handoff(GpuPool(P).view(), GpuPool(D).view(), batch)
+
+
+# ----------------------------------------------------------------------------- dedup wire image
+
+
+def dedup_case(kind, shape, seed, lengths):
+    rng, nrng = random.Random(seed), np.random.default_rng(seed)
+    planes = shape[5]
+    P, D = oracle_pool(kind, shape), sentinel_destination(kind, shape)
+    P.fill_random(nrng)
+    P.shuffle_free_list(rng)
+    D.shuffle_free_list(rng)
+    reqs, exits = [], []
+    for i, n in enumerate(lengths):
+        assert P.allocate(f"r{i}", n) and D.allocate(f"r{i}", n)
+        start = rng.choice([0, rng.randrange(n)])
+        end = rng.randint(start + 1, n)
+        e = [rng.randrange(planes) for _ in range(n)]
+        for pos in range(n):
+            P.finalize_token(f"r{i}", pos, e[pos])
+        reqs.append((f"r{i}", start, end))
+        exits.append(e)
+    return P, D, reqs, exits
+
+
+@pytest.mark.parametrize("name", ["ouro_bf16_small", "ouro_fp8_small", "huginn_fp8_rows", "odd_rows", "block32"])
+@pytest.mark.parametrize("variant", VARIANTS)
+def test_dedup_wire_carries_only_executed_planes_and_scatter_rebuilds_the_rest(name, variant):
+    k = kh()
+    kind, shape = SHAPES[name]
+    page, planes = shape[4], shape[5]
+    P, D, reqs, exits = dedup_case(kind, shape, 21, [3 * page + 5, page, 2 * page - 1])
+    gp, gd = GpuPool(P), GpuPool(D)
+    batch = k.HandoffBatch(
+        [P.plane_block_tables(r) for r, *_ in reqs], [D.plane_block_tables(r) for r, *_ in reqs],
+        [(s, e) for _, s, e in reqs], block_size=page, exit_planes=exits,
+    )
+    want = np.concatenate([
+        ho.pack_rows(P, P.plane_block_tables(r), s, e, mode=ho.MODE_DEDUP, exit_planes=exits[i])
+        for i, (r, s, e) in enumerate(reqs)
+    ])
+    pairs = sum(exits[i][t] + 1 for i, (_, s, e) in enumerate(reqs) for t in range(s, e))
+    full = k.packed_bytes(gp.view(), batch.total_tokens, planes)
+    assert want.size == k.packed_bytes(gp.view(), pairs, 1) < full
+    workspace = k.dedup_workspace(batch, planes)
+    packed = torch.full((full,), 0x5A, dtype=torch.uint8, device="cuda")
+    status = k.new_status()
+    k.kv_pack(gp.view(), batch, packed, mode=k.MODE_DEDUP, status=status, workspace=workspace, variant=variant)
+    k.raise_for_status(status)
+    assert k.dedup_wire_tokens(workspace) == pairs
+    got = packed.cpu().numpy()
+    assert np.array_equal(got[: want.size], want)
+    assert (got[want.size :] == 0x5A).all()
+    # the receiver plans from the same exit planes and rebuilds every plane
+    workspace2 = k.dedup_workspace(batch, planes)
+    k.kv_scatter(packed[: want.size], gd.view(), batch, mode=k.MODE_DEDUP, status=status, workspace=workspace2, variant=variant)
+    k.raise_for_status(status)
+    for i, (r, s, e) in enumerate(reqs):
+        ho.handoff_reference(P, D, P.plane_block_tables(r), D.plane_block_tables(r), s, e)
+    assert_pools_equal(gd, D)
+
+
+def test_dedup_pack_needs_a_workspace_of_the_stated_size():
+    k = kh()
+    kind, shape = SHAPES["ouro_bf16_small"]
+    P, D, reqs, exits = dedup_case(kind, shape, 3, [20])
+    gp = GpuPool(P)
+    batch = k.HandoffBatch([P.plane_block_tables("r0")], None, [(0, 20)], block_size=16, exit_planes=exits)
+    packed = torch.zeros(k.packed_bytes(gp.view(), 20, 4), dtype=torch.uint8, device="cuda")
+    with pytest.raises(ValueError, match="invalid argument"):
+        k.kv_pack(gp.view(), batch, packed, mode=k.MODE_DEDUP)
+    small = torch.zeros(32, dtype=torch.uint8, device="cuda")
+    with pytest.raises(ValueError, match="size limit"):
+        k.kv_pack(gp.view(), batch, packed, mode=k.MODE_DEDUP, workspace=small)

@@ -67,6 +67,8 @@ class RltOptions(C.Structure):
         ("status", C.c_void_p),
         ("grid_limit", C.c_int32),
         ("variant", C.c_int32),
+        ("workspace", C.c_void_p),
+        ("workspace_bytes", C.c_int64),
     ]
 
 
@@ -77,6 +79,7 @@ SIGNATURES = {
     "rlt_last_cuda_error": (C.c_int, []),
     "rlt_kernel_launches": (C.c_int64, []),
     "rlt_kv_handoff": (C.c_int, [C.POINTER(RltPool), C.POINTER(RltPool), C.POINTER(RltBatch), C.POINTER(RltOptions), C.c_void_p]),
+    "rlt_kv_dedup_workspace_bytes": (C.c_int64, [C.c_int32, C.c_int32, C.c_int32]),
     "rlt_kv_packed_bytes": (C.c_int64, [C.POINTER(RltPool), C.c_int64, C.c_int32, C.c_int32]),
     "rlt_kv_pack": (C.c_int, [C.POINTER(RltPool), C.POINTER(RltBatch), C.POINTER(RltOptions), C.c_void_p, C.c_int64, C.c_void_p]),
     "rlt_kv_scatter": (C.c_int, [C.c_void_p, C.c_int64, C.POINTER(RltPool), C.POINTER(RltBatch), C.POINTER(RltOptions), C.c_void_p]),

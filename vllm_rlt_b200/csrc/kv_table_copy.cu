@@ -70,6 +70,8 @@ struct TableCopyParams {
   int dst_packed;   // destination is the packed image (pack)
   long long packed_token_bytes;  // 2 * layers in slice * (codes row + scales row)
   long long packed_bytes;        // size of the packed image; rows past it are skipped
+  int dedup_wire;                // the packed image holds, per token, only planes up to its exit plane
+  const int* dedup_prefix;       // [planes * total blocks] wire tokens before each (request, plane, block)
   int* status;
 };
 
@@ -172,8 +174,26 @@ struct Unit {
   int begin, end;      // token range of the request
   int tok_lo, n_tok;   // tokens of this block that lie in the range
   int layer0, n_layers;
-  int rows;            // n_layers * n_tok
+  int rows;            // n_layers * tokens carried by this unit
+  int blk_first, n_blk;             // first flat block index and block count of the request
+  unsigned long long sel_mask;      // dedup pack: tokens of the block whose exit plane reaches this plane
+  int n_sel;
 };
+
+// Bit i set: token tok_lo + i of request r exits at or beyond `plane`, so `plane` holds a row of its own for it.
+__device__ __forceinline__ unsigned long long exit_mask(const TableCopyParams& p, int r, int tok_lo, int n_tok, int plane) {
+  unsigned long long mask = 0;
+  const int* e = p.exit_planes + p.exit_offsets[r] + tok_lo;
+  for (int i = 0; i < n_tok; ++i) mask |= static_cast<unsigned long long>(e[i] >= plane) << i;
+  return mask;
+}
+
+// Position of the k-th (0-based) set bit of mask.
+__device__ __forceinline__ int nth_set_bit(unsigned long long mask, int k) {
+  const unsigned lo = static_cast<unsigned>(mask), hi = static_cast<unsigned>(mask >> 32);
+  const int in_lo = __popc(lo);
+  return k < in_lo ? static_cast<int>(__fns(lo, 0, k + 1)) : 32 + static_cast<int>(__fns(hi, 0, k - in_lo + 1));
+}
 
 __device__ __forceinline__ int units_per_plane(const TableCopyParams& p) {
   int n = 0;
@@ -210,7 +230,15 @@ __device__ __forceinline__ Unit decode_unit(const TableCopyParams& p, const int*
   u.n_tok = min(u.end, (u.logical + 1) * p.block_size) - u.tok_lo;
   u.layer0 = p.layer_begin + chunk * rg.layers_per_unit;
   u.n_layers = min(rg.layers_per_unit, p.layer_end - u.layer0);
-  u.rows = u.n_layers * u.n_tok;
+  u.blk_first = blk_off[u.r];
+  u.n_blk = blk_off[u.r + 1] - u.blk_first;
+  u.sel_mask = 0;
+  u.n_sel = u.n_tok;
+  if (p.dedup_wire && p.dst_packed) {
+    u.sel_mask = exit_mask(p, u.r, u.tok_lo, u.n_tok, u.plane);
+    u.n_sel = __popcll(u.sel_mask);
+  }
+  u.rows = u.n_layers * u.n_sel;
   return u;
 }
 
@@ -219,22 +247,42 @@ __device__ __forceinline__ Unit decode_unit(const TableCopyParams& p, const int*
 __device__ __forceinline__ void row_offsets(const TableCopyParams& p, const Unit& u, const int* tok_off, int row,
                                             long long* src_off, long long* dst_off) {
   const RegionParams& rg = p.region[u.g];
-  const int l_rel = row / u.n_tok;
-  const int tok = row - l_rel * u.n_tok;
-  const int t_abs = u.tok_lo + tok;
+  const int l_rel = row / u.n_sel;
+  int tok = row - l_rel * u.n_sel;  // index among the unit's carried tokens
   const int layer = u.layer0 + l_rel;
   const int slice_layers = p.layer_end - p.layer_begin;
   long long so = -1, dof = -1;
   // Packed image: request, plane, block, region, tensor, layer, token (reference walk order).
   long long packed = 0;
   bool ok = true;
-  if (p.src_packed | p.dst_packed) {
+  if (p.dedup_wire) {
+    // Only rows whose plane is not deeper than the token's exit plane are on the wire. The wire
+    // plane of this row, the tokens of the block that plane carries, and this token's rank among them:
+    int wire_plane = u.plane, rank = tok, carried = u.n_sel;
+    if (p.dst_packed) {
+      tok = nth_set_bit(u.sel_mask, rank);
+    } else {
+      const int e = p.exit_planes[p.exit_offsets[u.r] + u.tok_lo + tok];
+      wire_plane = min(u.plane, e);
+      const unsigned long long mask = exit_mask(p, u.r, u.tok_lo, u.n_tok, wire_plane);
+      carried = __popcll(mask);
+      rank = __popcll(mask & ((1ull << tok) - 1ull));
+    }
+    const int entry = p.src_planes * u.blk_first + wire_plane * u.n_blk + (u.logical - u.begin / p.block_size);
+    packed = static_cast<long long>(p.dedup_prefix[entry]) * p.packed_token_bytes;
+    if (u.g == 1) packed += 2ll * slice_layers * carried * p.region[0].token_bytes;
+    packed += (static_cast<long long>(u.kv) * slice_layers * carried +
+               static_cast<long long>(layer - p.layer_begin) * carried + rank) * rg.token_bytes;
+  } else if (p.src_packed | p.dst_packed) {
     const long long n_req = u.end - u.begin;
     packed = (static_cast<long long>(tok_off[u.r]) * p.dst_planes + static_cast<long long>(u.plane) * n_req +
               (u.tok_lo - u.begin)) * p.packed_token_bytes;
     if (u.g == 1) packed += 2ll * slice_layers * u.n_tok * p.region[0].token_bytes;
     packed += (static_cast<long long>(u.kv) * slice_layers * u.n_tok +
                static_cast<long long>(layer - p.layer_begin) * u.n_tok + tok) * rg.token_bytes;
+  }
+  const int t_abs = u.tok_lo + tok;
+  if (p.src_packed | p.dst_packed) {
     if (packed + rg.token_bytes > p.packed_bytes) {
       report(p.status, RLT_STATUS_BAD_RANGE, u.r, u.begin, u.end);
       ok = false;
@@ -526,6 +574,141 @@ __global__ void __launch_bounds__(kBulkThreads, 1) table_bulk_kernel(const Table
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Dedup wire plan: where each (request, plane, block) starts in a wire image that carries, for
+// every token, only the planes up to its exit plane. Three small launches:
+//   count : tokens carried per (request, plane, block) entry, and the sum of every 1024-entry tile
+//   tiles : exclusive scan of the tile sums (one CTA); total wire tokens -> header
+//   finish: exclusive scan inside every tile, offset by its tile start (in place over the counts)
+// Entries are ordered request, plane, block - the wire order. All scans use warp shuffles.
+// Workspace layout: int64 header[2] = {wire tokens, entries}; int32 prefix[entries]; int32 tile[tiles + 1].
+constexpr int kPlanTile = 1024;
+constexpr int kPlanHeaderBytes = 16;
+
+__device__ __forceinline__ int block_exclusive_scan(int v, int* total) {
+  // Exclusive scan of one value per thread across a kThreads-wide CTA.
+  __shared__ int warp_part[kThreads / 32];
+  __shared__ int all;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int inc = warp_inclusive_scan(v);
+  if (lane == 31) warp_part[warp] = inc;
+  __syncthreads();
+  if (warp == 0) {
+    const int w = lane < kThreads / 32 ? warp_part[lane] : 0;
+    const int iw = warp_inclusive_scan(w);
+    if (lane < kThreads / 32) warp_part[lane] = iw - w;
+    if (lane == kThreads / 32 - 1) all = iw;
+  }
+  __syncthreads();
+  const int out = warp_part[warp] + inc - v;
+  *total = all;
+  __syncthreads();
+  return out;
+}
+
+__global__ void __launch_bounds__(kThreads) dedup_count_kernel(const TableCopyParams p, long long* header, int* prefix,
+                                                               int* tile_sum) {
+  extern __shared__ int dyn_smem[];
+  int* blk_off = dyn_smem;
+  int* tok_off = dyn_smem + p.num_requests + 1;
+  scan_requests<kThreads>(p, blk_off, tok_off);
+  const long long entries = static_cast<long long>(p.src_planes) * blk_off[p.num_requests];
+  if (blockIdx.x == 0 && threadIdx.x == 0) header[1] = entries;
+  const long long tiles = (entries + kPlanTile - 1) / kPlanTile;
+  for (long long tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
+    int mine = 0;
+    for (int k = 0; k < kPlanTile / kThreads; ++k) {
+      const long long idx = tile * kPlanTile + k * kThreads + threadIdx.x;
+      if (idx >= entries) continue;
+      int lo_r = 0, hi_r = p.num_requests;
+      while (hi_r - lo_r > 1) {
+        const int mid = (lo_r + hi_r) >> 1;
+        if (static_cast<long long>(p.src_planes) * blk_off[mid] <= idx) lo_r = mid; else hi_r = mid;
+      }
+      const int r = lo_r;
+      const int n_blk = blk_off[r + 1] - blk_off[r];
+      const int local = static_cast<int>(idx - static_cast<long long>(p.src_planes) * blk_off[r]);
+      const int plane = local / n_blk;
+      const int begin = p.tok_begin[r], end = p.tok_end[r];
+      const int logical = begin / p.block_size + (local - plane * n_blk);
+      const int lo = max(begin, logical * p.block_size);
+      const int hi = min(end, (logical + 1) * p.block_size);
+      const int count = __popcll(exit_mask(p, r, lo, hi - lo, plane));
+      prefix[idx] = count;
+      mine += count;
+    }
+    int total;
+    block_exclusive_scan(mine, &total);
+    if (threadIdx.x == 0) tile_sum[tile] = total;
+  }
+}
+
+__global__ void __launch_bounds__(kThreads) dedup_tiles_kernel(long long* header, int* tile_sum) {
+  const long long tiles = (header[1] + kPlanTile - 1) / kPlanTile;
+  int carry = 0;
+  for (long long base = 0; base < tiles; base += kThreads) {
+    const long long i = base + threadIdx.x;
+    const int v = i < tiles ? tile_sum[i] : 0;
+    int total;
+    const int ex = block_exclusive_scan(v, &total);
+    if (i < tiles) tile_sum[i] = carry + ex;
+    carry += total;
+  }
+  if (threadIdx.x == 0) {
+    tile_sum[tiles] = carry;
+    header[0] = carry;
+  }
+}
+
+__global__ void __launch_bounds__(kThreads) dedup_finish_kernel(const long long* header, int* prefix, const int* tile_sum) {
+  const long long entries = header[1];
+  const long long tiles = (entries + kPlanTile - 1) / kPlanTile;
+  constexpr int kPer = kPlanTile / kThreads;
+  for (long long tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
+    const long long first = tile * kPlanTile + static_cast<long long>(threadIdx.x) * kPer;
+    int v[kPer], sum = 0;
+#pragma unroll
+    for (int k = 0; k < kPer; ++k) {
+      v[k] = first + k < entries ? prefix[first + k] : 0;
+      sum += v[k];
+    }
+    int total;
+    int run = tile_sum[tile] + block_exclusive_scan(sum, &total);
+#pragma unroll
+    for (int k = 0; k < kPer; ++k) {
+      if (first + k < entries) prefix[first + k] = run;
+      run += v[k];
+    }
+  }
+}
+
+long long dedup_workspace_bytes(long long requests, long long width, long long planes) {
+  const long long entries = requests * width * planes;
+  const long long tiles = (entries + kPlanTile - 1) / kPlanTile;
+  return kPlanHeaderBytes + 4 * entries + 4 * (tiles + 1);
+}
+
+// Launch the three plan kernels into `workspace`; fills p.dedup_prefix.
+int plan_dedup(TableCopyParams& p, void* workspace, long long workspace_bytes, int sms, size_t scan_smem,
+               cudaStream_t stream) {
+  if (workspace == nullptr) return RLT_E_INVALID;
+  if (reinterpret_cast<uintptr_t>(workspace) & 15u) return RLT_E_ALIGN;
+  const long long entries_max = static_cast<long long>(p.num_requests) * p.table_width * p.src_planes;
+  if (workspace_bytes < dedup_workspace_bytes(p.num_requests, p.table_width, p.src_planes)) return RLT_E_LIMIT;
+  long long* header = static_cast<long long*>(workspace);
+  int* prefix = reinterpret_cast<int*>(static_cast<char*>(workspace) + kPlanHeaderBytes);
+  int* tile_sum = prefix + entries_max;
+  const long long tiles_max = (entries_max + kPlanTile - 1) / kPlanTile;
+  const int grid = static_cast<int>(tiles_max < sms * 4ll ? tiles_max : sms * 4ll);
+  dedup_count_kernel<<<grid, kThreads, scan_smem, stream>>>(p, header, prefix, tile_sum);
+  dedup_tiles_kernel<<<1, kThreads, 0, stream>>>(header, tile_sum);
+  dedup_finish_kernel<<<grid, kThreads, 0, stream>>>(header, prefix, tile_sum);
+  RLT_CUDA_TRY(cudaGetLastError());
+  g_launches.fetch_add(3, std::memory_order_relaxed);
+  p.dedup_prefix = prefix;
+  return RLT_OK;
+}
+
 bool dense(const RltRegion& r, const RltPool& pool) {
   return r.token_bytes > 0 && r.layer_bytes == r.token_bytes * pool.block_size &&
          r.block_bytes == r.layer_bytes * pool.num_layers;
@@ -543,8 +726,13 @@ int vector_width(const void* a, const void* b, const void* c, const void* d, lon
 enum Direction { kDirect, kPack, kScatter };
 
 int launch_table_copy(Direction dir, const RltPool* src, const RltPool* dst, const RltBatch* batch,
-                      const RltOptions* opt, void* packed, long long packed_bytes, cudaStream_t stream) {
+                      const RltOptions* opt, void* packed, long long packed_bytes, cudaStream_t stream,
+                      void* workspace = nullptr, long long workspace_bytes = 0) {
   if (batch == nullptr || opt == nullptr) return RLT_E_INVALID;
+  if (workspace == nullptr) {
+    workspace = opt->workspace;
+    workspace_bytes = opt->workspace_bytes;
+  }
   const RltPool* any = dir == kScatter ? dst : src;
   if (any == nullptr || (dir == kDirect && dst == nullptr)) return RLT_E_INVALID;
   if (batch->num_requests < 1 || batch->table_width < 1 || batch->tok_begin == nullptr ||
@@ -559,7 +747,8 @@ int launch_table_copy(Direction dir, const RltPool* src, const RltPool* dst, con
   if (opt->mode != RLT_MODE_ALL_PLANES && dir != kScatter &&
       (batch->exit_planes == nullptr || batch->exit_offsets == nullptr))
     return RLT_E_INVALID;
-  if (dir == kPack && opt->mode == RLT_MODE_DEDUP) return RLT_E_INVALID;
+  const bool dedup_wire = dir != kDirect && opt->mode == RLT_MODE_DEDUP;
+  if (dedup_wire && (batch->exit_planes == nullptr || batch->exit_offsets == nullptr)) return RLT_E_INVALID;
 
   const int layer_begin = opt->layer_begin;
   const int layer_end = opt->layer_end == 0 ? any->num_layers : opt->layer_end;
@@ -622,7 +811,7 @@ int launch_table_copy(Direction dir, const RltPool* src, const RltPool* dst, con
     p.src_planes = wire_planes;
     p.dst_planes = dst->num_planes;
     p.dst_blocks = dst->num_blocks;
-    p.exit_planes = nullptr;
+    p.exit_planes = dedup_wire ? batch->exit_planes : nullptr;
   }
   p.plane_bias = opt->mode == RLT_MODE_EXIT_ONLY ? p.src_planes : 0;
 
@@ -685,6 +874,11 @@ int launch_table_copy(Direction dir, const RltPool* src, const RltPool* dst, con
   int grid = sms * per_sm;
   if (opt->grid_limit > 0 && grid > opt->grid_limit) grid = opt->grid_limit;
   const size_t smem = 2 * (static_cast<size_t>(batch->num_requests) + 1) * sizeof(int);
+  if (dedup_wire) {
+    p.dedup_wire = 1;
+    const int planned = plan_dedup(p, workspace, workspace_bytes, sms, smem, stream);
+    if (planned != RLT_OK) return planned;
+  }
   switch (opt->variant & 0xf) {
     case 0:
       table_copy_kernel<8, true><<<grid, kThreads, smem, stream>>>(p);
@@ -729,6 +923,11 @@ int rlt_kv_handoff(const RltPool* src, const RltPool* dst, const RltBatch* batch
                    const RltOptions* options, rlt_stream_t stream) {
   return rlt::launch_table_copy(rlt::kDirect, src, dst, batch, options, nullptr, 0,
                                 reinterpret_cast<cudaStream_t>(stream));
+}
+
+int64_t rlt_kv_dedup_workspace_bytes(int32_t num_requests, int32_t table_width, int32_t planes) {
+  if (num_requests < 1 || table_width < 1 || planes < 1) return RLT_E_INVALID;
+  return rlt::dedup_workspace_bytes(num_requests, table_width, planes);
 }
 
 int64_t rlt_kv_packed_bytes(const RltPool* pool, int64_t total_tokens, int32_t wire_planes, int32_t layers) {

@@ -274,11 +274,27 @@ def raise_for_status(status: torch.Tensor) -> None:
     raise ValueError(f"{text} (request {words[1]}, detail {words[2]}, {words[3]})")
 
 
-def _options(mode, layer_begin, layer_end, wire_planes, status, grid_limit, variant) -> _lib.RltOptions:
+def _options(mode, layer_begin, layer_end, wire_planes, status, grid_limit, variant, workspace=None) -> _lib.RltOptions:
+    if workspace is not None and (workspace.dtype != torch.uint8 or not workspace.is_contiguous() or not workspace.is_cuda):
+        raise ValueError("workspace must be a contiguous CUDA uint8 tensor")
     return _lib.RltOptions(
         int(mode), int(layer_begin), int(layer_end), int(wire_planes),
         status.data_ptr() if status is not None else None, int(grid_limit), int(variant),
+        workspace.data_ptr() if workspace is not None else None, workspace.numel() if workspace is not None else 0,
     )
+
+
+def dedup_workspace(batch: "HandoffBatch", planes: int, device=None) -> torch.Tensor:
+    """Scratch tensor for pack/scatter in ``MODE_DEDUP`` (holds the wire plan of the batch)."""
+    n = _lib.load().rlt_kv_dedup_workspace_bytes(batch.num_requests, batch.table_width, planes)
+    if n < 0:
+        _lib.check(int(n), "rlt_kv_dedup_workspace_bytes")
+    return torch.empty(int(n), dtype=torch.uint8, device=device or "cuda")
+
+
+def dedup_wire_tokens(workspace: torch.Tensor) -> int:
+    """(token, plane) pairs on the wire of the last dedup pack/scatter that used ``workspace`` (synchronises)."""
+    return int(workspace[:8].view(torch.int64).item())
 
 
 # --------------------------------------------------------------------------- ops
@@ -303,24 +319,25 @@ def packed_bytes(pool: PoolView, total_tokens: int, wire_planes: int, layers: in
 
 
 def kv_pack(src: PoolView, batch: HandoffBatch, out: torch.Tensor, *, mode=MODE_ALL_PLANES, layer_begin=0,
-            layer_end=0, wire_planes=0, status=None, stream=None, grid_limit=0, variant=0) -> None:
+            layer_end=0, wire_planes=0, status=None, stream=None, grid_limit=0, variant=0, workspace=None) -> None:
     """Gather a batch into ``out`` (uint8, contiguous) in the reference's segment order."""
     if out.dtype != torch.uint8 or not out.is_contiguous() or not out.is_cuda:
         raise ValueError("packed buffer must be a contiguous CUDA uint8 tensor")
     lib = _lib.load()
     s, b = src.as_struct(), batch.as_struct()
-    o = _options(mode, layer_begin, layer_end, wire_planes, status, grid_limit, variant)
+    o = _options(mode, layer_begin, layer_end, wire_planes, status, grid_limit, variant, workspace)
     _lib.check(lib.rlt_kv_pack(C.byref(s), C.byref(b), C.byref(o), out.data_ptr(), out.numel(), _stream_ptr(stream)), "rlt_kv_pack")
 
 
-def kv_scatter(packed: torch.Tensor, dst: PoolView, batch: HandoffBatch, *, layer_begin=0, layer_end=0,
-               wire_planes=0, status=None, stream=None, grid_limit=0, variant=0) -> None:
+def kv_scatter(packed: torch.Tensor, dst: PoolView, batch: HandoffBatch, *, mode=MODE_ALL_PLANES, layer_begin=0,
+               layer_end=0, wire_planes=0, status=None, stream=None, grid_limit=0, variant=0, workspace=None) -> None:
     """Write a packed image into the destination blocks of a batch."""
     if packed.dtype != torch.uint8 or not packed.is_contiguous() or not packed.is_cuda:
         raise ValueError("packed buffer must be a contiguous CUDA uint8 tensor")
     lib = _lib.load()
     d, b = dst.as_struct(), batch.as_struct()
-    o = _options(MODE_ALL_PLANES, layer_begin, layer_end, wire_planes, status, grid_limit, variant)
+    o = _options(mode if mode == MODE_DEDUP else MODE_ALL_PLANES, layer_begin, layer_end, wire_planes, status,
+                 grid_limit, variant, workspace)
     _lib.check(lib.rlt_kv_scatter(packed.data_ptr(), packed.numel(), C.byref(d), C.byref(b), C.byref(o), _stream_ptr(stream)), "rlt_kv_scatter")
 
 
