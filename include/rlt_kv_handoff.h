@@ -185,6 +185,35 @@ RLT_API int rlt_kv_pack(const RltPool* src, const RltBatch* batch, const RltOpti
                         void* packed, int64_t packed_bytes, rlt_stream_t stream);
 
 /*
+ * rlt_kv_pack in RLT_MODE_DEDUP for callers that must not allocate. It has no
+ * counterpart in the reference.
+ *
+ * Who needs it: a stage worker that hands every free byte of HBM to its KV pool
+ * at start-up and then serves with allocation switched off. For such a worker a
+ * later cudaMalloc of the wire-plan scratch can fail outright, or stall the whole
+ * device in the middle of serving, so it cannot provide options->workspace.
+ *
+ * This entry point takes no workspace (options->workspace is ignored): the plan
+ * lives in an array inside the library image, about 4.2 MB that every GPU
+ * which loads the library holds until the process exits. It calls no
+ * cudaMalloc, cudaFree or any other allocating routine. Limit: num_requests *
+ * table_width * source planes <= rlt_kv_static_plan_entries() (2^20); larger
+ * batches get RLT_E_LIMIT and nothing is launched. Inputs and the packed
+ * output are still the caller's. options->mode must be RLT_MODE_DEDUP.
+ *
+ * The first call on each device looks up the array's device address (one
+ * runtime query, with that device current); make that first call before
+ * starting any stream capture. All calls on a device share the one array and
+ * it keeps the previous call's contents; every word a call reads is written
+ * by that call first, so nothing has to be cleared, but two calls that overlap
+ * on the GPU (different streams, no ordering between them) race on it: order
+ * them, or use rlt_kv_pack with separate workspaces.
+ */
+RLT_API int rlt_kv_pack_dedup_static(const RltPool* src, const RltBatch* batch, const RltOptions* options,
+                                     void* packed, int64_t packed_bytes, rlt_stream_t stream);
+RLT_API int64_t rlt_kv_static_plan_entries(void);
+
+/*
  * Inverse of rlt_kv_pack: write a packed image into the destination blocks
  * named by batch->dst_tables (batch->src_tables is ignored). Writes only the
  * rows of valid tokens. In RLT_MODE_DEDUP (exit planes and workspace needed)

@@ -917,7 +917,53 @@ int launch_table_copy(Direction dir, const RltPool* src, const RltPool* dst, con
 }  // namespace
 }  // namespace rlt
 
+namespace rlt {
+namespace {
+
+// Scratch of rlt_kv_pack_dedup_static: lives in the library image, one copy per GPU that loads it.
+constexpr long long kStaticPlanEntries = 1ll << 20;
+constexpr long long kStaticPlanBytes =
+    kPlanHeaderBytes + 4 * kStaticPlanEntries + 4 * (kStaticPlanEntries / kPlanTile + 1);
+static __device__ __align__(256) unsigned char g_static_plan[kStaticPlanBytes];
+
+// Device address of g_static_plan on the current device, looked up once per device. In host code
+// the array's name is only a handle for the runtime; the address has to be asked for.
+int static_plan_address(void** out) {
+  constexpr int kMaxDevices = 64;
+  static std::atomic<void*> cached[kMaxDevices];
+  int device = 0;
+  RLT_CUDA_TRY(cudaGetDevice(&device));
+  if (device < 0 || device >= kMaxDevices) return RLT_E_LIMIT;
+  void* ptr = cached[device].load(std::memory_order_acquire);
+  if (ptr == nullptr) {
+    RLT_CUDA_TRY(cudaGetSymbolAddress(&ptr, g_static_plan));
+    if (ptr == nullptr) return RLT_E_CUDA;
+    cached[device].store(ptr, std::memory_order_release);
+  }
+  *out = ptr;
+  return RLT_OK;
+}
+
+}  // namespace
+}  // namespace rlt
+
 extern "C" {
+
+int rlt_kv_pack_dedup_static(const RltPool* src, const RltBatch* batch, const RltOptions* options, void* packed,
+                             int64_t packed_bytes, rlt_stream_t stream) {
+  if (src == nullptr || batch == nullptr || options == nullptr) return RLT_E_INVALID;
+  if (options->mode != RLT_MODE_DEDUP) return RLT_E_INVALID;
+  if (batch->num_requests < 1 || batch->table_width < 1 || src->num_planes < 1) return RLT_E_INVALID;
+  const long long entries = static_cast<long long>(batch->num_requests) * batch->table_width * src->num_planes;
+  if (entries > rlt::kStaticPlanEntries) return RLT_E_LIMIT;
+  void* scratch = nullptr;
+  const int rc = rlt::static_plan_address(&scratch);
+  if (rc != RLT_OK) return rc;
+  return rlt::launch_table_copy(rlt::kPack, src, nullptr, batch, options, packed, packed_bytes,
+                                reinterpret_cast<cudaStream_t>(stream), scratch, rlt::kStaticPlanBytes);
+}
+
+int64_t rlt_kv_static_plan_entries(void) { return rlt::kStaticPlanEntries; }
 
 int rlt_kv_handoff(const RltPool* src, const RltPool* dst, const RltBatch* batch,
                    const RltOptions* options, rlt_stream_t stream) {
