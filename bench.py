@@ -145,6 +145,7 @@ def build_device_side(w, device, seed):
 
 def spot_check(w, src, dst, requests=(0, -1)):
     """Independent check with torch indexing: destination rows equal the selected source rows."""
+    import numpy as np
     import torch
 
     ok = True
@@ -156,10 +157,10 @@ def spot_check(w, src, dst, requests=(0, -1)):
             if w.exit_planes is None:
                 sp = torch.full((n,), plane, device=src.device)
             else:
-                e = torch.tensor(w.exit_planes[r][:n], device=src.device)
+                e = torch.tensor(np.asarray(w.exit_planes[r][:n]), device=src.device)
                 sp = e if w.extra["mode"] == "exit_only" else torch.minimum(e, torch.full_like(e, plane))
-            st = torch.tensor(w.src_tables[r], device=src.device)
-            dt = torch.tensor(w.dst_tables[r][plane], device=src.device)
+            st = torch.tensor(np.stack(w.src_tables[r]), device=src.device)
+            dt = torch.tensor(np.asarray(w.dst_tables[r][plane]), device=src.device)
             sb = st[sp, pos // bs]
             db = dt[pos // bs]
             pairs = [(src.key_cache, dst.key_cache), (src.value_cache, dst.value_cache)]

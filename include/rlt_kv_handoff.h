@@ -122,9 +122,10 @@ typedef struct RltOptions {
   int32_t layer_end;   /* 0 means num_layers                                                    */
   int32_t wire_planes; /* pack/scatter: planes on the wire; 0 = source planes (1 for EXIT_ONLY) */
   int32_t* status;     /* NULL or device/mapped int32[RLT_STATUS_WORDS], zeroed by the caller   */
-  int32_t grid_limit;  /* 0 = one full wave of resident CTAs; else cap on CTAs launched        */
-  int32_t variant;     /* low 4 bits pick the kernel flavour: 0 register path (default), 3 and 4
-                          cp.async.bulk rings; the other bits are tuning knobs and may stay 0       */
+  int32_t grid_limit;  /* 0 = one persistent wave (a few CTAs per SM); else cap on CTAs launched */
+  int32_t variant;     /* low 4 bits pick the kernel flavour: 0 register path (default), 1 and 2 its
+                          deeper-unrolled forms, 3 and 4 cp.async.bulk rings; bits 4-11 = unit size in
+                          16 KiB steps and bits 12-15 = CTAs per SM are tuning knobs, 0 = default     */
   void* workspace;     /* device scratch; needed only by pack/scatter in RLT_MODE_DEDUP          */
   int64_t workspace_bytes; /* at least rlt_kv_dedup_workspace_bytes(...) for those calls          */
 } RltOptions;
@@ -240,6 +241,25 @@ RLT_API int rlt_kv_push(const void* src, void* dst, int64_t nbytes, rlt_stream_t
  */
 RLT_API int rlt_kv_copy_segments(const int64_t* segments, int32_t count, rlt_stream_t stream);
 #define RLT_MAX_SEGMENTS 4096
+
+/* --- exit-depth propagation ------------------------------------------------------------------ */
+
+/*
+ * For each row (request index, exit plane, token position) copy the token's K,
+ * V and scale rows of the exit plane into every deeper plane of the same pool,
+ * for the layers whose bit is set in layer_mask (0 = all layers; the reference
+ * copies its recurrent_layers). rows is a device int32[count][3]; tables is the
+ * device int32[num_requests][planes][table_width] of the pool. One launch.
+ *
+ * Replaces KVCacheManager.finalize_token (vllm_rlt/core/kv_cache_manager.py:1053-1076)
+ * and the finalize_kernel launches of ModelRunner.finalize_many
+ * (vllm_rlt/kernels/routing.py:147-179, vllm_rlt/worker/model_runner.py:1349-1395).
+ * Scale tensors are copied whenever pool->scales is set, fixed-scale pools
+ * included, as the reference does.
+ */
+RLT_API int rlt_kv_finalize(const RltPool* pool, const int32_t* tables, int32_t num_requests, int32_t table_width,
+                            const int32_t* rows, int32_t count, uint64_t layer_mask, int32_t* status,
+                            rlt_stream_t stream);
 
 /* --- completion ----------------------------------------------------------------------------- */
 

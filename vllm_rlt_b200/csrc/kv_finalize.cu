@@ -1,0 +1,145 @@
+// Batched exit-depth propagation inside one LAST_EXITED pool.
+//
+// When a token leaves the recurrence at plane e, every deeper plane must hold a copy of
+// plane e's K/V row so that later tokens attending at those depths read the last computed
+// state. The reference does this per token with basic-index copies
+// (KVCacheManager.finalize_token, vllm_rlt/core/kv_cache_manager.py:1053-1076) or with a
+// Triton kernel over (row, target plane, channel tile) plus a second launch for the scales
+// (finalize_kernel, vllm_rlt/kernels/routing.py:147-179; ModelRunner.finalize_many,
+// vllm_rlt/worker/model_runner.py:1349-1395). Here one launch covers K, V and both scale
+// tensors: a work unit is (row, target plane, tensor) and moves the token's row of every
+// selected layer with 16-byte streaming loads and stores.
+//
+// HBM roofline: each selected (layer, tensor) row is read once per target plane (served by L2
+// after the first) and written once per target plane.
+
+#include "common.cuh"
+
+namespace rlt {
+namespace {
+
+struct FinalizeRegion {
+  char* key;
+  char* value;
+  long long block_bytes, layer_bytes, token_bytes;
+  int vec_bytes;
+};
+
+struct FinalizeParams {
+  FinalizeRegion region[2];
+  int num_regions;
+  int planes, block_size, num_blocks, num_layers;
+  unsigned long long layer_mask;  // bit l set: layer l is copied (the recurrent layers)
+  const int* tables;              // [requests, planes, table_width]
+  int table_width, num_requests;
+  const int* rows;                // [n][3]: request index, exit plane, token position
+  int n;
+  int* status;
+};
+
+template <typename T>
+__device__ __forceinline__ void copy_row(const char* src, char* dst, int vecs) {
+  const T* s = reinterpret_cast<const T*>(src);
+  T* d = reinterpret_cast<T*>(dst);
+  for (int i = threadIdx.x; i < vecs; i += kThreads) st_stream(d + i, ld_stream(s + i));
+}
+
+__global__ void __launch_bounds__(kThreads, 4) finalize_kernel(const FinalizeParams p) {
+  const int tensors = 2 * p.num_regions;
+  const int targets = p.planes - 1;
+  const long long units = static_cast<long long>(p.n) * targets * tensors;
+  for (long long w = blockIdx.x; w < units; w += gridDim.x) {
+    const int tensor = static_cast<int>(w % tensors);
+    const long long rest = w / tensors;
+    const int target = 1 + static_cast<int>(rest % targets);
+    const int row = static_cast<int>(rest / targets);
+    const int request = p.rows[3 * row], exit_plane = p.rows[3 * row + 1], position = p.rows[3 * row + 2];
+    if (request < 0 || request >= p.num_requests || exit_plane < 0 || exit_plane >= p.planes || position < 0 ||
+        position >= p.table_width * p.block_size) {
+      if (threadIdx.x == 0 && target == 1 && tensor == 0) report(p.status, RLT_STATUS_BAD_PLANE, row, position, exit_plane);
+      continue;
+    }
+    if (target <= exit_plane) continue;  // that plane was computed, not copied
+    const int page = position / p.block_size, offset = position - page * p.block_size;
+    const long long base = (static_cast<long long>(request) * p.planes) * p.table_width + page;
+    const int sb = p.tables[base + static_cast<long long>(exit_plane) * p.table_width];
+    const int db = p.tables[base + static_cast<long long>(target) * p.table_width];
+    if (sb < 0 || sb >= p.num_blocks || db < 0 || db >= p.num_blocks) {
+      if (threadIdx.x == 0) report(p.status, RLT_STATUS_BAD_BLOCK, request, page, sb < 0 || sb >= p.num_blocks ? sb : db);
+      continue;
+    }
+    const FinalizeRegion& rg = p.region[tensor >> 1];
+    char* pool = (tensor & 1) ? rg.value : rg.key;
+    for (int layer = 0; layer < p.num_layers; ++layer) {
+      if (!((p.layer_mask >> layer) & 1ull)) continue;
+      const long long in_block = layer * rg.layer_bytes + offset * rg.token_bytes;
+      const char* src = pool + sb * rg.block_bytes + in_block;
+      char* dst = pool + db * rg.block_bytes + in_block;
+      if (rg.vec_bytes == 16) {
+        copy_row<uint4>(src, dst, static_cast<int>(rg.token_bytes >> 4));
+      } else if (rg.vec_bytes == 4) {
+        copy_row<uint32_t>(src, dst, static_cast<int>(rg.token_bytes >> 2));
+      } else {
+        copy_row<uint8_t>(src, dst, static_cast<int>(rg.token_bytes));
+      }
+    }
+  }
+}
+
+}  // namespace
+}  // namespace rlt
+
+extern "C" {
+
+int rlt_kv_finalize(const RltPool* pool, const int32_t* tables, int32_t num_requests, int32_t table_width,
+                    const int32_t* rows, int32_t count, uint64_t layer_mask, int32_t* status, rlt_stream_t stream) {
+  if (count == 0) return RLT_OK;
+  if (pool == nullptr || tables == nullptr || rows == nullptr || count < 0 || num_requests < 1 || table_width < 1)
+    return RLT_E_INVALID;
+  if (pool->codes.key == nullptr || pool->codes.value == nullptr) return RLT_E_INVALID;
+  if (pool->num_layers < 1 || pool->num_layers > 64 || pool->block_size < 1 || pool->num_planes < 1 ||
+      pool->num_blocks < 1)
+    return RLT_E_LIMIT;
+  if (pool->num_planes == 1) return RLT_OK;  // a SHARED pool has nothing deeper to fill
+  rlt::FinalizeParams p{};
+  p.num_regions = pool->scales.key != nullptr ? 2 : 1;
+  if (p.num_regions == 2 && pool->scales.value == nullptr) return RLT_E_INVALID;
+  for (int g = 0; g < p.num_regions; ++g) {
+    const RltRegion& r = g == 0 ? pool->codes : pool->scales;
+    if (r.token_bytes <= 0 || r.layer_bytes != r.token_bytes * pool->block_size ||
+        r.block_bytes != r.layer_bytes * pool->num_layers)
+      return RLT_E_GEOMETRY;
+    rlt::FinalizeRegion& out = p.region[g];
+    out.key = static_cast<char*>(r.key);
+    out.value = static_cast<char*>(r.value);
+    out.block_bytes = r.block_bytes;
+    out.layer_bytes = r.layer_bytes;
+    out.token_bytes = r.token_bytes;
+    const uintptr_t bits = reinterpret_cast<uintptr_t>(r.key) | reinterpret_cast<uintptr_t>(r.value) |
+                           static_cast<uintptr_t>(r.token_bytes);
+    out.vec_bytes = (bits & 15u) == 0 ? 16 : (bits & 3u) == 0 ? 4 : 1;
+  }
+  p.planes = pool->num_planes;
+  p.block_size = pool->block_size;
+  p.num_blocks = pool->num_blocks;
+  p.num_layers = pool->num_layers;
+  const uint64_t all = pool->num_layers == 64 ? ~0ull : ((1ull << pool->num_layers) - 1ull);
+  p.layer_mask = layer_mask == 0 ? all : (layer_mask & all);
+  p.tables = tables;
+  p.table_width = table_width;
+  p.num_requests = num_requests;
+  p.rows = rows;
+  p.n = count;
+  p.status = status;
+  int sms = 0;
+  const int rc = rlt::sm_count(&sms);
+  if (rc != RLT_OK) return rc;
+  const long long units = static_cast<long long>(count) * (p.planes - 1) * 2 * p.num_regions;
+  const int grid = static_cast<int>(units < sms * 4ll ? units : sms * 4ll);
+  rlt::finalize_kernel<<<grid, rlt::kThreads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(p);
+  RLT_CUDA_TRY(cudaGetLastError());
+  rlt::g_launches.fetch_add(1, std::memory_order_relaxed);
+  return RLT_OK;
+}
+
+}  // extern "C"

@@ -201,6 +201,7 @@ __device__ __forceinline__ int units_per_plane(const TableCopyParams& p) {
   return n;
 }
 
+template <bool kDedup>
 __device__ __forceinline__ Unit decode_unit(const TableCopyParams& p, const int* blk_off, long long w,
                                             int per_plane, int per_block) {
   Unit u;
@@ -234,7 +235,7 @@ __device__ __forceinline__ Unit decode_unit(const TableCopyParams& p, const int*
   u.n_blk = blk_off[u.r + 1] - u.blk_first;
   u.sel_mask = 0;
   u.n_sel = u.n_tok;
-  if (p.dedup_wire && p.dst_packed) {
+  if (kDedup && p.dst_packed) {
     u.sel_mask = exit_mask(p, u.r, u.tok_lo, u.n_tok, u.plane);
     u.n_sel = __popcll(u.sel_mask);
   }
@@ -244,6 +245,7 @@ __device__ __forceinline__ Unit decode_unit(const TableCopyParams& p, const int*
 
 // Byte offsets (from the unit's source and destination tensor bases) of row `row` of a unit.
 // This is where block tables and exit planes are read. A row that must be skipped gets -1 / -1.
+template <bool kDedup>
 __device__ __forceinline__ void row_offsets(const TableCopyParams& p, const Unit& u, const int* tok_off, int row,
                                             long long* src_off, long long* dst_off) {
   const RegionParams& rg = p.region[u.g];
@@ -255,7 +257,7 @@ __device__ __forceinline__ void row_offsets(const TableCopyParams& p, const Unit
   // Packed image: request, plane, block, region, tensor, layer, token (reference walk order).
   long long packed = 0;
   bool ok = true;
-  if (p.dedup_wire) {
+  if (kDedup) {
     // Only rows whose plane is not deeper than the token's exit plane are on the wire. The wire
     // plane of this row, the tokens of the block that plane carries, and this token's rank among them:
     int wire_plane = u.plane, rank = tok, carried = u.n_sel;
@@ -333,7 +335,7 @@ __device__ __forceinline__ char* unit_dst(const TableCopyParams& p, const Unit& 
   return p.dst_packed ? rg.dst_key : (u.kv ? rg.dst_value : rg.dst_key);
 }
 
-template <int kUnroll, bool kStreaming>
+template <int kUnroll, bool kStreaming, bool kDedup>
 __global__ void __launch_bounds__(kThreads, 4) table_copy_kernel(const TableCopyParams p) {
   extern __shared__ int dyn_smem[];
   int* blk_off = dyn_smem;                       // [num_requests + 1]
@@ -349,11 +351,11 @@ __global__ void __launch_bounds__(kThreads, 4) table_copy_kernel(const TableCopy
 
   int parity = 0;
   for (long long w = blockIdx.x; w < total_units; w += gridDim.x, parity ^= 1) {
-    const Unit u = decode_unit(p, blk_off, w, per_plane, per_block);
+    const Unit u = decode_unit<kDedup>(p, blk_off, w, per_plane, per_block);
     const RegionParams& rg = p.region[u.g];
     long long* rs = row_src[parity];
     long long* rd = row_dst[parity];
-    if (threadIdx.x < u.rows) row_offsets(p, u, tok_off, threadIdx.x, &rs[threadIdx.x], &rd[threadIdx.x]);
+    if (threadIdx.x < u.rows) row_offsets<kDedup>(p, u, tok_off, threadIdx.x, &rs[threadIdx.x], &rd[threadIdx.x]);
     __syncthreads();  // one barrier per unit: the offset tables are double buffered
 
     const char* src = unit_src(p, u);
@@ -500,7 +502,7 @@ __device__ __forceinline__ void warp_copy_rows(const char* src, char* dst, long 
   }
 }
 
-template <int kBulkStages>
+template <int kBulkStages, bool kDedup>
 __global__ void __launch_bounds__(kBulkThreads, 1) table_bulk_kernel(const TableCopyParams p) {
   constexpr int kBulkStageBytes = kBulkWarpBytes / kBulkStages;
   extern __shared__ __align__(128) unsigned char bulk_smem[];
@@ -526,7 +528,7 @@ __global__ void __launch_bounds__(kBulkThreads, 1) table_bulk_kernel(const Table
   const long long stride = static_cast<long long>(gridDim.x) * kBulkWarps;
 
   for (long long w = first; w < total_units; w += stride) {
-    const Unit u = decode_unit(p, blk_off, w, per_plane, per_block);
+    const Unit u = decode_unit<kDedup>(p, blk_off, w, per_plane, per_block);
     const RegionParams& rg = p.region[u.g];
     const char* src = unit_src(p, u);
     char* dst = unit_dst(p, u);
@@ -536,7 +538,7 @@ __global__ void __launch_bounds__(kBulkThreads, 1) table_bulk_kernel(const Table
     int run_n = 0;
     for (int base = 0; base < u.rows; base += 32) {
       long long so = -1, dof = -1;
-      if (base + lane < u.rows) row_offsets(p, u, tok_off, base + lane, &so, &dof);
+      if (base + lane < u.rows) row_offsets<kDedup>(p, u, tok_off, base + lane, &so, &dof);
       const int count = min(32, u.rows - base);
       if (!bulk) {
         if (rg.vec_bytes == 16) {
@@ -870,7 +872,7 @@ int launch_table_copy(Direction dir, const RltPool* src, const RltPool* dst, con
   const int rc = sm_count(&sms);
   if (rc != RLT_OK) return rc;
   int per_sm = (opt->variant >> 12) & 0xf;
-  if (per_sm == 0) per_sm = 4;
+  if (per_sm == 0) per_sm = 3;
   int grid = sms * per_sm;
   if (opt->grid_limit > 0 && grid > opt->grid_limit) grid = opt->grid_limit;
   const size_t smem = 2 * (static_cast<size_t>(batch->num_requests) + 1) * sizeof(int);
@@ -879,35 +881,36 @@ int launch_table_copy(Direction dir, const RltPool* src, const RltPool* dst, con
     const int planned = plan_dedup(p, workspace, workspace_bytes, sms, smem, stream);
     if (planned != RLT_OK) return planned;
   }
-  switch (opt->variant & 0xf) {
-    case 0:
-      table_copy_kernel<8, true><<<grid, kThreads, smem, stream>>>(p);
-      break;
-    case 1:
-      table_copy_kernel<4, true><<<grid, kThreads, smem, stream>>>(p);
-      break;
-    case 2:
-      table_copy_kernel<8, false><<<grid, kThreads, smem, stream>>>(p);
-      break;
-    case 3:
-    case 4: {
-      // 3: eight 4 KiB stages per warp (six loads in flight); 4: four 8 KiB stages (two in flight).
-      const size_t bulk_smem_bytes = kBulkStageTotal + kBulkWarps * sizeof(BulkRing<8>) + smem;
-      // Opting in to large dynamic shared memory is per device; the call is cheap, so it is simply repeated.
-      const int want = static_cast<int>(bulk_smem_bytes);
-      RLT_CUDA_TRY(cudaFuncSetAttribute(table_bulk_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, want));
-      RLT_CUDA_TRY(cudaFuncSetAttribute(table_bulk_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, want));
-      int bulk_grid = sms;  // one CTA of kBulkWarps pipelines per SM
-      if (opt->grid_limit > 0 && bulk_grid > opt->grid_limit) bulk_grid = opt->grid_limit;
-      if ((opt->variant & 0xf) == 3) {
-        table_bulk_kernel<8><<<bulk_grid, kBulkThreads, bulk_smem_bytes, stream>>>(p);
-      } else {
-        table_bulk_kernel<4><<<bulk_grid, kBulkThreads, bulk_smem_bytes, stream>>>(p);
-      }
-      break;
+  const int flavour = opt->variant & 0xf;
+  if (flavour <= 2) {
+    void (*kernel)(const TableCopyParams) = nullptr;
+    if (dedup_wire) {
+      kernel = flavour == 1 ? table_copy_kernel<8, true, true>
+               : flavour == 2 ? table_copy_kernel<8, false, true> : table_copy_kernel<4, true, true>;
+    } else {
+      // Default: four 16-byte loads in flight per thread and three CTAs per SM. On the benchmark workload
+      // this measured 6.5-6.6 TB/s of HBM traffic; eight loads in flight or four CTAs per SM were 5-8 % slower.
+      kernel = flavour == 1 ? table_copy_kernel<8, true, false>
+               : flavour == 2 ? table_copy_kernel<8, false, false> : table_copy_kernel<4, true, false>;
     }
-    default:
-      return RLT_E_INVALID;
+    kernel<<<grid, kThreads, smem, stream>>>(p);
+  } else if (flavour <= 4) {
+    // 3: eight 4 KiB stages per warp (six loads in flight); 4: four 8 KiB stages (two in flight).
+    void (*kernel)(const TableCopyParams) = nullptr;
+    if (dedup_wire) {
+      kernel = flavour == 3 ? table_bulk_kernel<8, true> : table_bulk_kernel<4, true>;
+    } else {
+      kernel = flavour == 3 ? table_bulk_kernel<8, false> : table_bulk_kernel<4, false>;
+    }
+    const size_t bulk_smem_bytes = kBulkStageTotal + kBulkWarps * sizeof(BulkRing<8>) + smem;
+    // Opting in to large dynamic shared memory is per device; the call is cheap, so it is simply repeated.
+    RLT_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      static_cast<int>(bulk_smem_bytes)));
+    int bulk_grid = sms;  // one CTA of kBulkWarps pipelines per SM
+    if (opt->grid_limit > 0 && bulk_grid > opt->grid_limit) bulk_grid = opt->grid_limit;
+    kernel<<<bulk_grid, kBulkThreads, bulk_smem_bytes, stream>>>(p);
+  } else {
+    return RLT_E_INVALID;
   }
   RLT_CUDA_TRY(cudaGetLastError());
   g_launches.fetch_add(1, std::memory_order_relaxed);

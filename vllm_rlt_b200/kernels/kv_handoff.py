@@ -128,6 +128,42 @@ class PoolView:
 # --------------------------------------------------------------------------- batches
 
 
+class _Staging:
+    """One pinned host buffer; reusable once the copy that read it has completed."""
+
+    def __init__(self, capacity: int):
+        self.buffer = torch.empty(capacity, dtype=torch.uint8, pin_memory=True)
+        self.event = None
+
+    def free(self) -> bool:
+        return self.event is None or self.event.query()
+
+    def release(self) -> None:
+        self.event = torch.cuda.Event()
+        self.event.record()
+
+
+class _PinnedPool:
+    """Pinned staging buffers are costly to allocate (a driver call each), so they are kept and reused."""
+
+    def __init__(self):
+        self.buffers: list[_Staging] = []
+
+    def acquire(self, size: int) -> _Staging:
+        for b in self.buffers:
+            if b.buffer.numel() >= size and b.free():
+                b.event = None
+                return b
+        capacity = 1 << max(16, (size - 1).bit_length())
+        b = _Staging(capacity)
+        if len(self.buffers) < 64:
+            self.buffers.append(b)
+        return b
+
+
+_PINNED = _PinnedPool()
+
+
 class HandoffBatch:
     """Per-request tables and ranges, staged in pinned memory and copied to the device once.
 
@@ -162,34 +198,45 @@ class HandoffBatch:
             if not 0 <= s < e:
                 raise ValueError("invalid KV range")
         self.total_tokens = sum(e - s for s, e in self.ranges)
-        sides = []
-        width = 1
+        arrays, width = [], 1
+        flats = []
         for tables, limit in ((src_tables, src_blocks), (dst_tables, dst_blocks)):
             if tables is None:
-                sides.append(None)
+                flats.append(None)
                 continue
             if len(tables) != n:
                 raise ValueError("one table set per request is required")
             planes = len(tables[0])
+            pages = []
             for req, (s, e) in zip(tables, self.ranges):
                 if len(req) != planes:
                     raise ValueError("requests of one batch must have the same number of planes")
+                m = len(req[0])
                 for table in req:
                     if e > len(table) * block_size:
                         raise ValueError("KV range exceeds allocation")
-                    width = max(width, len(table))
-            sides.append((tables, planes, limit))
+                    if len(table) != m:
+                        raise ValueError("the planes of one request must have tables of equal length")
+                pages.append(m)
+                width = max(width, m)
+            # one flat conversion of every table entry, in (request, plane, page) order
+            total = planes * sum(pages)
+            if isinstance(tables[0][0], np.ndarray):
+                flat = np.concatenate([t for req in tables for t in req]).astype(np.int32, copy=False)
+            else:
+                flat = np.fromiter((b for req in tables for table in req for b in table), np.int32, count=total)
+            flats.append((flat, planes, pages, limit))
         self.table_width = width
-        arrays = []
-        for side in sides:
+        for side in flats:
             if side is None:
                 arrays.append(None)
                 continue
-            tables, planes, limit = side
+            flat, planes, pages, limit = side
             a = np.zeros((n, planes, width), np.int32)
-            for r, req in enumerate(tables):
-                for p, table in enumerate(req):
-                    a[r, p, : len(table)] = table
+            at = 0
+            for r, m in enumerate(pages):
+                a[r, :, :m] = flat[at : at + planes * m].reshape(planes, m)
+                at += planes * m
                 s, e = self.ranges[r]
                 used = a[r, :, s // block_size : (e - 1) // block_size + 1]
                 if used.min() < 0 or (limit is not None and used.max() >= limit):
@@ -225,16 +272,14 @@ class HandoffBatch:
             size += a.nbytes
         self.metadata_bytes = size
         device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
-        self._host = torch.empty(size, dtype=torch.uint8, pin_memory=True)
-        host = self._host.numpy()
+        staging = _PINNED.acquire(size)
+        host = staging.buffer.numpy()
         for name, (at, a) in layout.items():
             host[at : at + a.nbytes] = a.reshape(-1).view(np.uint8)
         self._dev = torch.empty(size, dtype=torch.uint8, device=device)
-        if stream is None:
-            self._dev.copy_(self._host, non_blocking=True)
-        else:
-            with torch.cuda.stream(stream):
-                self._dev.copy_(self._host, non_blocking=True)
+        with torch.cuda.device(device), torch.cuda.stream(stream if stream is not None else torch.cuda.current_stream(device)):
+            self._dev.copy_(staging.buffer[:size], non_blocking=True)
+            staging.release()
         base = self._dev.data_ptr()
         self._ptr = {name: base + at for name, (at, _) in layout.items()}
         self.has_exit = exits is not None
@@ -339,6 +384,39 @@ def kv_scatter(packed: torch.Tensor, dst: PoolView, batch: HandoffBatch, *, mode
     o = _options(mode if mode == MODE_DEDUP else MODE_ALL_PLANES, layer_begin, layer_end, wire_planes, status,
                  grid_limit, variant, workspace)
     _lib.check(lib.rlt_kv_scatter(packed.data_ptr(), packed.numel(), C.byref(d), C.byref(b), C.byref(o), _stream_ptr(stream)), "rlt_kv_scatter")
+
+
+def kv_finalize(pool: PoolView, tables: torch.Tensor, rows: torch.Tensor, *, layers=None, status=None, stream=None) -> None:
+    """Copy each row's exit-plane K/V (and scales) into every deeper plane.
+
+    ``tables`` is the pool's device ``int32 [requests, planes, width]``; ``rows`` is a device
+    ``int32 [n, 3]`` of (request index, exit plane, token position); ``layers`` lists the layers to
+    copy (default all; pass the model's recurrent layers for boundary-KV models). For scale tensors
+    to be copied the view must carry them: build it with ``PoolView.from_tensors(..., key_scale,
+    value_scale)`` also for a fixed-scale pool.
+    """
+    for t, name, cols in ((tables, "tables", None), (rows, "rows", 3)):
+        if t.dtype != torch.int32 or not t.is_contiguous() or not t.is_cuda:
+            raise ValueError(f"{name} must be a contiguous CUDA int32 tensor")
+    if tables.dim() != 3 or tables.shape[1] != pool.num_planes:
+        raise ValueError("tables must be [requests, planes, width] with the pool's plane count")
+    if rows.dim() != 2 or rows.shape[1] != 3:
+        raise ValueError("rows must be [n, 3]: request index, exit plane, token position")
+    mask = 0
+    if layers is not None:
+        for layer in layers:
+            if not 0 <= layer < pool.num_layers:
+                raise ValueError("recurrent_layers must be valid cache layer indices")
+            mask |= 1 << layer
+        if mask == 0:
+            raise ValueError("recurrent_layers must be nonempty and unique")
+    s = pool.as_struct()
+    _lib.check(
+        _lib.load().rlt_kv_finalize(C.byref(s), tables.data_ptr(), tables.shape[0], tables.shape[2], rows.data_ptr(),
+                                    rows.shape[0], mask, status.data_ptr() if status is not None else None,
+                                    _stream_ptr(stream)),
+        "rlt_kv_finalize",
+    )
 
 
 def kv_push(src_ptr: int, dst_ptr: int, nbytes: int, *, stream=None) -> None:

@@ -18,6 +18,8 @@ import random
 import statistics
 import time
 
+import numpy as np
+
 
 
 def run_multi(args, rank: int, world: int) -> None:
@@ -149,9 +151,9 @@ def run_multi(args, rank: int, world: int) -> None:
             if w.exit_planes is None:
                 sp = torch.full((sample,), plane, device=device)
             else:
-                e = torch.tensor(w.exit_planes[0][:sample], device=device)
+                e = torch.tensor(np.asarray(w.exit_planes[0][:sample]), device=device)
                 sp = e if args.mode == "exit_only" else torch.clamp(e, max=plane)
-            st = torch.tensor(w.src_tables[0], device=device)
+            st = torch.tensor(np.stack(w.src_tables[0]), device=device)
             sb = st[sp, pos // s.block_size]
             expect[0] = src.key_cache[sb, :, pos % s.block_size]
             expect[1] = src.value_cache[sb, :, pos % s.block_size]

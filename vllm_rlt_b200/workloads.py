@@ -11,6 +11,8 @@ import math
 import random
 from dataclasses import dataclass, field
 
+import numpy as np
+
 SEED_BASE = 20261125
 
 
@@ -81,12 +83,13 @@ def _tables(rng: random.Random, lengths, planes, block_size, spare=0):
     total = sum(pages) * planes + spare
     order = list(range(total))
     rng.shuffle(order)
+    order = np.array(order, np.int32)
     at = 0
     tables = []
     for p in pages:
         req = []
         for _ in range(planes):
-            req.append(order[at : at + p])
+            req.append(order[at : at + p])  # host int32 arrays: what a worker would keep its tables in
             at += p
         tables.append(req)
     return tables, total
@@ -133,7 +136,8 @@ def last_exited_exit_only(
     dst_planes = 1 if mode == "exit_only" else shape.planes
     src_tables, src_blocks = _tables(rng, lengths, shape.planes, shape.block_size)
     dst_tables, dst_blocks = _tables(rng, lengths, dst_planes, shape.block_size)
-    exits = [[rng.randrange(shape.planes) for _ in range(n)] for n in lengths]
+    # per-token exit planes as int32 arrays (a model produces them as a tensor, not as Python lists)
+    exits = [np.array([rng.randrange(shape.planes) for _ in range(n)], np.int32) for n in lengths]
     return Workload(
         shape, lengths, [(0, n) for n in lengths], src_tables, dst_tables,
         exits if mode != "all" else None, src_blocks, dst_blocks, dst_planes,
