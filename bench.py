@@ -127,20 +127,27 @@ def build_device_side(w, device, seed):
     kw = dict(device=device, kv_cache_dtype="fp8_e4m3" if s.fp8 else "auto")
     src = KVPool(s.num_layers, s.num_kv_heads, s.head_dim, w.src_blocks, s.block_size, s.planes, **kw)
     dst = KVPool(s.num_layers, s.num_kv_heads, s.head_dim, w.dst_blocks, s.block_size, w.dst_planes, **kw)
-    gen = torch.Generator(device=device).manual_seed(seed)
-    if s.fp8:
+    fill_source(src, s, seed)
+    for t in (dst.key_cache, dst.value_cache):
+        t.view(torch.uint8).fill_(0xA5)
+    return src, dst
+
+
+def fill_source(src, shape, seed):
+    """N(0,1) bf16 values, or random e4m3 bytes without the NaN encodings plus U[0.01, 0.1] float32 scales."""
+    import torch
+
+    gen = torch.Generator(device=src.device).manual_seed(seed)
+    if shape.fp8:
         for t in (src.key_cache, src.value_cache):
             raw = t.view(torch.uint8)
             raw.random_(0, 256, generator=gen)
-            raw[(raw & 0x7F) == 0x7F] = 0x3C
+            raw.masked_fill_((raw & 0x7F) == 0x7F, 0x3C)
         for t in (src.key_scale, src.value_scale):
             t.uniform_(0.01, 0.1, generator=gen)
     else:
         src.key_cache.normal_(generator=gen)
         src.value_cache.normal_(generator=gen)
-    for t in (dst.key_cache, dst.value_cache):
-        t.view(torch.uint8).fill_(0xA5)
-    return src, dst
 
 
 def spot_check(w, src, dst, requests=(0, -1)):
@@ -438,6 +445,12 @@ def main():
     ap.add_argument("--variant", type=int, default=0)
     ap.add_argument("--cpu-tokens", type=int, default=1024)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--prefill", type=int, default=0, help="prefill ranks at N >= 2 (default N/2)")
+    ap.add_argument("--workload", default="ouro1p4b",
+                    choices=["ouro1p4b", "ouro2p6b", "ouro2p6b_fp8_shared", "huginn", "ouro2p6b_chunk"])
+    ap.add_argument("--streaming", action="store_true", help="also replay a layer-by-layer prefill and stream behind it")
+    ap.add_argument("--layer-us", type=float, default=200.0, help="simulated prefill time per layer and depth")
+    ap.add_argument("--layers-per-slice", type=int, default=4)
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     rank = int(os.environ.get("RANK", "0"))

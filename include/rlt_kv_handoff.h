@@ -128,6 +128,8 @@ typedef struct RltOptions {
                           16 KiB steps and bits 12-15 = CTAs per SM are tuning knobs, 0 = default     */
   void* workspace;     /* device scratch; needed only by pack/scatter in RLT_MODE_DEDUP          */
   int64_t workspace_bytes; /* at least rlt_kv_dedup_workspace_bytes(...) for those calls          */
+  int32_t plane_begin; /* destination (or wire) plane slice [plane_begin, plane_end): lets a   */
+  int32_t plane_end;   /* depth be handed off as soon as it is computed; 0 means all planes     */
 } RltOptions;
 
 /* --- information ---------------------------------------------------------------------------- */

@@ -413,3 +413,39 @@ def test_dedup_pack_needs_a_workspace_of_the_stated_size():
     small = torch.zeros(32, dtype=torch.uint8, device="cuda")
     with pytest.raises(ValueError, match="size limit"):
         k.kv_pack(gp.view(), batch, packed, mode=k.MODE_DEDUP, workspace=small)
+
+
+@pytest.mark.parametrize("mode_name", ["all", "dedup"])
+def test_plane_and_layer_slices_tile_the_full_handoff(mode_name):
+    """Per-depth streaming: every (plane slice, layer slice) launch moves exactly its part; together they are the handoff."""
+    k = kh()
+    kind, shape = SHAPES["ouro_fp8_small"]
+    planes, layers = shape[5], shape[0]
+    P, D, reqs, exits = dedup_case(kind, shape, 33, [45, 16, 7])
+    mode = ho.MODE_ALL_PLANES if mode_name == "all" else ho.MODE_DEDUP
+    gp, gd = GpuPool(P), GpuPool(D)
+    batch = k.HandoffBatch(
+        [P.plane_block_tables(r) for r, *_ in reqs], [D.plane_block_tables(r) for r, *_ in reqs],
+        [(s, e) for _, s, e in reqs], block_size=shape[4], exit_planes=exits,
+    )
+    status = k.new_status()
+    for p0, p1 in ((0, 1), (1, 3), (3, planes)):
+        for l0, l1 in ((0, 2), (2, layers)):
+            k.kv_handoff(gp.view(), gd.view(), batch, mode=mode, layer_begin=l0, layer_end=l1, plane_begin=p0,
+                         plane_end=p1, status=status)
+            for i, (r, s, e) in enumerate(reqs):
+                st, dt = P.plane_block_tables(r), D.plane_block_tables(r)
+                for plane in range(p0, p1):
+                    for t in range(s, e):
+                        sp = ho.source_plane(mode, plane, exits[i][t])
+                        for a, b in zip(P.tensors(), D.tensors()):
+                            b.data[dt[plane][t // 16], l0:l1, t % 16] = a.data[st[sp][t // 16], l0:l1, t % 16]
+            assert_pools_equal(gd, D)
+    k.raise_for_status(status)
+    D2 = sentinel_destination(kind, shape)
+    D2._free, D2.tables = [], dict(D.tables)
+    for r, s, e in reqs:
+        ho.handoff_reference(P, D2, P.plane_block_tables(r), D2.plane_block_tables(r), s, e)
+    assert_pools_equal(gd, D2)
+    with pytest.raises(ValueError, match="invalid argument"):
+        k.kv_handoff(gp.view(), gd.view(), batch, plane_begin=2, plane_end=planes + 1)

@@ -69,6 +69,8 @@ class RltOptions(C.Structure):
         ("variant", C.c_int32),
         ("workspace", C.c_void_p),
         ("workspace_bytes", C.c_int64),
+        ("plane_begin", C.c_int32),
+        ("plane_end", C.c_int32),
     ]
 
 

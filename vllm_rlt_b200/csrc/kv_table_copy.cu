@@ -53,7 +53,9 @@ struct TableCopyParams {
   int num_requests;
   int table_width;
   int src_planes;
-  int dst_planes;   // planes iterated: destination planes, or wire planes for pack
+  int dst_planes;   // destination planes, or wire planes for pack
+  int plane_begin;  // planes iterated by this launch: [plane_begin, plane_begin + plane_count)
+  int plane_count;
   int block_size;
   int src_blocks;
   int dst_blocks;
@@ -207,8 +209,9 @@ __device__ __forceinline__ Unit decode_unit(const TableCopyParams& p, const int*
   Unit u;
   const int blk_idx = static_cast<int>(w / per_block);
   int sub = static_cast<int>(w - static_cast<long long>(blk_idx) * per_block);
-  u.plane = sub / per_plane;
-  sub -= u.plane * per_plane;
+  const int plane_rel = sub / per_plane;
+  sub -= plane_rel * per_plane;
+  u.plane = p.plane_begin + plane_rel;
   u.g = 0;
   if (sub >= 2 * p.region[0].chunks) {
     u.g = 1;
@@ -346,7 +349,7 @@ __global__ void __launch_bounds__(kThreads, 4) table_copy_kernel(const TableCopy
   scan_requests<kThreads>(p, blk_off, tok_off);
 
   const int per_plane = units_per_plane(p);
-  const int per_block = per_plane * p.dst_planes;
+  const int per_block = per_plane * p.plane_count;
   const long long total_units = static_cast<long long>(blk_off[p.num_requests]) * per_block;
 
   int parity = 0;
@@ -522,7 +525,7 @@ __global__ void __launch_bounds__(kBulkThreads, 1) table_bulk_kernel(const Table
   scan_requests<kBulkThreads>(p, blk_off, tok_off);  // ends with __syncthreads: barriers are initialised for everyone
 
   const int per_plane = units_per_plane(p);
-  const int per_block = per_plane * p.dst_planes;
+  const int per_block = per_plane * p.plane_count;
   const long long total_units = static_cast<long long>(blk_off[p.num_requests]) * per_block;
   const long long first = static_cast<long long>(blockIdx.x) * kBulkWarps + warp;
   const long long stride = static_cast<long long>(gridDim.x) * kBulkWarps;
@@ -816,6 +819,10 @@ int launch_table_copy(Direction dir, const RltPool* src, const RltPool* dst, con
     p.exit_planes = dedup_wire ? batch->exit_planes : nullptr;
   }
   p.plane_bias = opt->mode == RLT_MODE_EXIT_ONLY ? p.src_planes : 0;
+  p.plane_begin = opt->plane_begin;
+  const int plane_end = opt->plane_end == 0 ? p.dst_planes : opt->plane_end;
+  if (p.plane_begin < 0 || plane_end <= p.plane_begin || plane_end > p.dst_planes) return RLT_E_INVALID;
+  p.plane_count = plane_end - p.plane_begin;
 
   const int slice_layers = layer_end - layer_begin;
   const long long row_total = any->codes.token_bytes + (scales ? any->scales.token_bytes : 0);

@@ -1,13 +1,18 @@
-"""Multi-GPU handoff harness: N/2 prefill GPUs push KV to N/2 decode GPUs over NVLink.
+"""Multi-GPU handoff harness: prefill GPUs push KV to decode GPUs over NVLink.
 
-One process per GPU (torchrun). Rank ``p`` in the first half is a prefill worker that owns a
-source pool; rank ``p + N/2`` is its decode worker and owns the destination pool. The pairs
-are independent: there is no collective on the data path. NCCL carries only the metadata a
-real deployment exchanges on its control channel (``reserved`` -> ``prefill`` messages,
-vllm_rlt/pd/engine.py:197-214): the decode side's block tables and the IPC handles of its
-pools. KV bytes go from the prefill GPU's SMs straight into the decode GPU's pool through
-peer pointers (plain per-thread stores), followed by a release-store of a
-completion flag in the decode GPU's memory that the decode side waits on with a bounded wait.
+One process per GPU (torchrun). The first ``P`` ranks are prefill workers that own source pools,
+the rest are decode workers that own destination pools; ``P`` defaults to half the ranks and can be
+any split (2:6, 4:4, 6:2 ...). Requests of a prefill worker are routed round-robin over its decode
+partners. Every P->D edge is independent: there is no collective on the data path. NCCL carries only
+the metadata a real deployment exchanges on its control channel (``reserved`` -> ``prefill``,
+vllm_rlt/pd/engine.py:197-214): the decode side's block tables and the IPC handles of its pools and
+flags. KV bytes go from the prefill GPU's SMs straight into the decode GPU's pool through peer
+pointers (plain per-thread stores), followed by a release-store of a completion flag in the decode
+GPU's memory that the decode side waits on with a bounded wait.
+
+Two timed modes: the default hands a finished batch off in one launch per edge; ``--streaming``
+replays a layer-by-layer prefill (a timed dummy kernel per layer) and streams each (depth, layer
+group) behind it, reporting how long after the prefill's end the last byte lands.
 """
 
 from __future__ import annotations
@@ -20,6 +25,29 @@ import time
 
 import numpy as np
 
+MODES = {"exit_only": 2, "dedup": 1, "all": 0}
+
+
+def make_workload(args, prefill_index: int):
+    """The workload of one prefill worker; every rank can rebuild any worker's from its index."""
+    from vllm_rlt_b200 import workloads as wl
+
+    seed = wl.SEED_BASE + 1 + 17 * prefill_index
+    name = getattr(args, "workload", "ouro1p4b")
+    if name == "ouro1p4b":
+        return wl.last_exited_exit_only(wl.OURO_1P4B, requests=args.requests, mode=args.mode, seed=seed)
+    if name == "ouro2p6b":
+        return wl.last_exited_exit_only(wl.OURO_2P6B, requests=args.requests, mode=args.mode, seed=seed)
+    if name == "ouro2p6b_fp8_shared":
+        # FP8 e4m3 with travelling float32 scales; "SHARED for loops >= 2" = two planes (loop 1, loops 2..4)
+        shape = wl.KVShape("ouro-2.6b-fp8 planes[0,1,1,1]", 48, 16, 128, 2, fp8=True)
+        return wl.per_depth_all_planes(shape, requests=args.requests, min_len=1024, max_len=8192, seed=seed, log_uniform=True)
+    if name == "huginn":
+        return wl.recurrent_depth_dedup(wl.HUGINN_3P5B, requests=args.requests, seed=seed)
+    if name == "ouro2p6b_chunk":
+        # one 2048-token prefill chunk per request, all planes (what a WCPB step finishes)
+        return wl.per_depth_all_planes(wl.OURO_2P6B, requests=args.requests, min_len=2048, max_len=2048, seed=seed)
+    raise SystemExit(f"unknown workload {name}")
 
 
 def run_multi(args, rank: int, world: int) -> None:
@@ -32,75 +60,157 @@ def run_multi(args, rank: int, world: int) -> None:
     from vllm_rlt_b200.kernels import kv_handoff as kh
     from vllm_rlt_b200.pd import exchange
     from vllm_rlt_b200.pd import peer as peerlib
+    from vllm_rlt_b200.pd.streaming import LayerStreamer
 
-    if world != args.gpus or world % 2:
-        raise SystemExit("--gpus must equal WORLD_SIZE and be even for a P:D split")
+    if world != args.gpus:
+        raise SystemExit("--gpus must equal WORLD_SIZE")
+    n_prefill = args.prefill or world // 2
+    n_decode = world - n_prefill
     local = int(os.environ.get("LOCAL_RANK", rank))
     device = torch.device("cuda", local)
     torch.cuda.set_device(device)
     dist.init_process_group("nccl", device_id=device)
-    pairs = world // 2
-    is_prefill, pair, partners = exchange.pairing(rank, world)
-    partner = partners[0]
+    is_prefill, index, partners = exchange.pairing(rank, world, n_prefill)
+    mode = MODES[args.mode]
 
-    # Same per-pair workload at every N (weak scaling); each pair gets its own seed.
-    w = workloads.last_exited_exit_only(requests=args.requests, mode=args.mode, seed=workloads.SEED_BASE + 1 + 17 * pair)
-    s = w.shape
-    mode = {"exit_only": kh.MODE_EXIT_ONLY, "dedup": kh.MODE_DEDUP, "all": kh.MODE_ALL_PLANES}[args.mode]
+    def assigned(p_index: int, d_rank: int, w):
+        """Requests of prefill worker p_index that go to decode rank d_rank (round-robin over its partners)."""
+        _, _, p_partners = exchange.pairing(p_index, world, n_prefill)
+        return [i for i in range(len(w.lengths)) if p_partners[i % len(p_partners)] == d_rank]
+
+    # ---- workloads: a prefill rank builds its own; a decode rank rebuilds those of its sources ----
+    if is_prefill:
+        w = make_workload(args, index)
+        shape = w.shape
+        sources = []
+    else:
+        sources = partners  # prefill ranks (== prefill indices) that send to this decode rank
+        per_source = {p: make_workload(args, p) for p in sources}
+        w = next(iter(per_source.values()))
+        shape = w.shape
+    s = shape
+    dst_planes = w.dst_planes
+    fan_in = max(len(exchange.pairing(r, world, n_prefill)[2]) for r in range(n_prefill, world))
+    width = -(-max(getattr(args, "max_len", 0) or 0, max(w.lengths)) // s.block_size)
+    width_t = torch.tensor([width], device=device)
+    dist.all_reduce(width_t, op=dist.ReduceOp.MAX)
+    width = int(width_t.item())
     kw = dict(device=device, kv_cache_dtype="fp8_e4m3" if s.fp8 else "auto")
-    width = max(len(t) for req in w.dst_tables for t in req)
+    n_req = len(w.lengths)
 
     # ---- set-up: pools, decode-side reservation, metadata exchange over NCCL ----------------
-    table_msg = torch.zeros((len(w.lengths), w.dst_planes, width), dtype=torch.int32, device=device)
-    handle_msg = torch.zeros((3, exchange.HANDLE_ROW), dtype=torch.uint8, device=device)  # key, value, flag
+    table_msg = torch.zeros((fan_in, n_req, dst_planes, width), dtype=torch.int32, device=device)
+    n_handles = (4 if s.fp8 else 2) + fan_in
+    handle_msg = torch.zeros((n_handles, exchange.HANDLE_ROW), dtype=torch.uint8, device=device)
     if is_prefill:
         src = KVPool(s.num_layers, s.num_kv_heads, s.head_dim, w.src_blocks, s.block_size, s.planes, **kw)
-        gen = torch.Generator(device=device).manual_seed(workloads.SEED_BASE + pair)
-        src.key_cache.normal_(generator=gen)
-        src.value_cache.normal_(generator=gen)
-        flag = None
+        bench.fill_source(src, s, workloads.SEED_BASE + index)
     else:
-        dst = KVPool(s.num_layers, s.num_kv_heads, s.head_dim, w.dst_blocks, s.block_size,
-                     w.dst_planes, layout="last_exited", **kw)
+        total_blocks = 0
+        for p, wp in per_source.items():
+            total_blocks += sum(-(-wp.lengths[i] // s.block_size) for i in assigned(p, rank, wp)) * dst_planes
+        dst = KVPool(s.num_layers, s.num_kv_heads, s.head_dim, max(total_blocks, 1), s.block_size, dst_planes,
+                     layout="last_exited", **kw)
         for t in (dst.key_cache, dst.value_cache):
             t.view(torch.uint8).fill_(0xA5)
-        # decode-side allocation hook: a seeded permutation of the free list, then one reservation per request
-        random.Random(workloads.SEED_BASE + 1000 + pair).shuffle(dst._free_blocks)
-        tables = []
-        for i, n in enumerate(w.lengths):
-            got = dst.reserve_transfer(f"r{i}", n)
-            assert got is not None
-            tables.append(got)
-        table_msg.copy_(exchange.encode_tables(tables, w.dst_planes, width))
-        flag = torch.zeros(1, dtype=torch.int64, device=device)
-        handle_msg.copy_(exchange.encode_handles([peerlib.export_tensor(t) for t in (dst.key_cache, dst.value_cache, flag)]))
+        # decode-side allocation hook: seeded permutation of the free list, one reservation per incoming request
+        random.Random(workloads.SEED_BASE + 1000 + index).shuffle(dst._free_blocks)
+        reserved = {}
+        for slot, p in enumerate(sources):
+            wp = per_source[p]
+            tables = [[] for _ in range(n_req)]
+            for i in assigned(p, rank, wp):
+                got = dst.reserve_transfer(f"p{p}-r{i}", wp.lengths[i])
+                assert got is not None
+                tables[i] = got
+                reserved[(p, i)] = got
+            padded = [t if t else [[] for _ in range(dst_planes)] for t in tables]
+            table_msg[slot].copy_(exchange.encode_tables(padded, dst_planes, width))
+        flags = torch.zeros(fan_in, dtype=torch.int64, device=device)
+        exported = [dst.key_cache, dst.value_cache] + ([dst.key_scale, dst.value_scale] if s.fp8 else [])
+        rows = [peerlib.export_tensor(t) for t in exported]
+        flag_export = peerlib.export_tensor(flags)
+        for slot in range(fan_in):
+            rows.append(dict(flag_export, offset=flag_export["offset"] + 8 * slot))
+        handle_msg.copy_(exchange.encode_handles(rows))
     all_tables, all_handles = exchange.all_gather_metadata(table_msg, handle_msg)
+    blocks_msg = torch.tensor([0 if is_prefill else dst.num_blocks], device=device)
+    all_blocks = [torch.zeros_like(blocks_msg) for _ in range(world)]
+    dist.all_gather(all_blocks, blocks_msg)
     torch.cuda.synchronize()
 
     status = kh.new_status(device)
     mapping = peerlib.PeerMapping()
+    edges = []  # prefill side: one entry per decode partner
     if is_prefill:
-        dst_tables = exchange.decode_tables(all_tables[partner], w.lengths, s.block_size)
-        ptrs = [mapping.pointer(e) for e in exchange.decode_handles(all_handles[partner])]
         sv = kh.PoolView.from_cache(src)
-        dv = kh.PoolView(sv.codes.rebased(ptrs[0], ptrs[1]), None, w.dst_blocks, s.block_size, s.num_layers, w.dst_planes, -1)
-        flag_ptr = ptrs[2]
+        for d_rank in partners:
+            d_sources = exchange.pairing(d_rank, world, n_prefill)[2]
+            slot = d_sources.index(rank)
+            mine = assigned(index, d_rank, w)
+            if not mine:
+                continue
+            decoded = exchange.decode_tables(all_tables[d_rank][slot], w.lengths, s.block_size)
+            ptrs = [mapping.pointer(e) for e in exchange.decode_handles(all_handles[d_rank])]
+            n_pool = 4 if s.fp8 else 2
+            scales = sv.scales.rebased(ptrs[2], ptrs[3]) if s.fp8 else None
+            d_blocks = int(all_blocks[d_rank].item())
+            dv = kh.PoolView(sv.codes.rebased(ptrs[0], ptrs[1]), scales, d_blocks, s.block_size, s.num_layers, dst_planes, -1)
+            sub = dict(
+                src_tables=[w.src_tables[i] for i in mine], dst_tables=[decoded[i] for i in mine],
+                ranges=[w.ranges[i] for i in mine],
+                exit_planes=None if w.exit_planes is None else [w.exit_planes[i] for i in mine],
+            )
+            edge = dict(d_rank=d_rank, dv=dv, flag_ptr=ptrs[n_pool + slot], sub=sub, mine=mine,
+                        payload=sum(w.ranges[i][1] - w.ranges[i][0] for i in mine) * dst_planes * s.token_plane_bytes)
 
-        def make_batch():
-            return kh.HandoffBatch(w.src_tables, dst_tables, w.ranges, block_size=s.block_size, exit_planes=w.exit_planes,
-                                   src_blocks=w.src_blocks, dst_blocks=w.dst_blocks, device=device)
+            def make_batch(sub=sub):
+                return kh.HandoffBatch(sub["src_tables"], sub["dst_tables"], sub["ranges"], block_size=s.block_size,
+                                       exit_planes=sub["exit_planes"], src_blocks=w.src_blocks, device=device)
 
-        batch = make_batch()
+            edge["make_batch"] = make_batch
+            edge["batch"] = make_batch()
+            edges.append(edge)
+    my_payload = sum(e["payload"] for e in edges)
     counter = 0
 
     def step():
         nonlocal counter
         counter += 1
         if is_prefill:
-            kh.kv_handoff(sv, dv, batch, mode=mode, status=status, variant=args.variant)
-            kh.kv_signal(flag_ptr, counter)
+            for e in edges:
+                kh.kv_handoff(sv, e["dv"], e["batch"], mode=mode, status=status, variant=args.variant)
+                kh.kv_signal(e["flag_ptr"], counter)
         else:
-            kh.kv_wait(flag.data_ptr(), counter, kh._lib.MAX_WAIT_NS, status)
+            for slot in range(len(sources)):
+                kh.kv_wait(flags.data_ptr() + 8 * slot, counter, kh._lib.MAX_WAIT_NS, status)
+
+    # ---- streaming replay: a dummy prefill of `layer_us` per layer and depth, handoff slices behind it ----
+    def streaming_step(layer_us: float, layers_per_slice: int):
+        """Returns (prefill end event, handoff end event, compute stream) for one chunk pass on a prefill rank."""
+        nonlocal counter
+        counter += 1
+        if not is_prefill:
+            for slot in range(len(sources)):
+                kh.kv_wait(flags.data_ptr() + 8 * slot, counter, kh._lib.MAX_WAIT_NS, status)
+            return None
+        compute = torch.cuda.current_stream(device)
+        streamers = [LayerStreamer(sv, e["dv"], e["batch"], mode=mode, layers_per_slice=layers_per_slice,
+                                   status=status, variant=args.variant) for e in edges]
+        for st in streamers:
+            st.stream.wait_stream(compute)
+        cycles = int(layer_us * 1e-6 * 1.9e9)
+        for plane in range(dst_planes):
+            for layer in range(s.num_layers):
+                torch.cuda._sleep(cycles)  # stands in for one layer of prefill compute at this depth
+                for st in streamers:
+                    st.layer_done(plane, layer, producer_stream=compute)
+        prefill_end = torch.cuda.Event(enable_timing=True)
+        prefill_end.record(compute)
+        ends = [st.finish(e["flag_ptr"], counter) for st, e in zip(streamers, edges)]
+        for st in streamers:
+            compute.wait_stream(st.stream)
+        return prefill_end, ends, sum(st.launched for st in streamers)
 
     for _ in range(args.warmup):
         step()
@@ -136,35 +246,50 @@ def run_multi(args, rank: int, world: int) -> None:
     total_ms = torch.tensor([t0.elapsed_time(t1)], device=device)
     dist.all_reduce(total_ms, op=dist.ReduceOp.MAX)
     kernel_ms = statistics.mean(a.elapsed_time(b) for a, b in events)
+    # per-GPU rates: egress of a prefill GPU, ingress of a decode GPU (bytes it received / its wait time)
+    egress = torch.tensor([my_payload / (kernel_ms * 1e-3) / 1e9 if is_prefill else float("inf")], device=device)
+    dist.all_reduce(egress, op=dist.ReduceOp.MIN)
     k_ms = torch.tensor([kernel_ms if is_prefill else 0.0], device=device)
     dist.all_reduce(k_ms, op=dist.ReduceOp.MAX)
     n_launch = torch.tensor([launches], device=device)
     dist.all_reduce(n_launch)
+    payload_all = torch.tensor([float(my_payload)], device=device, dtype=torch.float64)
+    dist.all_reduce(payload_all)
 
-    # ---- verification: prefill gathers what the first tokens of request 0 should hold, decode compares
-    sample = min(64, w.lengths[0])
-    expect = torch.zeros((2, sample, s.num_layers, s.num_kv_heads, s.head_dim), dtype=torch.bfloat16, device=device)
+    # ---- verification: each prefill rank gathers what the first tokens of one request per edge should hold
     ok = torch.ones(1, device=device)
-    for plane in range(w.dst_planes):
-        if is_prefill:
-            pos = torch.arange(sample, device=device)
-            if w.exit_planes is None:
-                sp = torch.full((sample,), plane, device=device)
-            else:
-                e = torch.tensor(np.asarray(w.exit_planes[0][:sample]), device=device)
-                sp = e if args.mode == "exit_only" else torch.clamp(e, max=plane)
-            st = torch.tensor(np.stack(w.src_tables[0]), device=device)
-            sb = st[sp, pos // s.block_size]
-            expect[0] = src.key_cache[sb, :, pos % s.block_size]
-            expect[1] = src.value_cache[sb, :, pos % s.block_size]
-            dist.send(expect, partner)
-        else:
-            dist.recv(expect, partner)
-            pos = torch.arange(sample, device=device)
-            db = torch.tensor(tables[0][plane], device=device)[pos // s.block_size]
-            same = torch.equal(dst.key_cache[db, :, pos % s.block_size].view(torch.int16), expect[0].view(torch.int16)) and \
-                torch.equal(dst.value_cache[db, :, pos % s.block_size].view(torch.int16), expect[1].view(torch.int16))
-            ok *= float(same)
+    store_dtype = torch.uint8 if s.fp8 else torch.int16
+    sample = 48
+    for p in range(n_prefill):
+        for d_rank in exchange.pairing(p, world, n_prefill)[2]:
+            wp = w if (is_prefill and p == rank) else (per_source.get(p) if not is_prefill else None)
+            if rank not in (p, d_rank):
+                continue
+            mine = assigned(p, d_rank, wp)
+            if not mine:
+                continue
+            i = mine[0]
+            n = min(sample, wp.lengths[i])
+            expect = torch.zeros((2, n, s.num_layers, s.num_kv_heads, s.head_dim), dtype=store_dtype, device=device)
+            for plane in range(dst_planes):
+                pos = torch.arange(n, device=device)
+                if rank == p:
+                    if wp.exit_planes is None:
+                        sp = torch.full((n,), plane, device=device)
+                    else:
+                        e = torch.tensor(np.asarray(wp.exit_planes[i][:n]), device=device).long()
+                        sp = e if args.mode == "exit_only" else torch.clamp(e, max=plane)
+                    st = torch.tensor(np.stack([np.asarray(t) for t in wp.src_tables[i]]), device=device).long()
+                    sb = st[sp, pos // s.block_size]
+                    expect[0] = src.key_cache[sb, :, pos % s.block_size].view(store_dtype)
+                    expect[1] = src.value_cache[sb, :, pos % s.block_size].view(store_dtype)
+                    dist.send(expect, d_rank)
+                else:
+                    dist.recv(expect, p)
+                    db = torch.tensor(list(reserved[(p, i)][plane]), device=device)[pos // s.block_size]
+                    same = torch.equal(dst.key_cache[db, :, pos % s.block_size].view(store_dtype), expect[0]) and \
+                        torch.equal(dst.value_cache[db, :, pos % s.block_size].view(store_dtype), expect[1])
+                    ok *= float(same)
     dist.all_reduce(ok, op=dist.ReduceOp.MIN)
 
     # ---- end to end on the prefill side: host tables -> device, launch, flag, status read back
@@ -175,33 +300,90 @@ def run_multi(args, rank: int, world: int) -> None:
         t_start = time.perf_counter()
         counter += 1
         if is_prefill:
-            b = make_batch()
-            kh.kv_handoff(sv, dv, b, mode=mode, status=status, variant=args.variant)
-            kh.kv_signal(flag_ptr, counter)
+            for e in edges:
+                b = e["make_batch"]()
+                kh.kv_handoff(sv, e["dv"], b, mode=mode, status=status, variant=args.variant)
+                kh.kv_signal(e["flag_ptr"], counter)
         else:
-            kh.kv_wait(flag.data_ptr(), counter, kh._lib.MAX_WAIT_NS, status)
+            for slot in range(len(sources)):
+                kh.kv_wait(flags.data_ptr() + 8 * slot, counter, kh._lib.MAX_WAIT_NS, status)
         kh.raise_for_status(status)
         if i >= args.warmup:
             e2e.append(time.perf_counter() - t_start)
     e2e_s = torch.tensor([statistics.mean(e2e)], device=device, dtype=torch.float64)
     dist.all_reduce(e2e_s, op=dist.ReduceOp.MAX)
 
-    # ---- per-request latency on pair 0: launch + flag, observed on the prefill stream
+    # ---- per-request latency on every prefill rank's first edge: launch + flag, on the prefill stream
     lat = []
-    if is_prefill:
-        for r in range(min(len(w.lengths), 32)):
-            one = workloads.subset(w, [r])
-            b = kh.HandoffBatch(one.src_tables, [dst_tables[r]], one.ranges, block_size=s.block_size,
-                                exit_planes=one.exit_planes, device=device)
-            kh.kv_handoff(sv, dv, b, mode=mode, status=status, variant=args.variant)
+    if is_prefill and edges:
+        e = edges[0]
+        for r in range(min(len(e["mine"]), 32)):
+            sub = e["sub"]
+            b = kh.HandoffBatch([sub["src_tables"][r]], [sub["dst_tables"][r]], [sub["ranges"][r]], block_size=s.block_size,
+                                exit_planes=None if sub["exit_planes"] is None else [sub["exit_planes"][r]], device=device)
+            kh.kv_handoff(sv, e["dv"], b, mode=mode, status=status, variant=args.variant)
             a, z = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a.record(stream)
-            kh.kv_handoff(sv, dv, b, mode=mode, status=status, variant=args.variant)
+            kh.kv_handoff(sv, e["dv"], b, mode=mode, status=status, variant=args.variant)
             counter += 1
-            kh.kv_signal(flag_ptr, counter)
+            kh.kv_signal(e["flag_ptr"], counter)
             z.record(stream)
             torch.cuda.synchronize()
             lat.append(a.elapsed_time(z))
+        # keep the decode side's expected counter in step for what follows
+    counter_t = torch.tensor([counter], device=device)
+    dist.all_reduce(counter_t, op=dist.ReduceOp.MAX)
+    counter = int(counter_t.item())
+    if is_prefill:
+        for e in edges:
+            kh.kv_signal(e["flag_ptr"], counter)
+    torch.cuda.synchronize()
+    dist.barrier()
+
+    # ---- streaming replay -------------------------------------------------------------------
+    streaming = None
+    if getattr(args, "streaming", False):
+        tails, fulls, slices = [], [], 0
+        for i in range(2 + args.steps):
+            dist.barrier()
+            torch.cuda.synchronize()
+            out = streaming_step(args.layer_us, args.layers_per_slice)
+            torch.cuda.synchronize()
+            kh.raise_for_status(status)
+            if is_prefill and i >= 2:
+                prefill_end, ends, slices = out
+                tails.append(max(prefill_end.elapsed_time(z) for z in ends))
+        # the same pass without streaming: the handoff starts only when the whole prefill has finished
+        for i in range(2 + args.steps):
+            dist.barrier()
+            torch.cuda.synchronize()
+            counter += 1
+            if is_prefill:
+                torch.cuda._sleep(int(args.layer_us * 1e-6 * 1.9e9) * s.num_layers * dst_planes)
+                a, z = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record(stream)
+                for e in edges:
+                    kh.kv_handoff(sv, e["dv"], e["batch"], mode=mode, status=status, variant=args.variant)
+                    kh.kv_signal(e["flag_ptr"], counter)
+                z.record(stream)
+            else:
+                for slot in range(len(sources)):
+                    kh.kv_wait(flags.data_ptr() + 8 * slot, counter, kh._lib.MAX_WAIT_NS, status)
+            torch.cuda.synchronize()
+            kh.raise_for_status(status)
+            if is_prefill and i >= 2:
+                fulls.append(a.elapsed_time(z))
+        tail = torch.tensor([statistics.median(tails) if tails else 0.0], device=device)
+        full = torch.tensor([statistics.median(fulls) if fulls else 0.0], device=device)
+        dist.all_reduce(tail, op=dist.ReduceOp.MAX)
+        dist.all_reduce(full, op=dist.ReduceOp.MAX)
+        streaming = {
+            "tail_ms_after_prefill_end": float(tail.item()), "unstreamed_ms_after_prefill_end": float(full.item()),
+            "simulated_prefill_ms": args.layer_us * 1e-3 * s.num_layers * dst_planes, "layer_us": args.layer_us,
+            "layers_per_slice": args.layers_per_slice, "slices_per_pass": slices,
+            "what": "max over prefill ranks of the median time from the end of the simulated prefill to the completion flag",
+        }
+
     torch.cuda.synchronize()
     dist.barrier()
     if is_prefill:
@@ -210,27 +392,35 @@ def run_multi(args, rank: int, world: int) -> None:
 
     if rank == 0:
         ms_per_step = float(total_ms.item()) / args.steps
-        total_payload = w.payload_bytes * pairs  # every pair has the same token count distribution parameters
+        total_payload = float(payload_all.item())
         value = total_payload / (ms_per_step * 1e-3) / 1e9
-        per_pair = w.payload_bytes / (float(k_ms.item()) * 1e-3) / 1e9
+        per_gpu = float(egress.item())
+        # the busier side bounds an uneven split: n_prefill egress links feed n_decode ingress links
+        links = min(n_prefill, n_decode)
+        per_link = value / links
         line = {
             "metric": bench.METRIC, "value": value, "unit": bench.UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "u8", "data": "synthetic",
-            "config": bench.config_of(w, args, {"split": f"{pairs}P:{pairs}D", "variant": args.variant,
-                                                "transport": "peer stores over NVLink (CUDA IPC mapping), completion flag per step"}),
-            "roofline": {"bound": "nvlink", "achieved": per_pair, "peak": bench.NVLINK_MEASURED_GBS, "unit": "GB/s",
-                         "frac": per_pair / bench.NVLINK_MEASURED_GBS, "traffic": None,
-                         "peak_source": "measured peer copy on this pool, 770 GB/s per direction (nominal 900)",
+            "config": bench.config_of(w, args, {
+                "split": f"{n_prefill}P:{n_decode}D", "variant": args.variant, "workload_name": getattr(args, "workload", "ouro1p4b"),
+                "per_prefill_worker": w.description, "payload_bytes": total_payload,
+                "transport": "peer stores over NVLink (CUDA IPC mapping), completion flag per step"}),
+            "roofline": {"bound": "nvlink", "achieved": per_link, "peak": bench.NVLINK_MEASURED_GBS, "unit": "GB/s",
+                         "frac": per_link / bench.NVLINK_MEASURED_GBS, "traffic": None,
+                         "peak_source": "measured peer copy on this pool, 770 GB/s per direction per GPU (nominal 900)",
                          "kernel": "table_copy_kernel", "algorithmic_bytes_per_launch": w.payload_bytes,
-                         "kernel_ms": float(k_ms.item()), "frac_of_nominal_900": per_pair / 900.0},
-            "per_pair_gbps": per_pair,
+                         "kernel_ms": float(k_ms.item()), "frac_of_nominal_900": per_link / 900.0,
+                         "what": "aggregate payload rate / min(prefill, decode) GPUs: the per-GPU link rate of the busier side"},
+            "per_pair_gbps": per_link, "slowest_prefill_gpu_egress_gbps": per_gpu,
             "e2e": {"value": total_payload / float(e2e_s.item()) / 1e9, "unit": bench.UNIT,
-                    "h2d_bytes_per_step": batch.metadata_bytes, "d2h_bytes_per_step": 16,
+                    "h2d_bytes_per_step": sum(e["batch"].metadata_bytes for e in edges), "d2h_bytes_per_step": 16,
                     "ms_per_step": float(e2e_s.item()) * 1e3},
             "latency_ms": {"p50": statistics.median(lat), "max": max(lat), "min": min(lat),
-                           "what": "pair 0, one launch + completion flag per request, CUDA events on the prefill stream"},
+                           "what": "rank 0, one launch + completion flag per request, CUDA events on the prefill stream"},
             "gpu_launches": int(n_launch.item()), "clocks": clocks, "verified": bool(ok.item() == 1.0),
         }
+        if streaming:
+            line["streaming"] = streaming
         print(json.dumps(line), flush=True)
     dist.destroy_process_group()

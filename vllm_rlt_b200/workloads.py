@@ -173,6 +173,34 @@ def per_depth_all_planes(
     )
 
 
+def recurrent_depth_dedup(
+    shape: KVShape = HUGINN_3P5B, *, requests: int = 2, min_len: int = 1024, max_len: int = 16384,
+    min_exit: int = 4, p_exit: float = 0.1, seed: int = SEED_BASE + 3,
+) -> Workload:
+    """Recurrent-depth model: per-token exit recurrence geometric(p) truncated to [min_exit, planes], dedup mode.
+
+    A token that exits at recurrence e holds distinct KV in planes 0..e-1; deeper planes are copies, so
+    the dedup handoff reads each distinct row once and rebuilds the copies on the destination.
+    """
+    rng = random.Random(seed)
+    lengths = [rng.randint(min_len, max_len) for _ in range(requests)]
+    src_tables, src_blocks = _tables(rng, lengths, shape.planes, shape.block_size)
+    dst_tables, dst_blocks = _tables(rng, lengths, shape.planes, shape.block_size)
+    exits = []
+    for n in lengths:
+        draws = np.array([min(shape.planes, max(min_exit, int(math.log(1.0 - rng.random()) / math.log(1.0 - p_exit)) + 1))
+                          for _ in range(n)], np.int32)
+        exits.append(draws - 1)  # zero-based exit plane
+    return Workload(
+        shape, lengths, [(0, n) for n in lengths], src_tables, dst_tables, exits, src_blocks, dst_blocks, shape.planes,
+        description=(
+            f"{shape.name} recurrent-depth dedup: {requests} requests, lengths U[{min_len},{max_len}], exit recurrence "
+            f"geometric(p={p_exit}) truncated to [{min_exit},{shape.planes}], block {shape.block_size}, seeded random block tables"
+        ),
+        extra=dict(mode="dedup"),
+    )
+
+
 def subset(w: Workload, indices) -> Workload:
     """The same workload restricted to some of its requests (tables keep their block ids)."""
     idx = list(indices)
