@@ -28,22 +28,29 @@ import numpy as np
 MODES = {"exit_only": 2, "dedup": 1, "all": 0}
 
 
-def make_workload(args, prefill_index: int):
-    """The workload of one prefill worker; every rank can rebuild any worker's from its index."""
+def make_workload(args, prefill_index: int, lengths=None):
+    """The workload of one prefill worker; every rank can rebuild any worker's from its index.
+
+    All workers get the same prompt lengths (those of worker 0), so that per-GPU work is identical at
+    every N (weak scaling); block tables and exit planes are seeded per worker.
+    """
     from vllm_rlt_b200 import workloads as wl
 
+    if lengths is None and prefill_index != 0:
+        lengths = make_workload(args, 0).lengths
     seed = wl.SEED_BASE + 1 + 17 * prefill_index
     name = getattr(args, "workload", "ouro1p4b")
     if name == "ouro1p4b":
-        return wl.last_exited_exit_only(wl.OURO_1P4B, requests=args.requests, mode=args.mode, seed=seed)
+        return wl.last_exited_exit_only(wl.OURO_1P4B, requests=args.requests, mode=args.mode, seed=seed, lengths=lengths)
     if name == "ouro2p6b":
-        return wl.last_exited_exit_only(wl.OURO_2P6B, requests=args.requests, mode=args.mode, seed=seed)
+        return wl.last_exited_exit_only(wl.OURO_2P6B, requests=args.requests, mode=args.mode, seed=seed, lengths=lengths)
     if name == "ouro2p6b_fp8_shared":
         # FP8 e4m3 with travelling float32 scales; "SHARED for loops >= 2" = two planes (loop 1, loops 2..4)
         shape = wl.KVShape("ouro-2.6b-fp8 planes[0,1,1,1]", 48, 16, 128, 2, fp8=True)
-        return wl.per_depth_all_planes(shape, requests=args.requests, min_len=1024, max_len=8192, seed=seed, log_uniform=True)
+        return wl.per_depth_all_planes(shape, requests=args.requests, min_len=1024, max_len=8192, seed=seed,
+                                       log_uniform=True, lengths=lengths)
     if name == "huginn":
-        return wl.recurrent_depth_dedup(wl.HUGINN_3P5B, requests=args.requests, seed=seed)
+        return wl.recurrent_depth_dedup(wl.HUGINN_3P5B, requests=args.requests, seed=seed, lengths=lengths)
     if name == "ouro2p6b_chunk":
         # one 2048-token prefill chunk per request, all planes (what a WCPB step finishes)
         return wl.per_depth_all_planes(wl.OURO_2P6B, requests=args.requests, min_len=2048, max_len=2048, seed=seed)
@@ -258,7 +265,7 @@ def run_multi(args, rank: int, world: int) -> None:
 
     # ---- verification: each prefill rank gathers what the first tokens of one request per edge should hold
     ok = torch.ones(1, device=device)
-    store_dtype = torch.uint8 if s.fp8 else torch.int16
+    store_dtype = torch.uint8  # compare raw bytes (NCCL carries uint8)
     sample = 48
     for p in range(n_prefill):
         for d_rank in exchange.pairing(p, world, n_prefill)[2]:
@@ -270,7 +277,7 @@ def run_multi(args, rank: int, world: int) -> None:
                 continue
             i = mine[0]
             n = min(sample, wp.lengths[i])
-            expect = torch.zeros((2, n, s.num_layers, s.num_kv_heads, s.head_dim), dtype=store_dtype, device=device)
+            expect = torch.zeros((2, n, s.num_layers, s.num_kv_heads, s.head_dim * s.element), dtype=store_dtype, device=device)
             for plane in range(dst_planes):
                 pos = torch.arange(n, device=device)
                 if rank == p:

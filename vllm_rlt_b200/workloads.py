@@ -152,11 +152,13 @@ def last_exited_exit_only(
 
 def per_depth_all_planes(
     shape: KVShape = OURO_1P4B, *, requests: int = 8, min_len: int = 128, max_len: int = 1024,
-    seed: int = SEED_BASE, log_uniform: bool = False,
+    seed: int = SEED_BASE, log_uniform: bool = False, lengths: list[int] | None = None,
 ) -> Workload:
     """The reference's own case: every plane of every prompt token is sent."""
     rng = random.Random(seed)
-    if log_uniform:
+    if lengths is not None:
+        lengths, requests = list(lengths), len(lengths)
+    elif log_uniform:
         lengths = [int(round(math.exp(rng.uniform(math.log(min_len), math.log(max_len))))) for _ in range(requests)]
     else:
         lengths = [rng.randint(min_len, max_len) for _ in range(requests)]
@@ -175,7 +177,7 @@ def per_depth_all_planes(
 
 def recurrent_depth_dedup(
     shape: KVShape = HUGINN_3P5B, *, requests: int = 2, min_len: int = 1024, max_len: int = 16384,
-    min_exit: int = 4, p_exit: float = 0.1, seed: int = SEED_BASE + 3,
+    min_exit: int = 4, p_exit: float = 0.1, seed: int = SEED_BASE + 3, lengths: list[int] | None = None,
 ) -> Workload:
     """Recurrent-depth model: per-token exit recurrence geometric(p) truncated to [min_exit, planes], dedup mode.
 
@@ -183,7 +185,10 @@ def recurrent_depth_dedup(
     the dedup handoff reads each distinct row once and rebuilds the copies on the destination.
     """
     rng = random.Random(seed)
-    lengths = [rng.randint(min_len, max_len) for _ in range(requests)]
+    if lengths is None:
+        lengths = [rng.randint(min_len, max_len) for _ in range(requests)]
+    else:
+        lengths, requests = list(lengths), len(lengths)
     src_tables, src_blocks = _tables(rng, lengths, shape.planes, shape.block_size)
     dst_tables, dst_blocks = _tables(rng, lengths, shape.planes, shape.block_size)
     exits = []
