@@ -334,13 +334,15 @@ def run_single(args):
 
     device = torch.device("cuda", 0)
     torch.cuda.set_device(device)
-    w = workloads.last_exited_exit_only(requests=args.requests, mode=args.mode)
+    from vllm_rlt_b200.pd.harness import make_workload
+
+    w = make_workload(args, 0)
     need = (w.src_blocks + w.dst_blocks) * w.shape.block_bytes
     free, _ = torch.cuda.mem_get_info()
     if need + (6 << 30) > free:
         raise SystemExit(f"workload needs {need / 2**30:.1f} GiB of pools but only {free / 2**30:.1f} GiB are free")
     src, dst = build_device_side(w, device, workloads.SEED_BASE + 1)
-    mode = {"exit_only": kh.MODE_EXIT_ONLY, "dedup": kh.MODE_DEDUP, "all": kh.MODE_ALL_PLANES}[args.mode]
+    mode = {"exit_only": kh.MODE_EXIT_ONLY, "dedup": kh.MODE_DEDUP, "all": kh.MODE_ALL_PLANES}[w.extra.get("mode", args.mode)]
     sv, dv = kh.PoolView.from_cache(src), kh.PoolView.from_cache(dst)
     status = kh.new_status(device)
 
@@ -414,6 +416,21 @@ def run_single(args):
         lat.append(a.elapsed_time(z))
     kh.raise_for_status(status)
 
+    # the streaming tail of one request: what is left to send after its last layer (one layer slice)
+    tail = []
+    one = workloads.subset(w, [0])
+    b = kh.HandoffBatch(one.src_tables, one.dst_tables, one.ranges, block_size=w.shape.block_size,
+                        exit_planes=one.exit_planes, device=device)
+    last = w.shape.num_layers - 1
+    for _ in range(12):
+        a, z = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(stream)
+        kh.kv_handoff(sv, dv, b, mode=mode, layer_begin=last, layer_end=last + 1, status=status, variant=args.variant)
+        z.record(stream)
+        torch.cuda.synchronize()
+        tail.append(a.elapsed_time(z))
+    kh.raise_for_status(status)
+
     cpu = None if args.no_cpu_baseline else cpu_baseline_sample(w, max_tokens=args.cpu_tokens)
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
@@ -426,7 +443,9 @@ def run_single(args):
                 "d2h_bytes_per_step": 16, "ms_per_step": statistics.mean(e2e_times) * 1e3,
                 "note": "KV pools are device-resident by the API's nature; host inputs are tables, ranges and exit planes"},
         "latency_ms": {"p50": statistics.median(lat), "max": max(lat), "min": min(lat),
-                       "what": "one launch per request, CUDA events, intra-device"},
+                       "what": "one launch per request, CUDA events, intra-device",
+                       "last_layer_slice_p50": statistics.median(tail),
+                       "tokens_p50": statistics.median(w.lengths)},
         "gpu_launches": launches, "clocks": clocks, "verified": verified,
     }
     if cpu is not None:
@@ -447,7 +466,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--prefill", type=int, default=0, help="prefill ranks at N >= 2 (default N/2)")
     ap.add_argument("--workload", default="ouro1p4b",
-                    choices=["ouro1p4b", "ouro2p6b", "ouro2p6b_fp8_shared", "huginn", "ouro2p6b_chunk"])
+                    choices=["ouro1p4b", "ouro2p6b", "ouro2p6b_fp8_shared", "huginn", "ouro2p6b_chunk", "ouro2p6b_4k",
+                             "ouro2p6b_fp8_4k"])
     ap.add_argument("--streaming", action="store_true", help="also replay a layer-by-layer prefill and stream behind it")
     ap.add_argument("--layer-us", type=float, default=200.0, help="simulated prefill time per layer and depth")
     ap.add_argument("--layers-per-slice", type=int, default=4)

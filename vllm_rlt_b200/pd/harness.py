@@ -49,6 +49,18 @@ def make_workload(args, prefill_index: int, lengths=None):
         shape = wl.KVShape("ouro-2.6b-fp8 planes[0,1,1,1]", 48, 16, 128, 2, fp8=True)
         return wl.per_depth_all_planes(shape, requests=args.requests, min_len=1024, max_len=8192, seed=seed,
                                        log_uniform=True, lengths=lengths)
+    if name == "ouro2p6b_4k":
+        # per-request latency probe: 4096-token Ouro-2.6B-shaped prompts
+        if args.mode == "all":
+            return wl.per_depth_all_planes(wl.OURO_2P6B, requests=args.requests, min_len=4096, max_len=4096, seed=seed)
+        return wl.last_exited_exit_only(wl.OURO_2P6B, requests=args.requests, min_len=4096, max_len=4096,
+                                        partial_fraction=0.0, mode=args.mode, seed=seed)
+    if name == "ouro2p6b_fp8_4k":
+        shape = wl.OURO_2P6B_FP8 if args.mode != "all" else wl.KVShape("ouro-2.6b-fp8 single plane", 48, 16, 128, 1, fp8=True)
+        if args.mode == "all":
+            return wl.per_depth_all_planes(shape, requests=args.requests, min_len=4096, max_len=4096, seed=seed)
+        return wl.last_exited_exit_only(shape, requests=args.requests, min_len=4096, max_len=4096, partial_fraction=0.0,
+                                        mode=args.mode, seed=seed)
     if name == "huginn":
         return wl.recurrent_depth_dedup(wl.HUGINN_3P5B, requests=args.requests, seed=seed, lengths=lengths)
     if name == "ouro2p6b_chunk":
