@@ -263,6 +263,31 @@ RLT_API int rlt_kv_finalize(const RltPool* pool, const int32_t* tables, int32_t 
                             const int32_t* rows, int32_t count, uint64_t layer_mask, int32_t* status,
                             rlt_stream_t stream);
 
+/* --- typed tensor transfer ------------------------------------------------------------------- */
+
+enum { RLT_DTYPE_I32 = 0, RLT_DTYPE_I64 = 1, RLT_DTYPE_F16 = 2, RLT_DTYPE_BF16 = 3, RLT_DTYPE_F32 = 4 };
+
+/*
+ * A batch of strided 2-D copies with element conversion. descriptors is an
+ * int64[count][8] table readable from the device (device memory or mapped pinned
+ * host memory): source address, destination address, rows, cols, source row and
+ * column stride, destination row and column stride, strides in elements.
+ * max_rows / max_cols bound the largest copy of the batch. Sources may be mapped
+ * host memory; destinations are on the current device. Replaces the segmented mode
+ * of tensor_transfer_kernel and TensorTransfer.submit
+ * (vllm_rlt/kernels/tensor_transfer.py:21-35, vllm_rlt/worker/tensors.py:321-365).
+ */
+RLT_API int rlt_tensor_transfer(const int64_t* descriptors, int32_t count, int32_t max_rows, int32_t max_cols,
+                                int32_t src_dtype, int32_t dst_dtype, rlt_stream_t stream);
+
+/*
+ * Flat copy of count elements with conversion, optionally writing a second output
+ * of its own type from the same source values (secondary may be NULL). Replaces
+ * copy_tensor's kernel path (vllm_rlt/worker/tensors.py:35-87).
+ */
+RLT_API int rlt_tensor_copy(const void* src, void* dst, void* secondary, int64_t count, int32_t src_dtype,
+                            int32_t dst_dtype, int32_t secondary_dtype, rlt_stream_t stream);
+
 /* --- completion ----------------------------------------------------------------------------- */
 
 /*

@@ -82,3 +82,27 @@ def test_table_codec_round_trip_and_errors():
         exchange.encode_tables(tables, 3, 3)
     with pytest.raises(ValueError):
         exchange.encode_tables(tables, 2, 2)
+
+
+def _lonely(rank, port, out):
+    import datetime
+
+    import torch.distributed as dist
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    try:
+        dist.init_process_group("gloo", rank=rank, world_size=2, timeout=datetime.timedelta(seconds=3))
+        out.put("joined")
+    except Exception as exc:
+        out.put(type(exc).__name__)
+
+
+def test_a_worker_that_never_joins_ends_the_exchange_with_an_error_not_a_hang():
+    """Failure injection on the host: the peer of a two-rank exchange is simply never started."""
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    proc = ctx.Process(target=_lonely, args=(0, _free_port(), out))
+    proc.start()
+    got = out.get(timeout=90)
+    proc.join(timeout=30)
+    assert got != "joined"

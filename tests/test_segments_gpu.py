@@ -161,3 +161,61 @@ def test_torch_ops_match_the_c_abi_path():
     with pytest.raises(RuntimeError, match="contiguous"):
         ops.kv_handoff(gp.key_cache.transpose(0, 1), gp.value_cache, None, None, gd.key_cache, gd.value_cache,
                        None, None, st, dt, begin, end, None, None, 0, 0, 0, None)
+
+
+def test_torch_ops_for_slices_dedup_wire_and_finalize():
+    """The remaining ops: each must equal its ctypes twin on the same inputs."""
+    from vllm_rlt_b200 import _build
+
+    torch.ops.load_library(str(_build.PACKAGE / _build.OPS_NAME))
+    ops, k = torch.ops.vllm_rlt, kh()
+    case = golden_json("finalize.json")[1]  # fp8 with travelling scales, per-token exit planes
+    arrays = golden_npz(case["name"])
+    shape = case["shape"]
+    P = oracle_pool(case["kind"], shape)
+    load_pool(P, arrays, "src_before_")
+    gp = GpuPool(P)
+    reqs = case["requests"]
+    planes, page = shape[5], shape[4]
+    width = max(len(t) for r in reqs for t in r["src_tables"])
+
+    def table_tensor(key):
+        a = np.zeros((len(reqs), planes, width), np.int32)
+        for i, r in enumerate(reqs):
+            for p, t in enumerate(r[key]):
+                a[i, p, : len(t)] = t
+        return torch.from_numpy(a).cuda()
+
+    st, dt = table_tensor("src_tables"), table_tensor("dst_tables")
+    begin = torch.zeros(len(reqs), dtype=torch.int32, device="cuda")
+    end = torch.tensor([r["tokens"] for r in reqs], dtype=torch.int32, device="cuda")
+    exits = torch.tensor([e for r in reqs for e in r["exit_planes"]], dtype=torch.int32, device="cuda")
+    offs = torch.tensor(np.cumsum([0] + [r["tokens"] for r in reqs])[:-1], dtype=torch.int64, device="cuda")
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    rows = torch.tensor([(i, e, pos) for i, r in enumerate(reqs) for pos, e in enumerate(r["exit_planes"])],
+                        dtype=torch.int32, device="cuda")
+    ops.kv_finalize(gp.key_cache, gp.value_cache, gp.key_scale, gp.value_scale, st, rows, 0, status)
+    load_pool(P, arrays, "src_after_")
+    assert_pools_equal(gp, P)
+    # dedup wire through the ops, then the replicating scatter
+    batch = k.HandoffBatch([r["src_tables"] for r in reqs], [r["dst_tables"] for r in reqs],
+                           [(0, r["tokens"]) for r in reqs], block_size=page, exit_planes=[r["exit_planes"] for r in reqs])
+    ws = k.dedup_workspace(batch, planes)
+    want = np.concatenate([ho.pack_rows(P, r["src_tables"], 0, r["tokens"], mode=ho.MODE_DEDUP, exit_planes=r["exit_planes"]) for r in reqs])
+    packed = torch.zeros(want.size, dtype=torch.uint8, device="cuda")
+    ops.kv_pack_dedup(gp.key_cache, gp.value_cache, gp.key_scale, gp.value_scale, st, begin, end, exits, offs, 0, 0, packed, ws, status)
+    assert np.array_equal(packed.cpu().numpy(), want)
+    D = oracle_pool(case["kind"], shape, device=1, base=1 << 40)
+    D.fill_sentinel()
+    gd, gd2 = GpuPool(D), GpuPool(D)
+    ops.kv_scatter_dedup(packed, dt, begin, end, exits, offs, 0, 0, gd.key_cache, gd.value_cache, gd.key_scale, gd.value_scale, ws, status)
+    load_pool(D, arrays, "dst_after_")
+    assert_pools_equal(gd, D)
+    # plane/layer slices tile the handoff
+    layers = shape[0]
+    for p0, p1 in ((0, 2), (2, planes)):
+        for l0, l1 in ((0, 1), (1, layers)):
+            ops.kv_handoff_slice(gp.key_cache, gp.value_cache, gp.key_scale, gp.value_scale, gd2.key_cache, gd2.value_cache,
+                                 gd2.key_scale, gd2.value_scale, st, dt, begin, end, None, None, 0, l0, l1, p0, p1, status)
+    assert_pools_equal(gd2, D)
+    assert status.tolist() == [0, 0, 0, 0]

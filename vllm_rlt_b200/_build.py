@@ -21,7 +21,8 @@ INCLUDE = ROOT / "include"
 LIB_NAME = "librlt_kv_handoff.so"
 OPS_NAME = "_C.so"
 
-CUDA_SOURCES = ["lib.cu", "kv_table_copy.cu", "kv_segment_copy.cu", "kv_finalize.cu", "kv_signal.cu", "peer.cu"]
+CUDA_SOURCES = ["lib.cu", "kv_table_copy.cu", "kv_segment_copy.cu", "kv_finalize.cu", "tensor_transfer.cu",
+                "kv_signal.cu", "peer.cu"]
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 
 

@@ -88,6 +88,8 @@ SIGNATURES = {
     "rlt_kv_static_plan_entries": (C.c_int64, []),
     "rlt_kv_scatter": (C.c_int, [C.c_void_p, C.c_int64, C.POINTER(RltPool), C.POINTER(RltBatch), C.POINTER(RltOptions), C.c_void_p]),
     "rlt_kv_finalize": (C.c_int, [C.POINTER(RltPool), C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_int32, C.c_uint64, C.c_void_p, C.c_void_p]),
+    "rlt_tensor_transfer": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p]),
+    "rlt_tensor_copy": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_void_p]),
     "rlt_kv_push": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p]),
     "rlt_kv_copy_segments": (C.c_int, [C.c_void_p, C.c_int32, C.c_void_p]),
     "rlt_kv_signal": (C.c_int, [C.c_void_p, C.c_uint64, C.c_void_p]),

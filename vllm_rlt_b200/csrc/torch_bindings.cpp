@@ -196,6 +196,80 @@ void kv_scatter_cuda(const at::Tensor& packed, const at::Tensor& tables, const a
   check_rc(rlt_kv_scatter(packed.data_ptr(), packed.numel(), &dst, &b.batch, &o, current_stream(device)), "kv_scatter");
 }
 
+void kv_handoff_slice_cuda(const at::Tensor& src_key, const at::Tensor& src_value, const OptTensor& src_key_scale,
+                           const OptTensor& src_value_scale, at::Tensor& dst_key, at::Tensor& dst_value,
+                           const OptTensor& dst_key_scale, const OptTensor& dst_value_scale, const at::Tensor& src_tables,
+                           const at::Tensor& dst_tables, const at::Tensor& tok_begin, const at::Tensor& tok_end,
+                           const OptTensor& exit_planes, const OptTensor& exit_offsets, int64_t mode, int64_t layer_begin,
+                           int64_t layer_end, int64_t plane_begin, int64_t plane_end, const OptTensor& status) {
+  const at::Device device = src_key.device();
+  const c10::cuda::CUDAGuard guard(device);
+  BatchArgs b = batch_of(&src_tables, &dst_tables, tok_begin, tok_end, exit_planes, exit_offsets, device);
+  const RltPool src = pool_of(src_key, src_value, src_key_scale, src_value_scale, b.src_planes);
+  const RltPool dst = pool_of(dst_key, dst_value, dst_key_scale, dst_value_scale, b.dst_planes);
+  RltOptions o = options_of(mode, layer_begin, layer_end, status_ptr(status, device));
+  o.plane_begin = static_cast<int32_t>(plane_begin);
+  o.plane_end = static_cast<int32_t>(plane_end);
+  check_rc(rlt_kv_handoff(&src, &dst, &b.batch, &o, current_stream(device)), "kv_handoff_slice");
+}
+
+namespace {
+
+void attach_workspace(RltOptions& o, at::Tensor& workspace, const at::Device& device) {
+  TORCH_CHECK(workspace.device() == device && workspace.scalar_type() == at::kByte && workspace.is_contiguous(),
+              "workspace must be a contiguous uint8 tensor on the pool's device");
+  o.workspace = workspace.data_ptr();
+  o.workspace_bytes = workspace.numel();
+}
+
+}  // namespace
+
+void kv_pack_dedup_cuda(const at::Tensor& key, const at::Tensor& value, const OptTensor& key_scale,
+                        const OptTensor& value_scale, const at::Tensor& tables, const at::Tensor& tok_begin,
+                        const at::Tensor& tok_end, const at::Tensor& exit_planes, const at::Tensor& exit_offsets,
+                        int64_t layer_begin, int64_t layer_end, at::Tensor& out, at::Tensor& workspace,
+                        const OptTensor& status) {
+  const at::Device device = key.device();
+  const c10::cuda::CUDAGuard guard(device);
+  BatchArgs b = batch_of(&tables, nullptr, tok_begin, tok_end, exit_planes, exit_offsets, device);
+  const RltPool src = pool_of(key, value, key_scale, value_scale, b.src_planes);
+  TORCH_CHECK(out.device() == device && out.scalar_type() == at::kByte && out.is_contiguous(),
+              "packed buffer must be a contiguous uint8 tensor on the pool's device");
+  RltOptions o = options_of(RLT_MODE_DEDUP, layer_begin, layer_end, status_ptr(status, device));
+  attach_workspace(o, workspace, device);
+  check_rc(rlt_kv_pack(&src, &b.batch, &o, out.data_ptr(), out.numel(), current_stream(device)), "kv_pack_dedup");
+}
+
+void kv_scatter_dedup_cuda(const at::Tensor& packed, const at::Tensor& tables, const at::Tensor& tok_begin,
+                           const at::Tensor& tok_end, const at::Tensor& exit_planes, const at::Tensor& exit_offsets,
+                           int64_t layer_begin, int64_t layer_end, at::Tensor& key, at::Tensor& value,
+                           const OptTensor& key_scale, const OptTensor& value_scale, at::Tensor& workspace,
+                           const OptTensor& status) {
+  const at::Device device = key.device();
+  const c10::cuda::CUDAGuard guard(device);
+  BatchArgs b = batch_of(nullptr, &tables, tok_begin, tok_end, exit_planes, exit_offsets, device);
+  const RltPool dst = pool_of(key, value, key_scale, value_scale, b.dst_planes);
+  TORCH_CHECK(packed.device() == device && packed.scalar_type() == at::kByte && packed.is_contiguous(),
+              "packed buffer must be a contiguous uint8 tensor on the pool's device");
+  RltOptions o = options_of(RLT_MODE_DEDUP, layer_begin, layer_end, status_ptr(status, device));
+  attach_workspace(o, workspace, device);
+  check_rc(rlt_kv_scatter(packed.data_ptr(), packed.numel(), &dst, &b.batch, &o, current_stream(device)), "kv_scatter_dedup");
+}
+
+void kv_finalize_cuda(at::Tensor& key, at::Tensor& value, const OptTensor& key_scale, const OptTensor& value_scale,
+                      const at::Tensor& tables, const at::Tensor& rows, int64_t layer_mask, const OptTensor& status) {
+  const at::Device device = key.device();
+  const c10::cuda::CUDAGuard guard(device);
+  TORCH_CHECK(tables.dim() == 3, "tables must be [requests, planes, pages]");
+  TORCH_CHECK(rows.dim() == 2 && rows.size(1) == 3, "rows must be [n, 3]: request index, exit plane, token position");
+  const RltPool pool = pool_of(key, value, key_scale, value_scale, tables.size(1));
+  check_rc(rlt_kv_finalize(&pool, i32(tables, device, "tables"), static_cast<int32_t>(tables.size(0)),
+                           static_cast<int32_t>(tables.size(2)), i32(rows, device, "rows"),
+                           static_cast<int32_t>(rows.size(0)), static_cast<uint64_t>(layer_mask),
+                           status_ptr(status, device), current_stream(device)),
+           "kv_finalize");
+}
+
 void kv_push_cuda(const at::Tensor& src, int64_t dst_ptr, int64_t nbytes) {
   TORCH_CHECK(src.is_cuda() && src.is_contiguous(), "kv_push source must be a contiguous CUDA tensor");
   TORCH_CHECK(nbytes >= 0 && nbytes <= static_cast<int64_t>(src.nbytes()), "kv_push size exceeds the source tensor");
@@ -250,6 +324,23 @@ TORCH_LIBRARY_FRAGMENT(vllm_rlt, ops) {
   ops.def(
       "kv_scatter(Tensor packed, Tensor tables, Tensor tok_begin, Tensor tok_end, int layer_begin, int layer_end, "
       "Tensor(a!) key, Tensor(b!) value, Tensor(c!)? key_scale, Tensor(d!)? value_scale, Tensor(e!)? status) -> ()");
+  ops.def(
+      "kv_handoff_slice(Tensor src_key, Tensor src_value, Tensor? src_key_scale, Tensor? src_value_scale, "
+      "Tensor(a!) dst_key, Tensor(b!) dst_value, Tensor(c!)? dst_key_scale, Tensor(d!)? dst_value_scale, "
+      "Tensor src_tables, Tensor dst_tables, Tensor tok_begin, Tensor tok_end, Tensor? exit_planes, "
+      "Tensor? exit_offsets, int mode, int layer_begin, int layer_end, int plane_begin, int plane_end, "
+      "Tensor(e!)? status) -> ()");
+  ops.def(
+      "kv_pack_dedup(Tensor key, Tensor value, Tensor? key_scale, Tensor? value_scale, Tensor tables, "
+      "Tensor tok_begin, Tensor tok_end, Tensor exit_planes, Tensor exit_offsets, int layer_begin, int layer_end, "
+      "Tensor(a!) out, Tensor(b!) workspace, Tensor(c!)? status) -> ()");
+  ops.def(
+      "kv_scatter_dedup(Tensor packed, Tensor tables, Tensor tok_begin, Tensor tok_end, Tensor exit_planes, "
+      "Tensor exit_offsets, int layer_begin, int layer_end, Tensor(a!) key, Tensor(b!) value, Tensor(c!)? key_scale, "
+      "Tensor(d!)? value_scale, Tensor(e!) workspace, Tensor(f!)? status) -> ()");
+  ops.def(
+      "kv_finalize(Tensor(a!) key, Tensor(b!) value, Tensor(c!)? key_scale, Tensor(d!)? value_scale, Tensor tables, "
+      "Tensor rows, int layer_mask, Tensor(e!)? status) -> ()");
   ops.def("kv_push(Tensor src, int dst_ptr, int nbytes) -> ()");
   ops.def("kv_copy_segments(Tensor segments) -> ()");
   ops.def("kv_signal(Tensor anchor, int flag_ptr, int value) -> ()");
@@ -261,6 +352,10 @@ TORCH_LIBRARY_IMPL(vllm_rlt, CUDA, ops) {
   ops.impl("kv_handoff_peer", &vllm_rlt_b200::kv_handoff_peer_cuda);
   ops.impl("kv_pack", &vllm_rlt_b200::kv_pack_cuda);
   ops.impl("kv_scatter", &vllm_rlt_b200::kv_scatter_cuda);
+  ops.impl("kv_handoff_slice", &vllm_rlt_b200::kv_handoff_slice_cuda);
+  ops.impl("kv_pack_dedup", &vllm_rlt_b200::kv_pack_dedup_cuda);
+  ops.impl("kv_scatter_dedup", &vllm_rlt_b200::kv_scatter_dedup_cuda);
+  ops.impl("kv_finalize", &vllm_rlt_b200::kv_finalize_cuda);
   ops.impl("kv_push", &vllm_rlt_b200::kv_push_cuda);
   ops.impl("kv_copy_segments", &vllm_rlt_b200::kv_copy_segments_cuda);
   ops.impl("kv_signal", &vllm_rlt_b200::kv_signal_cuda);
