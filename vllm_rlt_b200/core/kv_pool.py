@@ -30,6 +30,22 @@ class _Allocation:
     release_requested: bool = False
 
 
+@dataclass
+class KVSnapshot:
+    """Host copy of one request's pages; same fields and layout as the reference's ``KVSnapshot``
+    (vllm_rlt/core/kv_cache_manager.py:143-166): every page of every plane in block-table order,
+    ``[pages * planes, layer, token, kv_head, dim]``, in pinned host memory."""
+
+    max_tokens: int
+    pages: int
+    written: tuple
+    keys: torch.Tensor
+    values: torch.Tensor
+    key_scales: torch.Tensor | None = None
+    value_scales: torch.Tensor | None = None
+    fp8_scale: float | None = None
+
+
 class KVPool:
     def __init__(
         self,
@@ -163,3 +179,69 @@ class KVPool:
 
     def poll_prefixes(self) -> None:  # the connector calls this every progress(); nothing to do here
         return None
+
+    # -- preemption snapshots ------------------------------------------------------------------
+
+    def _block_copies(self, blocks, pairs, to_host: bool):
+        """(source address, destination address, bytes) of every (tensor, block) of a snapshot."""
+        out = []
+        for pool_t, host_t in pairs:
+            size = pool_t.stride(0) * pool_t.element_size()
+            base, host = pool_t.data_ptr(), host_t.data_ptr()
+            for row, block in enumerate(blocks):
+                a, b = base + block * size, host + row * size
+                out.append((a, b, size) if to_host else (b, a, size))
+        return out
+
+    def _run_copies(self, triples) -> None:
+        from ..kernels import kv_handoff as kh
+
+        with torch.cuda.device(self.device):
+            for at in range(0, len(triples), kh._lib.MAX_SEGMENTS):
+                table = torch.tensor(triples[at : at + kh._lib.MAX_SEGMENTS], dtype=torch.int64).pin_memory()
+                kh.kv_copy_segments(table.to(self.device, non_blocking=True))
+
+    def snapshot(self, request_id: str) -> KVSnapshot:
+        """Copy a request's pages to pinned host memory with one segment-copy launch per 4096 pages.
+
+        Same contract as ``KVCacheManager.snapshot`` (vllm_rlt/core/kv_cache_manager.py:625-656): refused
+        while the allocation is leased to a transfer; the kernels write straight into the host tensors, so
+        no request-sized temporary is taken on a device that may be full. Synchronises before returning.
+        """
+        a = self._get(request_id)
+        if a.transfer_leases:
+            raise RuntimeError("cannot snapshot KV during a transfer")
+        blocks = [b for table in a.block_tables for b in table]
+        keys = torch.empty((len(blocks), *self.key_cache.shape[1:]), dtype=self.key_cache.dtype, pin_memory=True)
+        values = torch.empty_like(keys, pin_memory=True)
+        pairs = [(self.key_cache, keys), (self.value_cache, values)]
+        key_scales = value_scales = None
+        if self.key_scale is not None:
+            key_scales = torch.empty((len(blocks), *self.key_scale.shape[1:]), dtype=torch.float32, pin_memory=True)
+            value_scales = torch.empty_like(key_scales, pin_memory=True)
+            pairs += [(self.key_scale, key_scales), (self.value_scale, value_scales)]
+        self._run_copies(self._block_copies(blocks, pairs, to_host=True))
+        torch.cuda.synchronize(self.device)
+        return KVSnapshot(a.max_tokens, len(a.block_tables[0]), (a.imported, a.prefix), keys, values, key_scales,
+                          value_scales, self.fp8_scale)
+
+    def restore(self, request_id: str, snapshot: KVSnapshot) -> None:
+        """Load a snapshot into a fresh allocation of the same size, on the current stream
+        (``KVCacheManager.restore``, vllm_rlt/core/kv_cache_manager.py:658-681; same checks and messages)."""
+        a = self._get(request_id)
+        if a.max_tokens != snapshot.max_tokens:
+            raise ValueError("snapshot capacity does not match the allocation")
+        if len(a.block_tables[0]) != snapshot.pages:
+            raise ValueError("snapshot page count does not match the allocation")
+        if a.imported is not None or a.prefix:
+            raise RuntimeError("cannot restore into an allocation that already holds KV")
+        if (self.key_scale is None) != (snapshot.key_scales is None):
+            raise ValueError("snapshot KV dtype does not match the pool")
+        if self.fp8_scale != snapshot.fp8_scale:
+            raise ValueError("snapshot FP8 scale policy does not match the pool")
+        blocks = [b for table in a.block_tables for b in table]
+        pairs = [(self.key_cache, snapshot.keys), (self.value_cache, snapshot.values)]
+        if self.key_scale is not None:
+            pairs += [(self.key_scale, snapshot.key_scales), (self.value_scale, snapshot.value_scales)]
+        self._run_copies(self._block_copies(blocks, pairs, to_host=False))
+        a.imported, a.prefix = snapshot.written
