@@ -33,22 +33,23 @@ def no_cuda(monkeypatch):
 
 
 class Worker:
-    def __init__(self, role, config, lane, *, blocks=64, fp8=False, seed=0):
-        self.pool = KVPool(3, 2, 8, blocks, 4, 2, device="cpu", kv_cache_dtype="fp8_e4m3" if fp8 else "auto")
+    def __init__(self, role, config, lane, *, blocks=64, fp8=False, seed=0, device="cpu"):
+        self.pool = KVPool(3, 2, 8, blocks, 4, 2, device=device, kv_cache_dtype="fp8_e4m3" if fp8 else "auto")
         gen = torch.Generator().manual_seed(seed)
         for t in (self.pool.key_cache, self.pool.value_cache):
             raw = t.view(torch.uint8)
-            raw.copy_(torch.randint(0, 256, raw.shape, dtype=torch.uint8, generator=gen) if role == "prefill" else torch.full_like(raw, 0xA5))
+            raw.copy_(torch.randint(0, 256, raw.shape, dtype=torch.uint8, generator=gen) if role == "prefill" else torch.full(raw.shape, 0xA5, dtype=torch.uint8))
         if fp8:
             for t in (self.pool.key_scale, self.pool.value_scale):
-                t.copy_(torch.rand(t.shape, generator=gen) if role == "prefill" else torch.full_like(t, -1.0))
+                t.copy_(torch.rand(t.shape, generator=gen) if role == "prefill" else torch.full(t.shape, -1.0))
         import random
 
         random.Random(seed).shuffle(self.pool._free_blocks)
         self.engine = FakeEngine(role, self.pool)
         self.messages = []
-        hidden = torch.zeros(6, 16)
-        self.transport = B200Transport(f"{role}-0", self.pool, hidden, config, backend=FakeBackend(), lane=lane)
+        hidden = torch.zeros(6, 16, device=device)
+        backend = FakeBackend() if device == "cpu" else None
+        self.transport = B200Transport(f"{role}-0", self.pool, hidden, config, backend=backend, lane=lane)
         self.connector = PDStageConnector(self.engine, hidden, self.transport, config,
                                           notify=lambda kind, **f: self.messages.append(dict(kind=kind, **f)))
 
