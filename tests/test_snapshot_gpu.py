@@ -26,8 +26,8 @@ def test_snapshot_matches_block_indexing_and_restore_round_trips(kv, scale):
     assert torch.equal(snap.keys.view(torch.uint8), pool.key_cache[blocks].cpu().view(torch.uint8))
     assert torch.equal(snap.values.view(torch.uint8), pool.value_cache[blocks].cpu().view(torch.uint8))
     if kv != "auto":
-        assert torch.equal(snap.key_scales, pool.key_scale[blocks].cpu())
-        assert torch.equal(snap.value_scales, pool.value_scale[blocks].cpu())
+        assert torch.equal(snap.key_scales.view(torch.uint8), pool.key_scale[blocks].cpu().view(torch.uint8))
+        assert torch.equal(snap.value_scales.view(torch.uint8), pool.value_scale[blocks].cpu().view(torch.uint8))
     else:
         assert snap.key_scales is None
     before = [t.clone() for t in (pool.key_cache, pool.value_cache)]
