@@ -154,14 +154,17 @@ def fill_source(src, shape, seed):
         src.value_cache.normal_(generator=gen)
 
 
-def spot_check(w, src, dst, requests=(0, -1)):
-    """Independent check with torch indexing: destination rows equal the selected source rows."""
+def spot_check(w, src, dst, requests=None):
+    """Independent check with torch indexing: destination rows equal the selected source rows.
+
+    By default every row of every request is compared (one request at a time, so the temporaries stay small).
+    """
     import numpy as np
     import torch
 
     ok = True
     bs = w.shape.block_size
-    for r in requests:
+    for r in (range(len(w.lengths)) if requests is None else requests):
         n = w.ranges[r][1]
         pos = torch.arange(n, device=src.device)
         for plane in range(w.dst_planes):

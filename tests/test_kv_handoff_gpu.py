@@ -449,3 +449,35 @@ def test_plane_and_layer_slices_tile_the_full_handoff(mode_name):
     assert_pools_equal(gd, D2)
     with pytest.raises(ValueError, match="invalid argument"):
         k.kv_handoff(gp.view(), gd.view(), batch, plane_begin=2, plane_end=planes + 1)
+
+
+def test_benchmark_shape_checked_row_by_row_with_torch_indexing():
+    """The benchmark's own shape (Ouro-1.4B, 16-token blocks, 4 KiB rows) at a size the oracle would take minutes
+    for: every destination row of every request is compared with the source row torch indexing selects."""
+    import bench
+    from vllm_rlt_b200 import workloads
+
+    k = kh()
+    for mode_name, mode in (("exit_only", k.MODE_EXIT_ONLY), ("dedup", k.MODE_DEDUP), ("all", k.MODE_ALL_PLANES)):
+        w = workloads.last_exited_exit_only(requests=6, min_len=200, max_len=900, mode=mode_name)
+        src, dst = bench.build_device_side(w, torch.device("cuda", 0), 7)
+        batch = k.HandoffBatch(w.src_tables, w.dst_tables, w.ranges, block_size=16, exit_planes=w.exit_planes)
+        status = k.new_status()
+        if mode_name == "dedup":
+            # dedup equals all-planes only on a finalized source: make planes beyond each exit a copy first
+            width = max(len(t) for r in w.src_tables for t in r)
+            tables = torch.zeros((len(w.lengths), 4, width), dtype=torch.int32)
+            for i, r in enumerate(w.src_tables):
+                for p, t in enumerate(r):
+                    tables[i, p, : len(t)] = torch.from_numpy(np.asarray(t))
+            rows = torch.tensor([(i, int(e), pos) for i, ex in enumerate(w.exit_planes) for pos, e in enumerate(ex)], dtype=torch.int32)
+            k.kv_finalize(k.PoolView.from_cache(src), tables.cuda(), rows.cuda(), status=status)
+        k.kv_handoff(k.PoolView.from_cache(src), k.PoolView.from_cache(dst), batch, mode=mode, status=status)
+        k.raise_for_status(status)
+        assert bench.spot_check(w, src, dst)
+        if mode_name == "dedup":
+            w_all = workloads.Workload(w.shape, w.lengths, w.ranges, w.src_tables, w.dst_tables, None, w.src_blocks,
+                                       w.dst_blocks, w.dst_planes, extra=dict(mode="all"))
+            assert bench.spot_check(w_all, src, dst)  # same bytes as the reference's all-planes handoff
+        del src, dst
+        torch.cuda.empty_cache()
