@@ -32,7 +32,7 @@ def test_header_and_ctypes_agree_on_the_symbol_list(lib):
     from vllm_rlt_b200 import _lib
 
     names = declared_symbols()
-    assert len(names) >= 21
+    assert len(names) >= 26
     assert names == sorted(_lib.SIGNATURES)
     for name in names:
         assert getattr(lib, name) is not None
@@ -140,3 +140,35 @@ def test_torch_ops_are_registered_in_the_reference_namespace():
     r = torch.zeros(1, dtype=torch.int32)
     with pytest.raises((NotImplementedError, RuntimeError)):
         torch.ops.vllm_rlt.kv_handoff(k, k, None, None, k.clone(), k.clone(), None, None, t, t, r, r, None, None, 0, 0, 0, None)
+
+
+def test_extension_loader_reports_and_caches_like_the_reference(monkeypatch):
+    import importlib
+
+    from vllm_rlt_b200.kernels import _extension
+
+    _extension.try_load_extension.cache_clear()
+    assert _extension.try_load_extension() is True
+    _extension.load_extension()
+    calls = []
+
+    def missing(name):
+        calls.append(name)
+        raise ModuleNotFoundError("nope", name="vllm_rlt_b200._C")
+
+    _extension.try_load_extension.cache_clear()
+    monkeypatch.setattr(_extension, "import_module", missing)
+    assert _extension.try_load_extension() is False and _extension.try_load_extension() is False
+    assert calls == ["vllm_rlt_b200._C"]  # the negative answer is cached
+    with pytest.raises(RuntimeError, match="not built"):
+        _extension.load_extension()
+
+    def broken(name):
+        raise ModuleNotFoundError("torch gone", name="torch")
+
+    _extension.try_load_extension.cache_clear()
+    monkeypatch.setattr(_extension, "import_module", broken)
+    with pytest.raises(ModuleNotFoundError):
+        _extension.try_load_extension()
+    _extension.try_load_extension.cache_clear()
+    importlib.reload(_extension)
