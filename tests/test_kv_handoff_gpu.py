@@ -18,8 +18,9 @@ from tests.gpu_support import GpuPool, assert_pools_equal
 
 pytestmark = pytest.mark.gpu
 
-# kernel flavours: 0 = register path (16-byte loads/stores), 3 and 4 = cp.async.bulk rings of 8 x 4 KiB / 4 x 8 KiB
-VARIANTS = [0, 3, 4]
+# kernel flavours: 0 = register path (16-byte loads/stores), 3 and 4 = cp.async.bulk rings of 8 x 4 KiB / 4 x 8 KiB,
+# 5 = register path with 32-byte loads/stores
+VARIANTS = [0, 3, 4, 5]
 
 
 def kh():

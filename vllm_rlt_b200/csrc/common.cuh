@@ -44,6 +44,23 @@ __device__ __forceinline__ void report(int32_t* status, int code, int a, int b, 
 // Streaming 16-byte accesses: the payload is touched once, keep it out of L1.
 __device__ __forceinline__ uint4 ld_stream(const uint4* p) { return __ldcs(p); }
 __device__ __forceinline__ void st_stream(uint4* p, uint4 v) { __stcs(p, v); }
+// 32-byte accesses (256-bit global loads and stores exist from sm_100 on).
+struct alignas(32) Vec32 {
+  uint32_t v[8];
+};
+__device__ __forceinline__ Vec32 ld_stream(const Vec32* p) {
+  Vec32 r;
+  asm volatile("ld.global.L1::no_allocate.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+               : "=r"(r.v[0]), "=r"(r.v[1]), "=r"(r.v[2]), "=r"(r.v[3]), "=r"(r.v[4]), "=r"(r.v[5]), "=r"(r.v[6]),
+                 "=r"(r.v[7])
+               : "l"(p));
+  return r;
+}
+__device__ __forceinline__ void st_stream(Vec32* p, const Vec32& r) {
+  asm volatile("st.global.L1::no_allocate.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p), "r"(r.v[0]), "r"(r.v[1]),
+               "r"(r.v[2]), "r"(r.v[3]), "r"(r.v[4]), "r"(r.v[5]), "r"(r.v[6]), "r"(r.v[7])
+               : "memory");
+}
 __device__ __forceinline__ uint32_t ld_stream(const uint32_t* p) { return __ldcs(p); }
 __device__ __forceinline__ void st_stream(uint32_t* p, uint32_t v) { __stcs(p, v); }
 __device__ __forceinline__ uint8_t ld_stream(const uint8_t* p) { return *p; }

@@ -43,6 +43,7 @@ struct RegionParams {
   int vec_bytes;        // 16, 4 or 1
   int row_vecs;         // token_bytes / vec_bytes
   unsigned row_magic;   // div_magic(row_vecs)
+  int wide_ok;          // rows and bases are 32-byte multiples: the 32-byte vector flavour may be used
   int layers_per_unit;  // layers one unit covers
   int chunks;           // ceil(layers in slice / layers_per_unit)
 };
@@ -338,7 +339,7 @@ __device__ __forceinline__ char* unit_dst(const TableCopyParams& p, const Unit& 
   return p.dst_packed ? rg.dst_key : (u.kv ? rg.dst_value : rg.dst_key);
 }
 
-template <int kUnroll, bool kStreaming, bool kDedup>
+template <int kUnroll, bool kStreaming, bool kDedup, bool kWide = false>
 __global__ void __launch_bounds__(kThreads, 4) table_copy_kernel(const TableCopyParams p) {
   extern __shared__ int dyn_smem[];
   int* blk_off = dyn_smem;                       // [num_requests + 1]
@@ -364,7 +365,11 @@ __global__ void __launch_bounds__(kThreads, 4) table_copy_kernel(const TableCopy
     const char* src = unit_src(p, u);
     char* dst = unit_dst(p, u);
     const int total_vecs = u.rows * rg.row_vecs;
-    if (rg.vec_bytes == 16) {
+    if (kWide && rg.wide_ok) {
+      const int wide_vecs = rg.row_vecs >> 1;
+      const unsigned wide_magic = wide_vecs == 1 ? 0u : static_cast<unsigned>((1ull << 32) / wide_vecs) + 1u;
+      stream_rows<Vec32, kUnroll, true>(src, dst, rs, rd, u.rows * wide_vecs, wide_vecs, wide_magic);
+    } else if (rg.vec_bytes == 16) {
       stream_rows<uint4, kUnroll, kStreaming>(src, dst, rs, rd, total_vecs, rg.row_vecs, rg.row_magic);
     } else if (rg.vec_bytes == 4) {
       stream_rows<uint32_t, kUnroll, kStreaming>(src, dst, rs, rd, total_vecs, rg.row_vecs, rg.row_magic);
@@ -862,6 +867,9 @@ int launch_table_copy(Direction dir, const RltPool* src, const RltPool* dst, con
     if (dir != kDirect && scales) align_bytes |= any->codes.token_bytes | any->scales.token_bytes;
     rg.vec_bytes = vector_width(rg.src_key, rg.src_value, rg.dst_key, rg.dst_value, align_bytes);
     rg.row_vecs = static_cast<int>(s.token_bytes / rg.vec_bytes);
+    rg.wide_ok = ((reinterpret_cast<uintptr_t>(rg.src_key) | reinterpret_cast<uintptr_t>(rg.src_value) |
+                   reinterpret_cast<uintptr_t>(rg.dst_key) | reinterpret_cast<uintptr_t>(rg.dst_value) |
+                   static_cast<uintptr_t>(align_bytes)) & 31u) == 0;
     rg.row_magic = rg.row_vecs == 1 ? 0u : div_magic(static_cast<uint32_t>(rg.row_vecs));
     long long lpu = unit_target / (s.token_bytes * any->block_size);
     if (lpu < 1) lpu = 1;
@@ -889,6 +897,7 @@ int launch_table_copy(Direction dir, const RltPool* src, const RltPool* dst, con
     if (planned != RLT_OK) return planned;
   }
   const int flavour = opt->variant & 0xf;
+  if (flavour > 5) return RLT_E_INVALID;
   if (flavour <= 2) {
     void (*kernel)(const TableCopyParams) = nullptr;
     if (dedup_wire) {
@@ -901,6 +910,13 @@ int launch_table_copy(Direction dir, const RltPool* src, const RltPool* dst, con
                : flavour == 2 ? table_copy_kernel<8, false, false> : table_copy_kernel<4, true, false>;
     }
     kernel<<<grid, kThreads, smem, stream>>>(p);
+  } else if (flavour == 5) {
+    // 32-byte vector loads and stores (two per thread in flight), same walk
+    if (dedup_wire) {
+      table_copy_kernel<2, true, true, true><<<grid, kThreads, smem, stream>>>(p);
+    } else {
+      table_copy_kernel<2, true, false, true><<<grid, kThreads, smem, stream>>>(p);
+    }
   } else if (flavour <= 4) {
     // 3: eight 4 KiB stages per warp (six loads in flight); 4: four 8 KiB stages (two in flight).
     void (*kernel)(const TableCopyParams) = nullptr;
