@@ -2,7 +2,7 @@
 
 Run once, in a container where the reference checkout is importable:
 
-    python tests/golden/make_golden.py --reference /path/to/vllm-rlt
+    python tests/golden/make_golden.py --reference <vllm-rlt checkout>
 
 The fixtures (``*.json`` and ``*.npz`` beside this file) are committed; the
 tests never import the reference. Every fixture is produced by reference code
@@ -14,6 +14,7 @@ of those descriptors).
 
 import argparse
 import json
+import os
 import random
 import sys
 from pathlib import Path
@@ -403,7 +404,8 @@ def allocation_cases():
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=os.environ.get("VLLM_RLT_REFERENCE", str(HERE.parents[2] / "reference")),
+                    help="path of the vllm-rlt checkout (default: $VLLM_RLT_REFERENCE or a sibling of this repository)")
     args = ap.parse_args()
     sys.path.insert(0, args.reference)
     import torch

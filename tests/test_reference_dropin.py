@@ -13,7 +13,7 @@ from pathlib import Path
 import pytest
 
 ROOT = Path(__file__).resolve().parent.parent
-REFERENCE = Path(os.environ.get("VLLM_RLT_REFERENCE", "/root/reference"))
+REFERENCE = Path(os.environ.get("VLLM_RLT_REFERENCE", str(ROOT.parent / "reference")))
 
 pytestmark = pytest.mark.skipif(not (REFERENCE / "tests" / "test_transfer_connector.py").is_file(),
                                 reason="reference checkout not present")
