@@ -488,6 +488,8 @@ def main():
     ap.add_argument("--streaming", action="store_true", help="also replay a layer-by-layer prefill and stream behind it")
     ap.add_argument("--layer-us", type=float, default=200.0, help="simulated prefill time per layer and depth")
     ap.add_argument("--layers-per-slice", type=int, default=4)
+    ap.add_argument("--path", default="direct", choices=["direct", "staged"],
+                    help="N >= 2: one kernel that writes destination blocks over NVLink, or pack into peer staging + scatter")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     rank = int(os.environ.get("RANK", "0"))
@@ -498,9 +500,14 @@ def main():
     if world == 1 and args.gpus == 1:
         run_single(args)
     else:
-        from vllm_rlt_b200.pd import harness
+        if args.path == "staged":
+            from vllm_rlt_b200.pd import staged
 
-        harness.run_multi(args, rank, world)
+            staged.run_staged(args, rank, world)
+        else:
+            from vllm_rlt_b200.pd import harness
+
+            harness.run_multi(args, rank, world)
 
 
 if __name__ == "__main__":

@@ -381,6 +381,16 @@ def kv_pack(src: PoolView, batch: HandoffBatch, out: torch.Tensor, *, mode=MODE_
     _lib.check(lib.rlt_kv_pack(C.byref(s), C.byref(b), C.byref(o), out.data_ptr(), out.numel(), _stream_ptr(stream)), "rlt_kv_pack")
 
 
+def kv_pack_to(src: PoolView, batch: HandoffBatch, out_ptr: int, out_bytes: int, *, mode=MODE_ALL_PLANES, layer_begin=0,
+               layer_end=0, wire_planes=0, status=None, stream=None, grid_limit=0, variant=0, workspace=None) -> None:
+    """``kv_pack`` into raw memory, typically a staging buffer on the decode GPU mapped through a peer pointer:
+    the gather and the push over NVLink become one kernel and nothing is staged on the prefill side."""
+    lib = _lib.load()
+    s, b = src.as_struct(), batch.as_struct()
+    o = _options(mode, layer_begin, layer_end, wire_planes, status, grid_limit, variant, workspace)
+    _lib.check(lib.rlt_kv_pack(C.byref(s), C.byref(b), C.byref(o), out_ptr, out_bytes, _stream_ptr(stream)), "rlt_kv_pack")
+
+
 def kv_scatter(packed: torch.Tensor, dst: PoolView, batch: HandoffBatch, *, mode=MODE_ALL_PLANES, layer_begin=0,
                layer_end=0, wire_planes=0, status=None, stream=None, grid_limit=0, variant=0, workspace=None) -> None:
     """Write a packed image into the destination blocks of a batch."""
