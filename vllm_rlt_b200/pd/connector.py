@@ -293,6 +293,14 @@ class PDStageConnector:
                 size + (hidden[2] if hidden and last else 0), hidden if last else None,
             ))
             transfer.next_sequence += 1
+        if self._device_ordered():
+            # No need to wait for the next progress() pass: queue the copies now, behind the producer's event
+            # on the device, for as long as the in-flight budget admits them.
+            while transfer.chunks and not transfer.cancelled and self._submit_chunk(transfer):
+                pass
+
+    def _device_ordered(self) -> bool:
+        return getattr(self.transport, "device_ordered", False) is True
 
     # ------------------------------------------------------------------ lifecycle
 
@@ -478,9 +486,10 @@ class PDStageConnector:
             return False
         chunk = t.chunks[0]
         if isinstance(chunk, TableChunk):
-            if not chunk.event.query():
+            ordered = self._device_ordered()
+            if not ordered and not chunk.event.query():
                 return False
-            sent = self._submit_tables(t, chunk)
+            sent = self._submit_tables(t, chunk, after=chunk.event if ordered else None)
         else:
             # a caller-built descriptor chunk: (event, sequence, local, remote, size)
             event, sequence, local, remote, size = chunk
@@ -491,11 +500,12 @@ class PDStageConnector:
         t.submitted_since_compute = True
         return True
 
-    def _submit_tables(self, t, chunk):
+    def _submit_tables(self, t, chunk, after=None):
         extra = [chunk.hidden] if chunk.hidden is not None else []
+        ordered = {} if after is None else {"after": after}
         if chunk.start >= chunk.end:  # nothing but the hidden row
             local = [(s, n, self.transport.info["device"]) for s, _, n in extra]
             remote = [(d, n, self.transport.peers[t.peer]["device"]) for _, d, n in extra]
-            return self.transport.submit(t.tid, chunk.sequence, t.peer, local, remote, chunk.size)
+            return self.transport.submit(t.tid, chunk.sequence, t.peer, local, remote, chunk.size, **ordered)
         requests = [(chunk.source_tables, chunk.target_tables, chunk.start, chunk.end)]
-        return self.transport.submit_tables(t.tid, chunk.sequence, t.peer, requests, chunk.size, extra=extra)
+        return self.transport.submit_tables(t.tid, chunk.sequence, t.peer, requests, chunk.size, extra=extra, **ordered)

@@ -137,7 +137,14 @@ class Mailbox:
 
 
 class CudaBackend:
-    """The device side of the transport: peer mappings, launches, events."""
+    """The device side of the transport: peer mappings, launches, events.
+
+    Every launch goes to one transfer stream owned by the backend, so copies never queue behind the model's
+    compute. ``device_ordered`` tells the connector that a submission may be handed a producer event to wait
+    for *on the device*: the copy is queued at once and starts when the event fires, with no host poll in between.
+    """
+
+    device_ordered = True
 
     def __init__(self, device):
         import torch
@@ -149,6 +156,15 @@ class CudaBackend:
         self.mapping = peerlib.PeerMapping()
         self.peerlib = peerlib
         self._mailboxes: dict[str, tuple[Mailbox, int]] = {}
+        self.stream = torch.cuda.Stream(self.device)
+
+    def _on_stream(self):
+        return self.torch.cuda.stream(self.stream)
+
+    def order_after(self, event) -> None:
+        """Make everything submitted from now on wait (on the device) for ``event``."""
+        if event is not None:
+            self.stream.wait_event(event)
 
     def export(self, tensor) -> dict:
         e = self.peerlib.export_tensor(tensor)
@@ -195,7 +211,7 @@ class CudaBackend:
         torch = self.torch
         host = torch.tensor(triples, dtype=torch.int64).reshape(-1, 3).pin_memory()
         keep = []
-        with torch.cuda.device(self.device):
+        with torch.cuda.device(self.device), self._on_stream():
             for at in range(0, len(host), kh._lib.MAX_SEGMENTS):
                 dev = host[at : at + kh._lib.MAX_SEGMENTS].to(self.device, non_blocking=True)
                 kh.kv_copy_segments(dev)
@@ -216,7 +232,7 @@ class CudaBackend:
         planes = 1 if mode == kh.MODE_EXIT_ONLY else peer_info["depths"]
         dst = kh.PoolView(codes, scales, peer_info["num_blocks"], peer_info["block_size"], peer_info["num_layers"],
                           planes, peer_info["device"])
-        with self.torch.cuda.device(self.device):
+        with self.torch.cuda.device(self.device), self._on_stream():
             batch = kh.HandoffBatch(
                 [r[0] for r in requests], [r[1] for r in requests], [(r[2], r[3]) for r in requests],
                 block_size=src.block_size, exit_planes=exit_planes, src_blocks=src.num_blocks,
@@ -231,12 +247,12 @@ class CudaBackend:
 
         with self.torch.cuda.device(self.device):
             buf = (C.c_uint8 * BODY_BYTES).from_buffer_copy(body)
-            _lib.check(_lib.load().rlt_kv_post(slot_ptr, buf, stamp, self.torch.cuda.current_stream().cuda_stream), "rlt_kv_post")
+            _lib.check(_lib.load().rlt_kv_post(slot_ptr, buf, stamp, self.stream.cuda_stream), "rlt_kv_post")
 
     def event(self):
         ev = self.torch.cuda.Event()
         with self.torch.cuda.device(self.device):
-            ev.record()
+            ev.record(self.stream)
         return ev
 
     def close(self):
@@ -266,6 +282,8 @@ class B200Transport:
         self.name = name
         self.cache = cache
         self.backend = backend if backend is not None else CudaBackend(cache.key_cache.device)
+        # True: submissions may carry a producer event that the copy waits for on the device (``after=``)
+        self.device_ordered = getattr(self.backend, "device_ordered", False) is True
         self.storage = (cache.key_cache, cache.value_cache, hidden)
         # Dynamic scales travel with their rows; a fixed scale is checked in the handshake instead
         # (vllm_rlt/pd/transport.py:132-137).
@@ -353,11 +371,15 @@ class B200Transport:
         self.inflight_bytes += size
         return True
 
-    def submit(self, transfer_id, sequence, peer, local, remote, size):
-        """WRITE the local ranges onto the remote ranges and notify the peer (vllm_rlt/pd/transport.py:182-201)."""
+    def submit(self, transfer_id, sequence, peer, local, remote, size, *, after=None):
+        """WRITE the local ranges onto the remote ranges and notify the peer (vllm_rlt/pd/transport.py:182-201).
+
+        ``after`` (device-ordered backends only): a producer event the copy waits for on the device.
+        """
         state = self._writer_state(peer)
         if not self._admit(size, state):
             return False
+        self._order_after(after)
         if len(local) != len(remote):
             raise ValueError("incompatible source/target KV geometry")
         translate = state["translate"]
@@ -369,14 +391,22 @@ class B200Transport:
         keep = self.backend.copy_segments(triples) if triples else ()
         return self._finish_submit(state, transfer_id, sequence, size, keep)
 
+    def _order_after(self, event) -> None:
+        if event is None:
+            return
+        if not self.device_ordered:
+            raise ValueError("this backend cannot wait for an event on the device; submit once it has fired")
+        self.backend.order_after(event)
+
     def submit_tables(self, transfer_id, sequence, peer, requests, size, *, mode=0, layer_begin=0, layer_end=0,
-                      exit_planes=None, extra=(), status=None):
+                      exit_planes=None, extra=(), status=None, after=None):
         """Table-driven form of ``submit``: ``requests`` is a list of ``(source tables, target tables,
         start, end)`` and the GPU walks the tables itself; ``extra`` holds plain ``(source address,
         peer address, bytes)`` ranges that ride along (the final hidden-state row)."""
         state = self._writer_state(peer)
         if not self._admit(size, state):
             return False
+        self._order_after(after)
         translate = state["translate"]
         keep = tuple(self.backend.handoff(self.cache, self.peers[peer], translate, requests, mode=mode,
                                           layer_begin=layer_begin, layer_end=layer_end, exit_planes=exit_planes,
