@@ -36,12 +36,11 @@ def test_reference_transfer_connector_suite_passes_with_this_connector():
 
 
 def test_reference_pd_cpu_cases_pass_with_this_connector():
-    out = run_reference_tests(
-        "tests/test_pd.py::test_pd_wavefront_transfer_uses_chunk_origin_after_budget_contention",
-        "tests/test_pd.py::test_cancelled_transfer_does_not_recycle_pending_hidden_copy",
-        "tests/test_stage_engine.py",
-    )
+    # the whole of test_pd.py (its GPU/NIXL-marked cases skip themselves) and the stage-engine suite, which
+    # includes a spawned worker process driving the connector over a pipe
+    out = run_reference_tests("tests/test_pd.py", "tests/test_stage_engine.py")
     assert out.returncode == 0, out.stdout[-4000:] + out.stderr[-2000:]
+    assert " passed" in out.stdout and "failed" not in out.stdout
 
 
 def test_plugin_really_swaps_the_class():
