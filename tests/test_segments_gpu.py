@@ -219,3 +219,50 @@ def test_torch_ops_for_slices_dedup_wire_and_finalize():
                                  gd2.key_scale, gd2.value_scale, st, dt, begin, end, None, None, 0, l0, l1, p0, p1, status)
     assert_pools_equal(gd2, D)
     assert status.tolist() == [0, 0, 0, 0]
+
+
+def test_handoff_op_uses_the_current_stream_and_replays_in_a_cuda_graph():
+    """Stream and graph behaviour the reference pins for its native op (tests/test_activation.py:328-367)."""
+    from vllm_rlt_b200 import _build
+
+    torch.ops.load_library(str(_build.PACKAGE / _build.OPS_NAME))
+    ops = torch.ops.vllm_rlt
+    shape = (8, 2, 4, 2, 16)  # blocks, layers, block size, heads, dim
+    src_k = torch.randn(shape, device="cuda", dtype=torch.bfloat16)
+    src_v = torch.randn(shape, device="cuda", dtype=torch.bfloat16)
+    dst_k, dst_v = torch.zeros_like(src_k), torch.zeros_like(src_v)
+    st = torch.tensor([[[5, 2]]], dtype=torch.int32, device="cuda")
+    dt = torch.tensor([[[1, 6]]], dtype=torch.int32, device="cuda")
+    begin = torch.tensor([1], dtype=torch.int32, device="cuda")
+    end = torch.tensor([7], dtype=torch.int32, device="cuda")
+
+    def launch():
+        ops.kv_handoff(src_k, src_v, None, None, dst_k, dst_v, None, None, st, dt, begin, end, None, None, 0, 0, 0, None)
+
+    def expected():
+        k, v = torch.zeros_like(src_k), torch.zeros_like(src_v)
+        for t in range(1, 7):
+            sb, db = (5, 2)[t // 4], (1, 6)[t // 4]
+            k[db, :, t % 4] = src_k[sb, :, t % 4]
+            v[db, :, t % 4] = src_v[sb, :, t % 4]
+        return k, v
+
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        launch()  # warm-up on the side stream, as graph capture wants
+    side.synchronize()
+    k, v = expected()
+    assert torch.equal(dst_k, k) and torch.equal(dst_v, v)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        launch()
+    for _ in range(2):
+        src_k.normal_()
+        src_v.normal_()
+        dst_k.zero_()
+        dst_v.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        k, v = expected()
+        assert torch.equal(dst_k, k) and torch.equal(dst_v, v)
