@@ -26,6 +26,17 @@
 // HBM roofline: the kernel reads and writes each payload byte once; tables add
 // 4 bytes per (request, plane, block). Algorithmic bytes per token per plane
 // are 2 * layers * kv_heads * (head_dim * elt + scale) read and the same written.
+//
+// Flavours (RltOptions.variant, low 4 bits), all bit-identical in result:
+//   0      register path, 4 x 16-byte streaming loads in flight per thread, 3 CTAs per SM (default;
+//          measured at the HBM copy peak)
+//   1, 2   the same with 8 loads in flight, with and without streaming cache hints
+//   3, 4   rows move global -> shared -> global with cp.async.bulk, per-warp rings tracked by mbarriers
+//   5      register path with 32-byte loads and stores
+//
+// The dedup wire image (pack / scatter in RLT_MODE_DEDUP) carries, per token, only the planes up to
+// its exit plane. Where each (request, plane, block) starts in that image is computed on the device by
+// three small kernels (count, tile scan, finish) into a caller-provided workspace; see plan_dedup.
 
 #include "common.cuh"
 
