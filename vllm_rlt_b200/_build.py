@@ -56,7 +56,7 @@ def build_library(force: bool = False, verbose: bool = False) -> Path:
     deps = sources + [CSRC / "common.cuh", INCLUDE / "rlt_kv_handoff.h"]
     if force or _stale(target, deps):
         cmd = [_nvcc(), *ARCH, "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC,-fvisibility=hidden",
-               f"-I{INCLUDE}", "-shared", "-o", str(target), *map(str, sources)]
+               f"-I{INCLUDE}", "-shared", "-o", str(target), *map(str, sources), "-ldl"]
         if verbose:
             cmd.insert(1, "-Xptxas=-v")
         _run(cmd)

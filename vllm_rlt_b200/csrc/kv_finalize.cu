@@ -93,6 +93,7 @@ extern "C" {
 
 int rlt_kv_finalize(const RltPool* pool, const int32_t* tables, int32_t num_requests, int32_t table_width,
                     const int32_t* rows, int32_t count, uint64_t layer_mask, int32_t* status, rlt_stream_t stream) {
+  const rlt::NvtxRange range("rlt.kv_finalize");
   if (count == 0) return RLT_OK;
   if (pool == nullptr || tables == nullptr || rows == nullptr || count < 0 || num_requests < 1 || table_width < 1)
     return RLT_E_INVALID;

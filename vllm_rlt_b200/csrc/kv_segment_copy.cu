@@ -110,6 +110,7 @@ __global__ void __launch_bounds__(kThreads, 4) segment_copy_kernel(const long lo
 extern "C" {
 
 int rlt_kv_push(const void* src, void* dst, int64_t nbytes, rlt_stream_t stream) {
+  const rlt::NvtxRange range("rlt.kv_push");
   if (nbytes == 0) return RLT_OK;
   if (src == nullptr || dst == nullptr || nbytes < 0) return RLT_E_INVALID;
   int sms = 0;
@@ -125,6 +126,7 @@ int rlt_kv_push(const void* src, void* dst, int64_t nbytes, rlt_stream_t stream)
 }
 
 int rlt_kv_copy_segments(const int64_t* segments, int32_t count, rlt_stream_t stream) {
+  const rlt::NvtxRange range("rlt.kv_copy_segments");
   if (count == 0) return RLT_OK;
   if (segments == nullptr || count < 0) return RLT_E_INVALID;
   if (count > RLT_MAX_SEGMENTS) return RLT_E_LIMIT;

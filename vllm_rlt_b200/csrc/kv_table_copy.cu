@@ -749,6 +749,7 @@ enum Direction { kDirect, kPack, kScatter };
 int launch_table_copy(Direction dir, const RltPool* src, const RltPool* dst, const RltBatch* batch,
                       const RltOptions* opt, void* packed, long long packed_bytes, cudaStream_t stream,
                       void* workspace = nullptr, long long workspace_bytes = 0) {
+  const NvtxRange range(dir == kDirect ? "rlt.kv_handoff" : dir == kPack ? "rlt.kv_pack" : "rlt.kv_scatter");
   if (batch == nullptr || opt == nullptr) return RLT_E_INVALID;
   if (workspace == nullptr) {
     workspace = opt->workspace;

@@ -65,7 +65,9 @@ def make_workload(args, prefill_index: int, lengths=None):
         return wl.recurrent_depth_dedup(wl.HUGINN_3P5B, requests=args.requests, seed=seed, lengths=lengths)
     if name == "ouro2p6b_chunk":
         # one 2048-token prefill chunk per request, all planes (what a WCPB step finishes)
-        return wl.per_depth_all_planes(wl.OURO_2P6B, requests=args.requests, min_len=2048, max_len=2048, seed=seed)
+        # half of the requests already have a 4096-token prefix on the decode side: only the chunk after it moves
+        return wl.per_depth_all_planes(wl.OURO_2P6B, requests=args.requests, min_len=2048, max_len=2048,
+                                       seed=wl.SEED_BASE + 5, resident_prefix=4096, resident_fraction=0.5)
     raise SystemExit(f"unknown workload {name}")
 
 
@@ -287,16 +289,17 @@ def run_multi(args, rank: int, world: int) -> None:
             mine = assigned(p, d_rank, wp)
             if not mine:
                 continue
-            i = mine[0]
-            n = min(sample, wp.lengths[i])
+            i = mine[-1]
+            lo, hi = wp.ranges[i]
+            n = min(sample, hi - lo)
             expect = torch.zeros((2, n, s.num_layers, s.num_kv_heads, s.head_dim * s.element), dtype=store_dtype, device=device)
             for plane in range(dst_planes):
-                pos = torch.arange(n, device=device)
+                pos = torch.arange(lo, lo + n, device=device)
                 if rank == p:
                     if wp.exit_planes is None:
                         sp = torch.full((n,), plane, device=device)
                     else:
-                        e = torch.tensor(np.asarray(wp.exit_planes[i][:n]), device=device).long()
+                        e = torch.tensor(np.asarray(wp.exit_planes[i][lo : lo + n]), device=device).long()
                         sp = e if args.mode == "exit_only" else torch.clamp(e, max=plane)
                     st = torch.tensor(np.stack([np.asarray(t) for t in wp.src_tables[i]]), device=device).long()
                     sb = st[sp, pos // s.block_size]

@@ -153,8 +153,14 @@ def last_exited_exit_only(
 def per_depth_all_planes(
     shape: KVShape = OURO_1P4B, *, requests: int = 8, min_len: int = 128, max_len: int = 1024,
     seed: int = SEED_BASE, log_uniform: bool = False, lengths: list[int] | None = None,
+    resident_prefix: int = 0, resident_fraction: float = 0.0,
 ) -> Workload:
-    """The reference's own case: every plane of every prompt token is sent."""
+    """The reference's own case: every plane of every prompt token is sent.
+
+    ``resident_fraction`` of the requests additionally own ``resident_prefix`` leading tokens that the decode
+    side already holds (a prefix-cache hit): their tables cover the prefix but the handoff range starts after it,
+    which is the ``start = max(start, cached_tokens)`` skip of the reference (vllm_rlt/pd/connector.py:223).
+    """
     rng = random.Random(seed)
     if lengths is not None:
         lengths, requests = list(lengths), len(lengths)
@@ -162,14 +168,17 @@ def per_depth_all_planes(
         lengths = [int(round(math.exp(rng.uniform(math.log(min_len), math.log(max_len))))) for _ in range(requests)]
     else:
         lengths = [rng.randint(min_len, max_len) for _ in range(requests)]
+    starts = [resident_prefix if resident_prefix and rng.random() < resident_fraction else 0 for _ in lengths]
+    lengths = [s + n for s, n in zip(starts, lengths)]
     src_tables, src_blocks = _tables(rng, lengths, shape.planes, shape.block_size)
     dst_tables, dst_blocks = _tables(rng, lengths, shape.planes, shape.block_size)
+    skipped = f", {sum(bool(s) for s in starts)} requests skip a resident {resident_prefix}-token prefix" if resident_prefix else ""
     return Workload(
-        shape, lengths, [(0, n) for n in lengths], src_tables, dst_tables, None, src_blocks, dst_blocks,
+        shape, lengths, [(s, n) for s, n in zip(starts, lengths)], src_tables, dst_tables, None, src_blocks, dst_blocks,
         shape.planes,
         description=(
             f"{shape.name} per-depth all planes: {requests} requests, lengths "
-            f"{'log-' if log_uniform else ''}U[{min_len},{max_len}], block {shape.block_size}, seeded random block tables"
+            f"{'log-' if log_uniform else ''}U[{min_len},{max_len}], block {shape.block_size}, seeded random block tables{skipped}"
         ),
         extra=dict(mode="all"),
     )
