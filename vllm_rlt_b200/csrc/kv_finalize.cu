@@ -23,6 +23,8 @@ struct FinalizeRegion {
   char* value;
   long long block_bytes, layer_bytes, token_bytes;
   int vec_bytes;
+  int row_vecs;        // token_bytes / vec_bytes
+  unsigned row_magic;  // div_magic(row_vecs), 0 for one-vector rows
 };
 
 struct FinalizeParams {
@@ -37,14 +39,46 @@ struct FinalizeParams {
   int* status;
 };
 
+constexpr int kUnroll = 4;
+
+// Copies the token's row of every selected layer as one flat vector array: vector i belongs to selected
+// layer i / row_vecs. kUnroll loads are in flight per thread before the first store.
 template <typename T>
-__device__ __forceinline__ void copy_row(const char* src, char* dst, int vecs) {
-  const T* s = reinterpret_cast<const T*>(src);
-  T* d = reinterpret_cast<T*>(dst);
-  for (int i = threadIdx.x; i < vecs; i += kThreads) st_stream(d + i, ld_stream(s + i));
+__device__ __forceinline__ void copy_layers(const char* src, char* dst, const int* layer_of, int layers, int row_vecs,
+                                            unsigned row_magic, long long layer_bytes) {
+  const int total = layers * row_vecs;
+  for (int base = threadIdx.x; base < total; base += kThreads * kUnroll) {
+    T regs[kUnroll];
+    long long at[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const int i = base + u * kThreads;
+      at[u] = -1;
+      if (i < total) {
+        const int slot = row_magic ? static_cast<int>(__umulhi(static_cast<unsigned>(i), row_magic)) : i;
+        at[u] = layer_of[slot] * layer_bytes + static_cast<long long>(i - slot * row_vecs) * static_cast<long long>(sizeof(T));
+        regs[u] = ld_stream(reinterpret_cast<const T*>(src + at[u]));
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      if (at[u] >= 0) st_stream(reinterpret_cast<T*>(dst + at[u]), regs[u]);
+    }
+  }
 }
 
 __global__ void __launch_bounds__(kThreads, 4) finalize_kernel(const FinalizeParams p) {
+  __shared__ int layer_of[64];  // the selected layers, in order
+  __shared__ int n_selected;
+  if (threadIdx.x == 0) {
+    int n = 0;
+    for (int layer = 0; layer < p.num_layers; ++layer) {
+      if ((p.layer_mask >> layer) & 1ull) layer_of[n++] = layer;
+    }
+    n_selected = n;
+  }
+  __syncthreads();
+  const int layers = n_selected;
   const int tensors = 2 * p.num_regions;
   const int targets = p.planes - 1;
   const long long units = static_cast<long long>(p.n) * targets * tensors;
@@ -70,18 +104,14 @@ __global__ void __launch_bounds__(kThreads, 4) finalize_kernel(const FinalizePar
     }
     const FinalizeRegion& rg = p.region[tensor >> 1];
     char* pool = (tensor & 1) ? rg.value : rg.key;
-    for (int layer = 0; layer < p.num_layers; ++layer) {
-      if (!((p.layer_mask >> layer) & 1ull)) continue;
-      const long long in_block = layer * rg.layer_bytes + offset * rg.token_bytes;
-      const char* src = pool + sb * rg.block_bytes + in_block;
-      char* dst = pool + db * rg.block_bytes + in_block;
-      if (rg.vec_bytes == 16) {
-        copy_row<uint4>(src, dst, static_cast<int>(rg.token_bytes >> 4));
-      } else if (rg.vec_bytes == 4) {
-        copy_row<uint32_t>(src, dst, static_cast<int>(rg.token_bytes >> 2));
-      } else {
-        copy_row<uint8_t>(src, dst, static_cast<int>(rg.token_bytes));
-      }
+    const char* src = pool + sb * rg.block_bytes + offset * rg.token_bytes;
+    char* dst = pool + db * rg.block_bytes + offset * rg.token_bytes;
+    if (rg.vec_bytes == 16) {
+      copy_layers<uint4>(src, dst, layer_of, layers, rg.row_vecs, rg.row_magic, rg.layer_bytes);
+    } else if (rg.vec_bytes == 4) {
+      copy_layers<uint32_t>(src, dst, layer_of, layers, rg.row_vecs, rg.row_magic, rg.layer_bytes);
+    } else {
+      copy_layers<uint8_t>(src, dst, layer_of, layers, rg.row_vecs, rg.row_magic, rg.layer_bytes);
     }
   }
 }
@@ -119,6 +149,10 @@ int rlt_kv_finalize(const RltPool* pool, const int32_t* tables, int32_t num_requ
     const uintptr_t bits = reinterpret_cast<uintptr_t>(r.key) | reinterpret_cast<uintptr_t>(r.value) |
                            static_cast<uintptr_t>(r.token_bytes);
     out.vec_bytes = (bits & 15u) == 0 ? 16 : (bits & 3u) == 0 ? 4 : 1;
+    out.row_vecs = static_cast<int>(r.token_bytes / out.vec_bytes);
+    out.row_magic = out.row_vecs == 1 ? 0u : rlt::div_magic(static_cast<uint32_t>(out.row_vecs));
+    // the flat index (selected layers x row vectors) times row_vecs must stay below 2^32 for the multiplier split
+    if (64ll * out.row_vecs * out.row_vecs >= (1ll << 32)) return RLT_E_LIMIT;
   }
   p.planes = pool->num_planes;
   p.block_size = pool->block_size;
