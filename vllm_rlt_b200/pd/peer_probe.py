@@ -19,6 +19,7 @@ def main() -> None:
     ap.add_argument("--requests", type=int, default=2)
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--mode", default="exit_only", choices=["exit_only", "all"])
+    ap.add_argument("--variant", type=int, default=0, help="kernel flavour (RltOptions.variant)")
     args = ap.parse_args()
 
     import torch
@@ -50,7 +51,7 @@ def main() -> None:
     for i in range(1 + args.steps):
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
-        kh.kv_handoff(sv, dv, batch, mode=mode, status=status)
+        kh.kv_handoff(sv, dv, batch, mode=mode, status=status, variant=args.variant)
         b.record()
         torch.cuda.synchronize(0)
         if i:
