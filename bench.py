@@ -28,6 +28,8 @@ METRIC = "kv_handoff_gbps"
 UNIT = "GB/s"
 FALLBACK_HBM_GBS = 6650.0
 NVLINK_MEASURED_GBS = 770.0
+# link bytes per payload byte for writes over NVLink (ncu: nvltx__bytes.sum / nvltx__bytes_data_user.sum of the handoff kernel)
+NVLINK_WRITE_OVERHEAD = 1.1875
 # DRAM traffic per algorithmic byte of table_copy_kernel, from the ncu capture summarised under profiles/
 TRAFFIC_PER_ALGORITHMIC_BYTE = 0.98
 

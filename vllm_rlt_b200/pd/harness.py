@@ -433,6 +433,10 @@ def run_multi(args, rank: int, world: int) -> None:
                          "peak_source": "measured peer copy on this pool, 770 GB/s per direction per GPU (nominal 900)",
                          "kernel": "table_copy_kernel", "algorithmic_bytes_per_launch": w.payload_bytes,
                          "kernel_ms": float(k_ms.item()), "frac_of_nominal_900": per_link / 900.0,
+                         "raw_link_gbps": per_link * bench.NVLINK_WRITE_OVERHEAD,
+                         "raw_link_frac_of_900": per_link * bench.NVLINK_WRITE_OVERHEAD / 900.0,
+                         "raw_link_note": "NVLink carries 18.75 % of protocol bytes on top of written payload (ncu nvltx__bytes "
+                                          "counters of this kernel)",
                          "what": "aggregate payload rate / min(prefill, decode) GPUs: the per-GPU link rate of the busier side"},
             "per_pair_gbps": per_link, "slowest_prefill_gpu_egress_gbps": per_gpu,
             "e2e": {"value": total_payload / float(e2e_s.item()) / 1e9, "unit": bench.UNIT,
