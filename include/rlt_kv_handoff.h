@@ -130,6 +130,10 @@ typedef struct RltOptions {
   int64_t workspace_bytes; /* at least rlt_kv_dedup_workspace_bytes(...) for those calls          */
   int32_t plane_begin; /* destination (or wire) plane slice [plane_begin, plane_end): lets a   */
   int32_t plane_end;   /* depth be handed off as soon as it is computed; 0 means all planes     */
+  uint64_t deep_layer_mask; /* rlt_kv_handoff only: layers carried for planes >= 1 (bit l = layer l);
+                          0 = all. Recurrent-depth models keep only their recurrent layers per
+                          depth (recurrent_layers, vllm_rlt/core/kv_cache_manager.py:228-238);
+                          plane 0 always carries the whole layer slice                          */
 } RltOptions;
 
 /* --- information ---------------------------------------------------------------------------- */

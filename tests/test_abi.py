@@ -93,6 +93,9 @@ def test_argument_errors_are_found_on_the_host_before_any_launch(lib):
     assert lib.rlt_kv_handoff(C.byref(pool), C.byref(pool), C.byref(batch), C.byref(opts), None) == _lib.RLT_E_LIMIT
     batch.num_requests = 1
     assert lib.rlt_kv_pack(C.byref(pool), C.byref(batch), C.byref(opts), 0x7001, 64, None) == _lib.RLT_E_ALIGN
+    opts.deep_layer_mask = 0b10  # a per-depth layer subset would leave holes in a packed image: handoff only
+    assert lib.rlt_kv_pack(C.byref(pool), C.byref(batch), C.byref(opts), 0x7000, 64, None) == _lib.RLT_E_INVALID
+    opts.deep_layer_mask = 0
     assert lib.rlt_kv_packed_bytes(C.byref(pool), 10, 3, 2) == 10 * 3 * 2 * 2 * 64
     assert lib.rlt_kv_copy_segments(None, 1, None) == _lib.RLT_E_INVALID
     assert lib.rlt_kv_copy_segments(0x1000, _lib.MAX_SEGMENTS + 1, None) == _lib.RLT_E_LIMIT

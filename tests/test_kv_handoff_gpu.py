@@ -482,3 +482,36 @@ def test_benchmark_shape_checked_row_by_row_with_torch_indexing():
             assert bench.spot_check(w_all, src, dst)  # same bytes as the reference's all-planes handoff
         del src, dst
         torch.cuda.empty_cache()
+
+
+@pytest.mark.parametrize("mode_name", ["all", "dedup"])
+def test_recurrent_depth_model_carries_only_its_recurrent_layers_in_deeper_planes(mode_name):
+    """Golden pools of a manager built with ``recurrent_layers=(2, 3)``: plane 0 moves whole, planes >= 1 move only
+    layers 2 and 3 (the only ones ``finalize_token`` maintains there); the other rows keep the sentinel."""
+    k = kh()
+    case = [c for c in golden_json("finalize.json") if c["recurrent_layers"] is not None][0]
+    arrays = golden_npz(case["name"])
+    shape, deep = case["shape"], case["recurrent_layers"]
+    P = oracle_pool(case["kind"], shape, recurrent_layers=deep)
+    load_pool(P, arrays, "src_after_")
+    D = sentinel_destination(case["kind"], shape)
+    gp, gd = GpuPool(P), GpuPool(D)
+    reqs = case["requests"]
+    batch = k.HandoffBatch([r["src_tables"] for r in reqs], [r["dst_tables"] for r in reqs],
+                           [(0, r["tokens"]) for r in reqs], block_size=shape[4],
+                           exit_planes=[r["exit_planes"] for r in reqs])
+    mode = k.MODE_ALL_PLANES if mode_name == "all" else k.MODE_DEDUP
+    status = k.new_status()
+    k.kv_handoff(gp.view(), gd.view(), batch, mode=mode, deep_layers=deep, status=status)
+    k.raise_for_status(status)
+    full = sentinel_destination(case["kind"], shape)
+    load_pool(full, arrays, "dst_after_")  # the reference's all-layer, all-plane destination
+    page = shape[4]
+    for r in reqs:
+        for plane, table in enumerate(r["dst_tables"]):
+            layers = range(shape[0]) if plane == 0 else deep
+            for t in range(r["tokens"]):
+                for a, b in zip(full.tensors(), D.tensors()):
+                    for layer in layers:
+                        b.data[table[t // page], layer, t % page] = a.data[table[t // page], layer, t % page]
+    assert_pools_equal(gd, D)

@@ -71,6 +71,7 @@ class RltOptions(C.Structure):
         ("workspace_bytes", C.c_int64),
         ("plane_begin", C.c_int32),
         ("plane_end", C.c_int32),
+        ("deep_layer_mask", C.c_uint64),
     ]
 
 

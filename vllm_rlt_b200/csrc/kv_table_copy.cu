@@ -84,6 +84,7 @@ struct TableCopyParams {
   int dst_packed;   // destination is the packed image (pack)
   long long packed_token_bytes;  // 2 * layers in slice * (codes row + scales row)
   long long packed_bytes;        // size of the packed image; rows past it are skipped
+  unsigned long long deep_layer_mask;  // layers carried for planes >= 1; 0 = all
   int dedup_wire;                // the packed image holds, per token, only planes up to its exit plane
   const int* dedup_prefix;       // [planes * total blocks] wire tokens before each (request, plane, block)
   int* status;
@@ -305,6 +306,7 @@ __device__ __forceinline__ void row_offsets(const TableCopyParams& p, const Unit
       ok = false;
     }
   }
+  if (p.deep_layer_mask != 0 && u.plane > 0 && !((p.deep_layer_mask >> layer) & 1ull)) ok = false;  // not carried
   const long long in_block = layer * rg.layer_bytes + (t_abs - u.logical * p.block_size) * rg.token_bytes;
   if (p.src_packed) {
     so = packed;
@@ -840,6 +842,10 @@ int launch_table_copy(Direction dir, const RltPool* src, const RltPool* dst, con
   const int plane_end = opt->plane_end == 0 ? p.dst_planes : opt->plane_end;
   if (p.plane_begin < 0 || plane_end <= p.plane_begin || plane_end > p.dst_planes) return RLT_E_INVALID;
   p.plane_count = plane_end - p.plane_begin;
+  if (opt->deep_layer_mask != 0) {
+    if (dir != kDirect || any->num_layers > 64) return RLT_E_INVALID;
+    p.deep_layer_mask = opt->deep_layer_mask;
+  }
 
   const int slice_layers = layer_end - layer_begin;
   const long long row_total = any->codes.token_bytes + (scales ? any->scales.token_bytes : 0);

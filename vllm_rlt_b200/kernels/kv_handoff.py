@@ -320,14 +320,14 @@ def raise_for_status(status: torch.Tensor) -> None:
 
 
 def _options(mode, layer_begin, layer_end, wire_planes, status, grid_limit, variant, workspace=None,
-             plane_begin=0, plane_end=0) -> _lib.RltOptions:
+             plane_begin=0, plane_end=0, deep_layer_mask=0) -> _lib.RltOptions:
     if workspace is not None and (workspace.dtype != torch.uint8 or not workspace.is_contiguous() or not workspace.is_cuda):
         raise ValueError("workspace must be a contiguous CUDA uint8 tensor")
     return _lib.RltOptions(
         int(mode), int(layer_begin), int(layer_end), int(wire_planes),
         status.data_ptr() if status is not None else None, int(grid_limit), int(variant),
         workspace.data_ptr() if workspace is not None else None, workspace.numel() if workspace is not None else 0,
-        int(plane_begin), int(plane_end),
+        int(plane_begin), int(plane_end), int(deep_layer_mask),
     )
 
 
@@ -348,16 +348,25 @@ def dedup_wire_tokens(workspace: torch.Tensor) -> int:
 
 
 def kv_handoff(src: PoolView, dst: PoolView, batch: HandoffBatch, *, mode=MODE_ALL_PLANES,
-               layer_begin=0, layer_end=0, plane_begin=0, plane_end=0, status=None, stream=None, grid_limit=0,
-               variant=0) -> None:
+               layer_begin=0, layer_end=0, plane_begin=0, plane_end=0, deep_layers=None, status=None, stream=None,
+               grid_limit=0, variant=0) -> None:
     """Pool-to-pool handoff of a batch, straight from source blocks to destination blocks.
 
     ``layer_begin/layer_end`` and ``plane_begin/plane_end`` restrict the launch to a slice of layers and
-    destination planes (0, 0 = everything), which is what layer-by-layer streaming uses.
+    destination planes (0, 0 = everything), which is what layer-by-layer streaming uses. ``deep_layers`` lists
+    the layers carried for planes >= 1 (a recurrent-depth model's recurrent layers); plane 0 carries them all.
     """
     lib = _lib.load()
+    mask = 0
+    if deep_layers is not None:
+        for layer in deep_layers:
+            if not 0 <= layer < min(src.num_layers, 64):
+                raise ValueError("recurrent_layers must be valid cache layer indices")
+            mask |= 1 << layer
+        if mask == 0:
+            raise ValueError("recurrent_layers must be nonempty and unique")
     s, d, b = src.as_struct(), dst.as_struct(), batch.as_struct()
-    o = _options(mode, layer_begin, layer_end, 0, status, grid_limit, variant, None, plane_begin, plane_end)
+    o = _options(mode, layer_begin, layer_end, 0, status, grid_limit, variant, None, plane_begin, plane_end, mask)
     _lib.check(lib.rlt_kv_handoff(C.byref(s), C.byref(d), C.byref(b), C.byref(o), _stream_ptr(stream)), "rlt_kv_handoff")
 
 
