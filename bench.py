@@ -485,7 +485,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--prefill", type=int, default=0, help="prefill ranks at N >= 2 (default N/2)")
     ap.add_argument("--workload", default="ouro1p4b",
-                    choices=["ouro1p4b", "ouro2p6b", "ouro2p6b_fp8_shared", "huginn", "ouro2p6b_chunk", "ouro2p6b_4k",
+                    choices=["ouro1p4b", "ouro2p6b", "ouro2p6b_fp8_shared", "huginn", "huginn_recurrent", "ouro2p6b_chunk", "ouro2p6b_4k",
                              "ouro2p6b_fp8_4k"])
     ap.add_argument("--streaming", action="store_true", help="also replay a layer-by-layer prefill and stream behind it")
     ap.add_argument("--layer-us", type=float, default=200.0, help="simulated prefill time per layer and depth")

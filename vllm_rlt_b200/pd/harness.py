@@ -63,6 +63,10 @@ def make_workload(args, prefill_index: int, lengths=None):
                                         mode=args.mode, seed=seed)
     if name == "huginn":
         return wl.recurrent_depth_dedup(wl.HUGINN_3P5B, requests=args.requests, seed=seed, lengths=lengths)
+    if name == "huginn_recurrent":
+        # prelude (layers 0-1) and coda (6-7) KV exist once; only the core layers 2-5 have one copy per recurrence
+        return wl.recurrent_depth_dedup(wl.HUGINN_3P5B, requests=args.requests, seed=seed, lengths=lengths,
+                                        deep_layers=(2, 3, 4, 5))
     if name == "ouro2p6b_chunk":
         # one 2048-token prefill chunk per request, all planes (what a WCPB step finishes)
         # half of the requests already have a 4096-token prefix on the decode side: only the chunk after it moves
@@ -113,6 +117,7 @@ def run_multi(args, rank: int, world: int) -> None:
         shape = w.shape
     s = shape
     dst_planes = w.dst_planes
+    deep = w.extra.get("deep_layers")
     fan_in = max(len(exchange.pairing(r, world, n_prefill)[2]) for r in range(n_prefill, world))
     width = -(-max(getattr(args, "max_len", 0) or 0, max(w.lengths)) // s.block_size)
     width_t = torch.tensor([width], device=device)
@@ -185,7 +190,7 @@ def run_multi(args, rank: int, world: int) -> None:
                 exit_planes=None if w.exit_planes is None else [w.exit_planes[i] for i in mine],
             )
             edge = dict(d_rank=d_rank, dv=dv, flag_ptr=ptrs[n_pool + slot], sub=sub, mine=mine,
-                        payload=sum(w.ranges[i][1] - w.ranges[i][0] for i in mine) * dst_planes * s.token_plane_bytes)
+                        payload=workloads.subset(w, mine).payload_bytes)
 
             def make_batch(sub=sub):
                 return kh.HandoffBatch(sub["src_tables"], sub["dst_tables"], sub["ranges"], block_size=s.block_size,
@@ -202,7 +207,7 @@ def run_multi(args, rank: int, world: int) -> None:
         counter += 1
         if is_prefill:
             for e in edges:
-                kh.kv_handoff(sv, e["dv"], e["batch"], mode=mode, status=status, variant=args.variant)
+                kh.kv_handoff(sv, e["dv"], e["batch"], mode=mode, status=status, variant=args.variant, deep_layers=deep)
                 kh.kv_signal(e["flag_ptr"], counter)
         else:
             for slot in range(len(sources)):
@@ -311,8 +316,9 @@ def run_multi(args, rank: int, world: int) -> None:
                 else:
                     dist.recv(expect, p)
                     db = torch.tensor(list(reserved[(p, i)][plane]), device=device)[pos // s.block_size]
-                    same = torch.equal(dst.key_cache[db, :, pos % s.block_size].view(store_dtype), expect[0]) and \
-                        torch.equal(dst.value_cache[db, :, pos % s.block_size].view(store_dtype), expect[1])
+                    carried = list(deep) if (deep and plane > 0) else list(range(s.num_layers))
+                    same = torch.equal(dst.key_cache[db, :, pos % s.block_size].view(store_dtype)[:, carried], expect[0][:, carried]) and \
+                        torch.equal(dst.value_cache[db, :, pos % s.block_size].view(store_dtype)[:, carried], expect[1][:, carried])
                     ok *= float(same)
     dist.all_reduce(ok, op=dist.ReduceOp.MIN)
 
@@ -326,7 +332,7 @@ def run_multi(args, rank: int, world: int) -> None:
         if is_prefill:
             for e in edges:
                 b = e["make_batch"]()
-                kh.kv_handoff(sv, e["dv"], b, mode=mode, status=status, variant=args.variant)
+                kh.kv_handoff(sv, e["dv"], b, mode=mode, status=status, variant=args.variant, deep_layers=deep)
                 kh.kv_signal(e["flag_ptr"], counter)
         else:
             for slot in range(len(sources)):
@@ -345,10 +351,10 @@ def run_multi(args, rank: int, world: int) -> None:
             sub = e["sub"]
             b = kh.HandoffBatch([sub["src_tables"][r]], [sub["dst_tables"][r]], [sub["ranges"][r]], block_size=s.block_size,
                                 exit_planes=None if sub["exit_planes"] is None else [sub["exit_planes"][r]], device=device)
-            kh.kv_handoff(sv, e["dv"], b, mode=mode, status=status, variant=args.variant)
+            kh.kv_handoff(sv, e["dv"], b, mode=mode, status=status, variant=args.variant, deep_layers=deep)
             a, z = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a.record(stream)
-            kh.kv_handoff(sv, e["dv"], b, mode=mode, status=status, variant=args.variant)
+            kh.kv_handoff(sv, e["dv"], b, mode=mode, status=status, variant=args.variant, deep_layers=deep)
             counter += 1
             kh.kv_signal(e["flag_ptr"], counter)
             z.record(stream)
@@ -387,7 +393,7 @@ def run_multi(args, rank: int, world: int) -> None:
                 a, z = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 a.record(stream)
                 for e in edges:
-                    kh.kv_handoff(sv, e["dv"], e["batch"], mode=mode, status=status, variant=args.variant)
+                    kh.kv_handoff(sv, e["dv"], e["batch"], mode=mode, status=status, variant=args.variant, deep_layers=deep)
                     kh.kv_signal(e["flag_ptr"], counter)
                 z.record(stream)
             else:

@@ -74,6 +74,12 @@ class Workload:
 
     @property
     def payload_bytes(self) -> int:
+        """Bytes written into the destination pool. With ``extra["deep_layers"]`` (a recurrent-depth model) planes
+        beyond the first carry only those layers."""
+        deep = self.extra.get("deep_layers")
+        if deep and self.dst_planes > 1:
+            per_layer = self.shape.token_plane_bytes // self.shape.num_layers
+            return self.tokens * (self.shape.token_plane_bytes + (self.dst_planes - 1) * len(deep) * per_layer)
         return self.tokens * self.dst_planes * self.shape.token_plane_bytes
 
 
@@ -187,6 +193,7 @@ def per_depth_all_planes(
 def recurrent_depth_dedup(
     shape: KVShape = HUGINN_3P5B, *, requests: int = 2, min_len: int = 1024, max_len: int = 16384,
     min_exit: int = 4, p_exit: float = 0.1, seed: int = SEED_BASE + 3, lengths: list[int] | None = None,
+    deep_layers: tuple[int, ...] | None = None,
 ) -> Workload:
     """Recurrent-depth model: per-token exit recurrence geometric(p) truncated to [min_exit, planes], dedup mode.
 
@@ -210,8 +217,9 @@ def recurrent_depth_dedup(
         description=(
             f"{shape.name} recurrent-depth dedup: {requests} requests, lengths U[{min_len},{max_len}], exit recurrence "
             f"geometric(p={p_exit}) truncated to [{min_exit},{shape.planes}], block {shape.block_size}, seeded random block tables"
+            + (f", planes >= 1 carry layers {list(deep_layers)} only" if deep_layers else "")
         ),
-        extra=dict(mode="dedup"),
+        extra=dict(mode="dedup", **({"deep_layers": tuple(deep_layers)} if deep_layers else {})),
     )
 
 
