@@ -39,8 +39,8 @@ def run_staged(args, rank: int, world: int) -> None:
     local = int(os.environ.get("LOCAL_RANK", rank))
     device = torch.device("cuda", local)
     torch.cuda.set_device(device)
-    if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
-        os.environ["NCCL_DEBUG"] = "WARN"  # keep NCCL's version banner off stdout: rank 0 prints exactly one JSON line
+    # NCCL prints its version banner to stdout at the VERSION and WARN levels; rank 0 must print exactly one JSON line
+    os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
     dist.init_process_group("nccl", device_id=device)
     pairs = world // 2
     is_prefill, index, partners = exchange.pairing(rank, world)
