@@ -6,6 +6,7 @@ relayed by hand the way the coordinator relays them. Destination bytes are compa
 """
 
 from contextlib import nullcontext
+from dataclasses import dataclass
 from types import SimpleNamespace
 
 import numpy as np
@@ -78,14 +79,15 @@ def pool_rows(pool, tables, start, end):
     return torch.cat(out)
 
 
-def run_handoff(p, d, tid, tokens, *, chunks=((0, None),), params=SimpleNamespace(max_tokens=4)):
-    """Relay the control messages by hand; returns the source request."""
-    from dataclasses import dataclass
+@dataclass
+class Params:
+    """Stands in for SamplingParams: the connector only narrows ``max_tokens`` on the prefill side."""
 
-    @dataclass
-    class Params:
-        max_tokens: int = 4
+    max_tokens: int = 4
 
+
+def run_handoff(p, d, tid, tokens, *, chunks=((0, None),)):
+    """Relay the control messages by hand; returns the source request and the decode side's reservation."""
     prompt = list(range(1, tokens + 1))
     d.connector.command(dict(kind="reserve", tid=tid, tokens=prompt, params=Params(), peer="prefill-0"))
     (reserved,) = d.take("reserved")
@@ -173,12 +175,6 @@ def test_chunks_respect_the_byte_limit_and_sequence_numbers_are_dense():
 def test_prefix_already_on_the_decode_side_is_skipped():
     p, d = make_pair()
     prompt = list(range(8))
-    from dataclasses import dataclass
-
-    @dataclass
-    class Params:
-        max_tokens: int = 4
-
     d.connector.command(dict(kind="reserve", tid="r", tokens=prompt, params=Params(), peer="prefill-0"))
     (reserved,) = d.take("reserved")
     d.pool._allocations["r"].prefix = 4  # the decode side found the first block in its prefix cache
@@ -232,12 +228,6 @@ def test_backpressure_and_cancellation_keep_resources_until_safe():
 
 def test_rejection_when_the_decode_pool_is_full_and_protocol_errors():
     p, d = make_pair(blocks=8)
-    from dataclasses import dataclass
-
-    @dataclass
-    class Params:
-        max_tokens: int = 4
-
     d.connector.command(dict(kind="reserve", tid="ok", tokens=list(range(12)), params=Params(), peer="prefill-0"))
     assert d.take("reserved")
     d.connector.command(dict(kind="reserve", tid="big", tokens=list(range(8)), params=Params(), peer="prefill-0"))

@@ -11,7 +11,7 @@ from types import SimpleNamespace
 import pytest
 import torch
 
-from tests.test_connector_cpu import Worker, pool_rows
+from tests.test_connector_cpu import Params, Worker, pool_rows
 
 pytestmark = pytest.mark.gpu
 
@@ -26,13 +26,7 @@ def pump(p, d, until, limit=20.0):
 
 @pytest.mark.parametrize("fp8", [False, True])
 def test_handoff_through_connector_transport_and_kernels(fp8):
-    from dataclasses import dataclass
-
     from vllm_rlt_b200.pd.config import PDConfig
-
-    @dataclass
-    class Params:
-        max_tokens: int = 4
 
     per_token = 2 * 3 * (2 * 8 * (1 if fp8 else 2) + (2 * 4 if fp8 else 0)) * 2
     config = PDConfig(transfer_chunk_bytes=5 * per_token + 100, max_inflight_bytes=16 * per_token)
@@ -87,13 +81,7 @@ def test_chunks_leave_behind_the_producer_event_without_another_progress_pass():
     """The reference submits a chunk only when a later ``progress()`` pass finds its event fired (the commit tail,
     vllm_rlt/pd/config.py:10-15). Here the copies are queued at once behind the event on the device: the decode
     side receives every notification although the prefill worker's host never runs ``progress()`` again."""
-    from dataclasses import dataclass
-
     from vllm_rlt_b200.pd.config import PDConfig
-
-    @dataclass
-    class Params:
-        max_tokens: int = 4
 
     per_token = 2 * 3 * (2 * 8 * 2) * 2
     config = PDConfig(transfer_chunk_bytes=6 * per_token, max_inflight_bytes=64 * per_token)
