@@ -20,6 +20,7 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--mode", default="exit_only", choices=["exit_only", "all"])
     ap.add_argument("--variant", type=int, default=0, help="kernel flavour (RltOptions.variant)")
+    ap.add_argument("--pull", action="store_true", help="run the kernel on the destination GPU and read the source over the link")
     args = ap.parse_args()
 
     import torch
@@ -33,6 +34,8 @@ def main() -> None:
     if torch.cuda.device_count() < 2:
         raise SystemExit("needs two GPUs")
     peer.enable_peer_access(0, 1)
+    peer.enable_peer_access(1, 0)
+    run_on = 1 if args.pull else 0
     torch.cuda.set_device(0)
     w = workloads.last_exited_exit_only(requests=args.requests, mode=args.mode)
     s = w.shape
@@ -43,9 +46,11 @@ def main() -> None:
         t.view(torch.uint8).fill_(0xA5)
     torch.cuda.synchronize(1)
     sv, dv = kh.PoolView.from_cache(src), kh.PoolView.from_cache(dst)
+    torch.cuda.synchronize(0)
+    torch.cuda.set_device(run_on)
     batch = kh.HandoffBatch(w.src_tables, w.dst_tables, w.ranges, block_size=s.block_size, exit_planes=w.exit_planes,
-                            device="cuda:0")
-    status = kh.new_status("cuda:0")
+                            device=f"cuda:{run_on}")
+    status = kh.new_status(f"cuda:{run_on}")
     mode = kh.MODE_EXIT_ONLY if args.mode == "exit_only" else kh.MODE_ALL_PLANES
     times = []
     for i in range(1 + args.steps):
@@ -53,10 +58,11 @@ def main() -> None:
         a.record()
         kh.kv_handoff(sv, dv, batch, mode=mode, status=status, variant=args.variant)
         b.record()
-        torch.cuda.synchronize(0)
+        torch.cuda.synchronize(run_on)
         if i:
             times.append(a.elapsed_time(b))
     kh.raise_for_status(status)
+    torch.cuda.set_device(0)
     # compare on the destination device: bring the expected rows of request 0 over with a plain copy
     n = min(64, w.lengths[0])
     import numpy as np
@@ -72,7 +78,8 @@ def main() -> None:
         got = dst.key_cache[db, :, (pos % s.block_size).to("cuda:1")]
         ok = ok and bool(torch.equal(want.view(torch.int16), got.view(torch.int16)))
     ms = statistics.median(times)
-    print(json.dumps({"payload_bytes": w.payload_bytes, "ms": ms, "gbps": w.payload_bytes / ms / 1e6, "verified": ok}), flush=True)
+    print(json.dumps({"direction": "pull (kernel on the destination GPU)" if args.pull else "push (kernel on the source GPU)",
+                      "payload_bytes": w.payload_bytes, "ms": ms, "gbps": w.payload_bytes / ms / 1e6, "verified": ok}), flush=True)
 
 
 if __name__ == "__main__":
