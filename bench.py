@@ -30,6 +30,8 @@ FALLBACK_HBM_GBS = 6650.0
 NVLINK_MEASURED_GBS = 770.0
 # link bytes per payload byte for writes over NVLink (ncu: nvltx__bytes.sum / nvltx__bytes_data_user.sum of the handoff kernel)
 NVLINK_WRITE_OVERHEAD = 1.1875
+# the same for read responses when the destination GPU pulls (ncu: nvlrx__bytes.sum / nvlrx__bytes_data_user.sum)
+NVLINK_READ_OVERHEAD = 1.125
 # DRAM traffic per algorithmic byte of table_copy_kernel, from the ncu capture summarised under profiles/
 TRAFFIC_PER_ALGORITHMIC_BYTE = 0.98
 
@@ -490,6 +492,8 @@ def main():
     ap.add_argument("--streaming", action="store_true", help="also replay a layer-by-layer prefill and stream behind it")
     ap.add_argument("--layer-us", type=float, default=200.0, help="simulated prefill time per layer and depth")
     ap.add_argument("--layers-per-slice", type=int, default=4)
+    ap.add_argument("--direction", default="pull", choices=["push", "pull"],
+                    help="N >= 2, direct path: the prefill GPU writes into the decode pool, or the decode GPU reads the prefill pool")
     ap.add_argument("--path", default="direct", choices=["direct", "staged"],
                     help="N >= 2: one kernel that writes destination blocks over NVLink, or pack into peer staging + scatter")
     args = ap.parse_args()
@@ -506,6 +510,10 @@ def main():
             from vllm_rlt_b200.pd import staged
 
             staged.run_staged(args, rank, world)
+        elif args.direction == "pull" and not args.streaming:
+            from vllm_rlt_b200.pd import pull_harness
+
+            pull_harness.run_pull(args, rank, world)
         else:
             from vllm_rlt_b200.pd import harness
 

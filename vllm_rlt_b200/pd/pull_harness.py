@@ -1,0 +1,307 @@
+"""Multi-GPU handoff, pull direction: the decode GPU reads the prefill GPU's pool over NVLink.
+
+Same deployment shape, workloads, metadata exchange and timing rules as ``harness.run_multi`` (the push
+direction), with the kernel on the other side of the link: the prefill worker only posts a "KV ready" flag
+behind its producer, the decode worker waits for it (bounded), runs ``rlt_kv_handoff`` with the *source*
+pool given as peer pointers and its own pool as destination, and posts a "done" flag into the prefill GPU's
+memory so that the source blocks may be released.
+
+Why it exists: NVLink charges writes 18.75 % of protocol bytes and read responses 12.5 %, and the read
+requests travel on the opposite, otherwise idle direction. Measured with the link counters on this kernel:
+push 713 GB/s of payload (847 GB/s raw), pull 769 GB/s of payload (865 GB/s raw) per pair. The price is
+that the copy runs on the decode GPU's SMs instead of the prefill GPU's.
+"""
+
+from __future__ import annotations
+
+import json
+import os
+import random
+import statistics
+import time
+
+import numpy as np
+
+
+def run_pull(args, rank: int, world: int) -> None:
+    import torch
+    import torch.distributed as dist
+
+    import bench
+    from vllm_rlt_b200 import workloads
+    from vllm_rlt_b200.core.kv_pool import KVPool
+    from vllm_rlt_b200.kernels import kv_handoff as kh
+    from vllm_rlt_b200.pd import exchange
+    from vllm_rlt_b200.pd import peer as peerlib
+    from vllm_rlt_b200.pd.harness import MODES, make_workload
+
+    if world != args.gpus:
+        raise SystemExit("--gpus must equal WORLD_SIZE")
+    n_prefill = args.prefill or world // 2
+    n_decode = world - n_prefill
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    device = torch.device("cuda", local)
+    torch.cuda.set_device(device)
+    os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
+    dist.init_process_group("nccl", device_id=device)
+    is_prefill, index, partners = exchange.pairing(rank, world, n_prefill)
+    mode = MODES[args.mode]
+
+    def partners_of(r):
+        return exchange.pairing(r, world, n_prefill)[2]
+
+    def assigned(p_rank: int, d_rank: int, w):
+        ps = partners_of(p_rank)
+        return [i for i in range(len(w.lengths)) if ps[i % len(ps)] == d_rank]
+
+    if is_prefill:
+        w = make_workload(args, index)
+        per_source = {}
+    else:
+        per_source = {p: make_workload(args, p) for p in partners}
+        w = next(iter(per_source.values()))
+    s = w.shape
+    dst_planes = w.dst_planes
+    deep = w.extra.get("deep_layers")
+    kw = dict(device=device, kv_cache_dtype="fp8_e4m3" if s.fp8 else "auto")
+    fan = max(len(partners_of(r)) for r in range(world))
+    n_pool = 4 if s.fp8 else 2
+
+    # ---- set-up: pools, reservation on the decode side, handles of pools and flags to everyone --------------
+    handle_msg = torch.zeros((4 + fan, exchange.HANDLE_ROW), dtype=torch.uint8, device=device)
+    flags = torch.zeros(fan, dtype=torch.int64, device=device)  # prefill: "done" per partner; decode: "ready" per source
+    if is_prefill:
+        pool = KVPool(s.num_layers, s.num_kv_heads, s.head_dim, w.src_blocks, s.block_size, s.planes, **kw)
+        bench.fill_source(pool, s, workloads.SEED_BASE + index)
+    else:
+        total_blocks = sum(
+            sum(-(-wp.lengths[i] // s.block_size) for i in assigned(p, rank, wp)) * dst_planes for p, wp in per_source.items())
+        pool = KVPool(s.num_layers, s.num_kv_heads, s.head_dim, max(total_blocks, 1), s.block_size, dst_planes, **kw)
+        for t in (pool.key_cache, pool.value_cache):
+            t.view(torch.uint8).fill_(0xA5)
+        random.Random(workloads.SEED_BASE + 1000 + index).shuffle(pool._free_blocks)
+        reserved = {}
+        for p, wp in per_source.items():
+            for i in assigned(p, rank, wp):
+                reserved[(p, i)] = pool.reserve_transfer(f"p{p}-r{i}", wp.lengths[i])
+                assert reserved[(p, i)] is not None
+    tensors = [pool.key_cache, pool.value_cache] + ([pool.key_scale, pool.value_scale] if s.fp8 else [])
+    rows = [peerlib.export_tensor(t) for t in tensors]
+    rows += [rows[0]] * (4 - len(rows))
+    flag_export = peerlib.export_tensor(flags)
+    rows += [dict(flag_export, offset=flag_export["offset"] + 8 * j) for j in range(fan)]
+    handle_msg.copy_(exchange.encode_handles(rows))
+    all_handles = [torch.zeros_like(handle_msg) for _ in range(world)]
+    dist.all_gather(all_handles, handle_msg)
+    torch.cuda.synchronize()
+
+    status = kh.new_status(device)
+    mapping = peerlib.PeerMapping()
+    edges = []
+    if is_prefill:
+        for j, d_rank in enumerate(partners):
+            mine = assigned(rank, d_rank, w)
+            if not mine:
+                continue
+            slot = partners_of(d_rank).index(rank)
+            ptrs = [mapping.pointer(e) for e in exchange.decode_handles(all_handles[d_rank])]
+            edges.append(dict(ready_ptr=ptrs[4 + slot], done=flags.data_ptr() + 8 * j, mine=mine,
+                              payload=workloads.subset(w, mine).payload_bytes))
+    else:
+        dv = kh.PoolView.from_cache(pool)
+        for slot, p in enumerate(partners):
+            wp = per_source[p]
+            mine = assigned(p, rank, wp)
+            if not mine:
+                continue
+            j = partners_of(p).index(rank)
+            ptrs = [mapping.pointer(e) for e in exchange.decode_handles(all_handles[p])]
+            scales = dv.scales.rebased(ptrs[2], ptrs[3]) if s.fp8 else None
+            sv = kh.PoolView(dv.codes.rebased(ptrs[0], ptrs[1]), scales, wp.src_blocks, s.block_size, s.num_layers, s.planes, -1)
+            sub = dict(src=[wp.src_tables[i] for i in mine], dst=[reserved[(p, i)] for i in mine],
+                       ranges=[wp.ranges[i] for i in mine],
+                       exits=None if wp.exit_planes is None else [wp.exit_planes[i] for i in mine])
+
+            def make_batch(sub=sub, wp=wp):
+                return kh.HandoffBatch(sub["src"], sub["dst"], sub["ranges"], block_size=s.block_size, exit_planes=sub["exits"],
+                                       src_blocks=wp.src_blocks, dst_blocks=pool.num_blocks, device=device)
+
+            edges.append(dict(sv=sv, ready=flags.data_ptr() + 8 * slot, done_ptr=ptrs[4 + j], sub=sub, make_batch=make_batch,
+                              batch=make_batch(), mine=mine, source=p, payload=workloads.subset(wp, mine).payload_bytes))
+    my_payload = sum(e["payload"] for e in edges) if not is_prefill else 0
+    counter = 0
+
+    def step(fresh_batches=False):
+        nonlocal counter
+        counter += 1
+        if is_prefill:
+            for e in edges:
+                kh.kv_signal(e["ready_ptr"], counter)  # behind the producer of the KV on this stream
+            for e in edges:
+                kh.kv_wait(e["done"], counter, kh._lib.MAX_WAIT_NS, status)  # the source may be released after this
+        else:
+            for e in edges:
+                b = e["make_batch"]() if fresh_batches else e["batch"]
+                kh.kv_wait(e["ready"], counter, kh._lib.MAX_WAIT_NS, status)
+                kh.kv_handoff(e["sv"], dv, b, mode=mode, status=status, variant=args.variant, deep_layers=deep)
+                kh.kv_signal(e["done_ptr"], counter)
+
+    for _ in range(args.warmup):
+        step()
+    torch.cuda.synchronize()
+    kh.raise_for_status(status)
+    dist.barrier()
+    sampler = bench.ClockSampler(bench.visible_device_index(local)) if rank == world - 1 else None
+    if sampler:
+        sampler.start()
+        time.sleep(0.3)
+    dist.barrier()
+    torch.cuda.synchronize()
+    stream = torch.cuda.current_stream()
+    launches0 = kh.kernel_launches()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    events = []
+    t0.record(stream)
+    for _ in range(args.steps):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(stream)
+        step()
+        b.record(stream)
+        events.append((a, b))
+    t1.record(stream)
+    torch.cuda.synchronize()
+    dist.barrier()
+    torch.cuda.synchronize()
+    launches = kh.kernel_launches() - launches0
+    kh.raise_for_status(status)
+    clocks = sampler.stop() if sampler else None
+    clock_box = [clocks]
+    dist.broadcast_object_list(clock_box, src=world - 1)
+    total_ms = torch.tensor([t0.elapsed_time(t1)], device=device)
+    dist.all_reduce(total_ms, op=dist.ReduceOp.MAX)
+    kernel_ms = statistics.mean(a.elapsed_time(b) for a, b in events)
+    k_ms = torch.tensor([kernel_ms if not is_prefill else 0.0], device=device)
+    dist.all_reduce(k_ms, op=dist.ReduceOp.MAX)
+    n_launch = torch.tensor([launches], device=device)
+    dist.all_reduce(n_launch)
+    payload_all = torch.tensor([float(my_payload)], device=device, dtype=torch.float64)
+    dist.all_reduce(payload_all)
+
+    # ---- verification: the source side gathers what some transferred tokens should hold, the decode side compares
+    ok = torch.ones(1, device=device)
+    for p in range(n_prefill):
+        for d_rank in partners_of(p):
+            if rank not in (p, d_rank):
+                continue
+            wp = w if rank == p else per_source[p]
+            mine = assigned(p, d_rank, wp)
+            if not mine:
+                continue
+            i = mine[-1]
+            lo, hi = wp.ranges[i]
+            n = min(48, hi - lo)
+            expect = torch.zeros((2, n, s.num_layers, s.num_kv_heads, s.head_dim * s.element), dtype=torch.uint8, device=device)
+            pos = torch.arange(lo, lo + n, device=device)
+            for plane in range(dst_planes):
+                if rank == p:
+                    if wp.exit_planes is None:
+                        sp = torch.full((n,), plane, device=device)
+                    else:
+                        e = torch.tensor(np.asarray(wp.exit_planes[i][lo : lo + n]), device=device).long()
+                        sp = e if args.mode == "exit_only" else torch.clamp(e, max=plane)
+                    st = torch.tensor(np.stack([np.asarray(t) for t in wp.src_tables[i]]), device=device).long()
+                    sb = st[sp, pos // s.block_size]
+                    expect[0] = pool.key_cache[sb, :, pos % s.block_size].view(torch.uint8)
+                    expect[1] = pool.value_cache[sb, :, pos % s.block_size].view(torch.uint8)
+                    dist.send(expect, d_rank)
+                else:
+                    dist.recv(expect, p)
+                    db = torch.tensor(list(reserved[(p, i)][plane]), device=device)[pos // s.block_size]
+                    carried = list(deep) if (deep and plane > 0) else list(range(s.num_layers))
+                    same = torch.equal(pool.key_cache[db, :, pos % s.block_size].view(torch.uint8)[:, carried], expect[0][:, carried]) and \
+                        torch.equal(pool.value_cache[db, :, pos % s.block_size].view(torch.uint8)[:, carried], expect[1][:, carried])
+                    ok *= float(same)
+    dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+
+    # ---- end to end: the decode side stages tables from the host every step, launches, reads the status back
+    e2e = []
+    for i in range(args.warmup + args.steps):
+        dist.barrier()
+        torch.cuda.synchronize()
+        t_start = time.perf_counter()
+        step(fresh_batches=True)
+        kh.raise_for_status(status)
+        if i >= args.warmup:
+            e2e.append(time.perf_counter() - t_start)
+    e2e_s = torch.tensor([statistics.mean(e2e)], device=device, dtype=torch.float64)
+    dist.all_reduce(e2e_s, op=dist.ReduceOp.MAX)
+    staged_bytes = torch.tensor([0 if is_prefill else sum(e["batch"].metadata_bytes for e in edges)], device=device)
+    dist.all_reduce(staged_bytes)
+
+    # ---- per-request latency between rank 0 and its first partner: ready flag -> pull -> done flag, timed on the prefill stream
+    lat = []
+    first_d = partners_of(0)[0]
+    probe = min(16, len(assigned(0, first_d, w if rank == 0 else (per_source.get(0) or w))))
+    for r in range(probe):
+        for repeat in range(2):
+            dist.barrier()
+            counter += 1
+            if rank == 0:
+                e = edges[0]
+                a, z = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record(stream)
+                kh.kv_signal(e["ready_ptr"], counter)
+                kh.kv_wait(e["done"], counter, kh._lib.MAX_WAIT_NS, status)
+                z.record(stream)
+                torch.cuda.synchronize()
+                if repeat:
+                    lat.append(a.elapsed_time(z))
+            elif rank == first_d:
+                e = next(x for x in edges if x["source"] == 0)
+                sub = e["sub"]
+                b = kh.HandoffBatch([sub["src"][r]], [sub["dst"][r]], [sub["ranges"][r]], block_size=s.block_size,
+                                    exit_planes=None if sub["exits"] is None else [sub["exits"][r]], device=device)
+                kh.kv_wait(e["ready"], counter, kh._lib.MAX_WAIT_NS, status)
+                kh.kv_handoff(e["sv"], dv, b, mode=mode, status=status, variant=args.variant, deep_layers=deep)
+                kh.kv_signal(e["done_ptr"], counter)
+                torch.cuda.synchronize()
+    kh.raise_for_status(status)
+    torch.cuda.synchronize()
+    dist.barrier()
+    mapping.close()
+    dist.barrier()
+
+    if rank == 0:
+        ms_per_step = float(total_ms.item()) / args.steps
+        total_payload = float(payload_all.item())
+        value = total_payload / (ms_per_step * 1e-3) / 1e9
+        links = min(n_prefill, n_decode)
+        per_link = value / links
+        line = {
+            "metric": bench.METRIC, "value": value, "unit": bench.UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "u8", "data": "synthetic",
+            "config": bench.config_of(w, args, {
+                "split": f"{n_prefill}P:{n_decode}D", "variant": args.variant, "workload_name": args.workload,
+                "per_prefill_worker": w.description, "payload_bytes": total_payload,
+                "transport": "decode GPU pulls through peer pointers over NVLink (CUDA IPC mapping); ready and done flags per step"}),
+            "roofline": {"bound": "nvlink", "achieved": per_link, "peak": bench.NVLINK_MEASURED_GBS, "unit": "GB/s",
+                         "frac": per_link / bench.NVLINK_MEASURED_GBS, "traffic": None,
+                         "peak_source": "measured peer copy on this pool, 770 GB/s per direction per GPU (nominal 900)",
+                         "kernel": "table_copy_kernel", "algorithmic_bytes_per_launch": w.payload_bytes,
+                         "kernel_ms": float(k_ms.item()), "frac_of_nominal_900": per_link / 900.0,
+                         "raw_link_gbps": per_link * bench.NVLINK_READ_OVERHEAD,
+                         "raw_link_frac_of_900": per_link * bench.NVLINK_READ_OVERHEAD / 900.0,
+                         "raw_link_note": "read responses carry 12.5 % of protocol bytes on top of the payload (ncu nvlrx__bytes "
+                                          "counters of this kernel); requests use the opposite direction",
+                         "what": "aggregate payload rate / min(prefill, decode) GPUs: the per-GPU link rate of the busier side"},
+            "per_pair_gbps": per_link,
+            "e2e": {"value": total_payload / float(e2e_s.item()) / 1e9, "unit": bench.UNIT,
+                    "h2d_bytes_per_step": int(staged_bytes.item()), "d2h_bytes_per_step": 16 * n_decode, "ms_per_step": float(e2e_s.item()) * 1e3,
+                    "note": "tables, ranges and exit planes are staged from the host on the decode ranks every step"},
+            "latency_ms": {"p50": statistics.median(lat), "max": max(lat), "min": min(lat),
+                           "what": "rank 0 -> its first decode partner: ready flag, pull, done flag; CUDA events on the prefill stream"},
+            "gpu_launches": int(n_launch.item()), "clocks": clock_box[0], "verified": bool(ok.item() == 1.0),
+        }
+        print(json.dumps(line), flush=True)
+    dist.destroy_process_group()
