@@ -9,6 +9,8 @@ KV bytes never pass through here.
 
 from __future__ import annotations
 
+import os
+
 import numpy as np
 import torch
 
@@ -78,3 +80,22 @@ def pairing(rank: int, world: int, prefill: int | None = None):
     else:
         partners = [p for p in range(prefill) if p % decode == index] if prefill >= decode else [index % prefill]
     return is_prefill, index, partners
+
+
+def init_process_group_quietly(device):
+    """Create the NCCL group with stdout pointed at stderr for the duration: NCCL prints its version banner to
+    stdout when its debug level is VERSION or WARN, and rank 0 must print exactly one JSON line there."""
+    import sys
+
+    import torch.distributed as dist
+
+    sys.stdout.flush()
+    saved = os.dup(1)
+    os.dup2(2, 1)
+    try:
+        dist.init_process_group("nccl", device_id=device)
+        dist.barrier()
+    finally:
+        sys.stdout.flush()
+        os.dup2(saved, 1)
+        os.close(saved)

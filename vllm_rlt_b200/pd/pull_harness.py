@@ -42,8 +42,7 @@ def run_pull(args, rank: int, world: int) -> None:
     local = int(os.environ.get("LOCAL_RANK", rank))
     device = torch.device("cuda", local)
     torch.cuda.set_device(device)
-    os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
-    dist.init_process_group("nccl", device_id=device)
+    exchange.init_process_group_quietly(device)
     is_prefill, index, partners = exchange.pairing(rank, world, n_prefill)
     mode = MODES[args.mode]
 

@@ -39,9 +39,7 @@ def run_staged(args, rank: int, world: int) -> None:
     local = int(os.environ.get("LOCAL_RANK", rank))
     device = torch.device("cuda", local)
     torch.cuda.set_device(device)
-    # NCCL prints its version banner to stdout at the VERSION and WARN levels; rank 0 must print exactly one JSON line
-    os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
-    dist.init_process_group("nccl", device_id=device)
+    exchange.init_process_group_quietly(device)
     pairs = world // 2
     is_prefill, index, partners = exchange.pairing(rank, world)
     partner = partners[0]
