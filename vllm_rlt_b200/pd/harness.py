@@ -28,16 +28,30 @@ import numpy as np
 MODES = {"exit_only": 2, "dedup": 1, "all": 0}
 
 
+POOL_LIMIT_BYTES = 165 << 30  # what one pool may take of a 180 GB GPU
+
+
 def make_workload(args, prefill_index: int, lengths=None):
     """The workload of one prefill worker; every rank can rebuild any worker's from its index.
 
     All workers get the same prompt lengths (those of worker 0), so that per-GPU work is identical at
-    every N (weak scaling); block tables and exit planes are seeded per worker.
+    every N (weak scaling); block tables and exit planes are seeded per worker. A workload whose source or
+    destination pool cannot fit one GPU is refused here, before anything is allocated.
     """
+    w = _make_workload(args, prefill_index, lengths)
+    for side, blocks in (("source", w.src_blocks), ("destination", w.dst_blocks)):
+        need = blocks * w.shape.block_bytes
+        if need > POOL_LIMIT_BYTES:
+            raise SystemExit(f"workload {getattr(args, 'workload', 'ouro1p4b')!r} with {len(w.lengths)} requests needs a "
+                             f"{need / 2**30:.0f} GiB {side} pool; run it in waves with a smaller --requests")
+    return w
+
+
+def _make_workload(args, prefill_index: int, lengths=None):
     from vllm_rlt_b200 import workloads as wl
 
     if lengths is None and prefill_index != 0:
-        lengths = make_workload(args, 0).lengths
+        lengths = _make_workload(args, 0).lengths
     seed = wl.SEED_BASE + 1 + 17 * prefill_index
     name = getattr(args, "workload", "ouro1p4b")
     if name == "ouro1p4b":
