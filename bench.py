@@ -459,7 +459,8 @@ def run_single(args):
                      "traffic": TRAFFIC_PER_ALGORITHMIC_BYTE * algorithmic, "peak_source": peak_note,
                      "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of a 2-request capture of the same "
                                        "kernel (traffic / algorithmic = 0.98), scaled by tokens",
-                     "kernel": "table_copy_kernel", "algorithmic_bytes_per_launch": algorithmic, "kernel_ms": avg_kernel_ms},
+                     "kernel": "table_fan_kernel" if w.extra.get("mode") == "dedup" and args.variant & 0xf not in (3, 4, 6) else "table_copy_kernel",
+                     "algorithmic_bytes_per_launch": algorithmic, "kernel_ms": avg_kernel_ms},
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": batch.metadata_bytes,
                 "d2h_bytes_per_step": 16, "ms_per_step": statistics.mean(e2e_times) * 1e3,
                 "note": "KV pools are device-resident by the API's nature; host inputs are tables, ranges and exit planes"},

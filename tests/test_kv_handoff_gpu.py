@@ -19,8 +19,9 @@ from tests.gpu_support import GpuPool, assert_pools_equal
 pytestmark = pytest.mark.gpu
 
 # kernel flavours: 0 = register path (16-byte loads/stores), 3 and 4 = cp.async.bulk rings of 8 x 4 KiB / 4 x 8 KiB,
-# 5 = register path with 32-byte loads/stores
-VARIANTS = [0, 3, 4, 5]
+# 5 = register path with 32-byte loads/stores, 6 = register path with the pool-to-pool dedup walking destination planes
+# (the default walks source planes and fans each row out; see the fan-out tests below)
+VARIANTS = [0, 3, 4, 5, 6]
 
 
 def kh():
@@ -514,4 +515,95 @@ def test_recurrent_depth_model_carries_only_its_recurrent_layers_in_deeper_plane
                 for a, b in zip(full.tensors(), D.tensors()):
                     for layer in layers:
                         b.data[table[t // page], layer, t % page] = a.data[table[t // page], layer, t % page]
+    assert_pools_equal(gd, D)
+
+
+# ----------------------------------------------------------------------------- pool-to-pool dedup, fan-out walk
+
+
+@pytest.mark.parametrize("planes,page,fp8", [(32, 16, False), (8, 64, True), (2, 1, False), (64, 4, False)])
+def test_dedup_fan_out_reads_each_row_once_and_fills_every_deeper_plane(planes, page, fp8):
+    """Many planes, geometric exits: the default dedup handoff (one unit per SOURCE plane, rows of tokens that
+    stop there stored to every deeper plane) equals the oracle and the walk over destination planes (variant 6)."""
+    k = kh()
+    kind = "fp8" if fp8 else "bf16"
+    lengths = [3 * page + 1, page, 2 * page - 1, 1]
+    blocks = sum(-(-n // page) for n in lengths) * planes + 3
+    shape = (3, 2, 16, blocks, page, planes)
+    rng, nrng = random.Random(planes * 131 + page), np.random.default_rng(planes)
+    P, D = oracle_pool(kind, shape), sentinel_destination(kind, shape)
+    P.fill_random(nrng)
+    P.shuffle_free_list(rng)
+    D.shuffle_free_list(rng)
+    reqs, exits = [], []
+    for i, n in enumerate(lengths):
+        assert P.allocate(f"r{i}", n) and D.allocate(f"r{i}", n)
+        e = [min(planes - 1, int(nrng.geometric(0.25)) - 1) for _ in range(n)]
+        e[0], e[-1] = planes - 1, 0  # both ends of the range occur
+        for pos in range(n):
+            P.finalize_token(f"r{i}", pos, e[pos])
+        start = rng.choice([0, rng.randrange(n)])
+        reqs.append((f"r{i}", start, rng.randint(start + 1, n)))
+        exits.append(e)
+    results = []
+    for variant in (0, 6):
+        gp, gd = GpuPool(P), GpuPool(D)
+        batch = k.HandoffBatch(
+            [P.plane_block_tables(r) for r, *_ in reqs], [D.plane_block_tables(r) for r, *_ in reqs],
+            [(s, e) for _, s, e in reqs], block_size=page, exit_planes=exits,
+            src_blocks=P.num_blocks, dst_blocks=D.num_blocks)
+        status = k.new_status()
+        k.kv_handoff(gp.view(), gd.view(), batch, mode=k.MODE_DEDUP, status=status, variant=variant)
+        k.raise_for_status(status)
+        results.append(gd)
+        assert_pools_equal(gp, P)  # the source is only read
+    for i, (r, s, e) in enumerate(reqs):
+        ho.handoff_rows(P, D, P.plane_block_tables(r), D.plane_block_tables(r), s, e, mode=ho.MODE_DEDUP, exit_planes=exits[i])
+    for gd in results:
+        assert_pools_equal(gd, D)
+
+
+def test_dedup_fan_out_reports_bad_exit_planes_and_bad_deeper_blocks():
+    k = kh()
+    kind, shape = "bf16", (2, 2, 8, 24, 4, 3)
+    P, D = oracle_pool(kind, shape), sentinel_destination(kind, shape)
+    P.fill_random(np.random.default_rng(5))
+    P.allocate("a", 8)
+    D.allocate("a", 8)
+    tables_s, tables_d = P.plane_block_tables("a"), D.plane_block_tables("a")
+    good = [0, 1, 2, 0, 1, 2, 0, 1]
+    for pos, e in enumerate(good):
+        P.finalize_token("a", pos, e)
+
+    # an exit plane outside [0, planes): reported, that token is skipped on every plane, the others arrive
+    for bad in (-1, 3):
+        D.fill_sentinel()
+        gp, gd = GpuPool(P), GpuPool(D)
+        exits = list(good)
+        exits[5] = bad
+        batch = k.HandoffBatch([tables_s], [tables_d], [(0, 8)], block_size=4, exit_planes=[exits])
+        status = k.new_status()
+        k.kv_handoff(gp.view(), gd.view(), batch, mode=k.MODE_DEDUP, status=status)
+        with pytest.raises(ValueError, match="exit plane"):
+            k.raise_for_status(status)
+        assert status.tolist()[0] == 3 and status.tolist()[3] == bad
+        ho.handoff_rows(P, D, tables_s, tables_d, 0, 5, mode=ho.MODE_DEDUP, exit_planes=exits)
+        ho.handoff_rows(P, D, tables_s, tables_d, 6, 8, mode=ho.MODE_DEDUP, exit_planes=exits)
+        assert_pools_equal(gd, D)
+
+    # a block id outside the pool on a deeper destination plane: reported; that plane's block keeps the sentinel,
+    # the rows of the valid planes arrive
+    D.fill_sentinel()
+    gp, gd = GpuPool(P), GpuPool(D)
+    broken = [list(t) for t in tables_d]
+    broken[2][0] = 77
+    batch = k.HandoffBatch([tables_s], [broken], [(0, 8)], block_size=4, exit_planes=[good])
+    status = k.new_status()
+    k.kv_handoff(gp.view(), gd.view(), batch, mode=k.MODE_DEDUP, status=status)
+    with pytest.raises(ValueError, match="physical block outside registered pool"):
+        k.raise_for_status(status)
+    assert status.tolist()[0] == 2 and status.tolist()[3] == 77
+    ho.handoff_rows(P, D, tables_s, tables_d, 0, 8, mode=ho.MODE_DEDUP, exit_planes=good)
+    for t in D.tensors():
+        t.data[tables_d[2][0]] = 0xA5
     assert_pools_equal(gd, D)

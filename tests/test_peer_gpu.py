@@ -91,3 +91,31 @@ def test_cross_gpu_exit_only_takes_each_token_at_its_exit_plane(two_gpus, case, 
     for r, tables in zip(reqs, one):
         ho.handoff_rows(P, D, r["src_tables"], tables, 0, r["tokens"], mode=ho.MODE_EXIT_ONLY, exit_planes=r["exit_planes"])
     assert_pools_equal(gd, D)
+
+
+@pytest.mark.parametrize("case", FULL_DEPTH, ids=lambda c: c["name"])
+@pytest.mark.parametrize("direction", ["push", "pull"])
+def test_cross_gpu_dedup_rebuilds_the_reference_destination(two_gpus, case, direction):
+    """Dedup between two GPUs: rows up to each token's exit plane are read once and stored to every plane they
+    fill; the destination equals what the reference wrote by sending all planes."""
+    from vllm_rlt_b200.kernels import kv_handoff as k
+
+    arrays = golden_npz(case["name"])
+    P = oracle_pool(case["kind"], case["shape"])
+    load_pool(P, arrays, "src_after_")
+    D = sentinel_destination(case["kind"], case["shape"])
+    reqs = case["requests"]
+    gp, gd = GpuPool(P, device="cuda:0"), GpuPool(D, device="cuda:1")
+    torch.cuda.synchronize(0)
+    torch.cuda.synchronize(1)
+    run_on = 0 if direction == "push" else 1
+    with torch.cuda.device(run_on):
+        status = k.new_status(f"cuda:{run_on}")
+        batch = k.HandoffBatch([r["src_tables"] for r in reqs], [r["dst_tables"] for r in reqs],
+                               [(0, r["tokens"]) for r in reqs], block_size=P.block_size,
+                               exit_planes=[r["exit_planes"] for r in reqs], device=f"cuda:{run_on}")
+        k.kv_handoff(gp.view(), gd.view(), batch, mode=k.MODE_DEDUP, status=status)
+        torch.cuda.synchronize(run_on)
+        k.raise_for_status(status)
+    load_pool(D, arrays, "dst_after_")
+    assert_pools_equal(gd, D)

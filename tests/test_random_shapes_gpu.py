@@ -17,7 +17,7 @@ from tests.test_kv_handoff_gpu import sentinel_destination
 
 pytestmark = pytest.mark.gpu
 
-VARIANTS = [0, 1, 2, 3, 4, 5]
+VARIANTS = [0, 1, 2, 3, 4, 5, 6]
 
 
 def draw(seed):

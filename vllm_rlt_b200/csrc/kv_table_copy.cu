@@ -87,6 +87,7 @@ struct TableCopyParams {
   unsigned long long deep_layer_mask;  // layers carried for planes >= 1; 0 = all
   int dedup_wire;                // the packed image holds, per token, only planes up to its exit plane
   const int* dedup_prefix;       // [planes * total blocks] wire tokens before each (request, plane, block)
+  int fan;                       // pool-to-pool dedup that reads each row once and stores it to every plane it fills
   int* status;
 };
 
@@ -251,8 +252,10 @@ __device__ __forceinline__ Unit decode_unit(const TableCopyParams& p, const int*
   u.n_blk = blk_off[u.r + 1] - u.blk_first;
   u.sel_mask = 0;
   u.n_sel = u.n_tok;
-  if (kDedup && p.dst_packed) {
+  if (kDedup && (p.dst_packed || p.fan)) {
     u.sel_mask = exit_mask(p, u.r, u.tok_lo, u.n_tok, u.plane);
+    // Fan-out: every token has a row on plane 0, so an exit plane below 0 is seen (and reported) there.
+    if (p.fan && u.plane == 0) u.sel_mask = u.n_tok >= 64 ? ~0ull : (1ull << u.n_tok) - 1ull;
     u.n_sel = __popcll(u.sel_mask);
   }
   u.rows = u.n_layers * u.n_sel;
@@ -388,6 +391,142 @@ __global__ void __launch_bounds__(kThreads, 4) table_copy_kernel(const TableCopy
       stream_rows<uint32_t, kUnroll, kStreaming>(src, dst, rs, rd, total_vecs, rg.row_vecs, rg.row_magic);
     } else {
       stream_rows<uint8_t, kUnroll, kStreaming>(src, dst, rs, rd, total_vecs, rg.row_vecs, rg.row_magic);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Fan-out flavour of the pool-to-pool dedup handoff. The destination of RLT_MODE_DEDUP holds, on every
+// plane deeper than a token's exit plane, a copy of the exit-plane row. The kernel above produces that by
+// walking destination planes, which reads the exit-plane row once per plane it fills. Here the walk is over
+// SOURCE planes: the unit of plane q loads the rows of the tokens that reach q (exit plane >= q) once,
+// stores them to plane q, and stores the rows of the tokens that stop at q to every deeper plane as well.
+// Bytes read = the dedup wire image, bytes written = the full destination; with the source behind a peer
+// pointer only the wire image crosses the link.
+constexpr long long kFanBit = 1ll << 62;          // in a destination offset: the row also goes to the deeper planes
+constexpr long long kNoPlane = -(1ll << 62);      // in a plane delta: that plane's block is invalid, skip it
+constexpr int kFanMaxPlanes = 64;
+
+template <typename T, int kUnroll>
+__device__ __forceinline__ void stream_rows_fan(const char* __restrict__ src, char* __restrict__ dst,
+                                                const long long* __restrict__ src_off,
+                                                const long long* __restrict__ dst_off,
+                                                const long long* __restrict__ plane_delta, int fan_begin,
+                                                int fan_end, int total_vecs, int row_vecs, unsigned row_magic) {
+  for (int base = threadIdx.x; base < total_vecs; base += kThreads * kUnroll) {
+    T regs[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const int i = base + u * kThreads;
+      if (i < total_vecs) {
+        const int row = row_magic ? static_cast<int>(__umulhi(static_cast<unsigned>(i), row_magic)) : i;
+        const long long so = src_off[row];
+        if (so >= 0) regs[u] = ld_stream(reinterpret_cast<const T*>(src + so) + (i - row * row_vecs));
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const int i = base + u * kThreads;
+      if (i < total_vecs) {
+        const int row = row_magic ? static_cast<int>(__umulhi(static_cast<unsigned>(i), row_magic)) : i;
+        long long to = dst_off[row];
+        if (to >= 0) {
+          const bool fan = (to & kFanBit) != 0;
+          to &= ~kFanBit;
+          char* at = dst + to + static_cast<long long>(i - row * row_vecs) * static_cast<long long>(sizeof(T));
+          st_stream(reinterpret_cast<T*>(at), regs[u]);
+          if (fan) {
+            for (int pl = fan_begin; pl < fan_end; ++pl) {
+              const long long d = plane_delta[pl];
+              if (d != kNoPlane) st_stream(reinterpret_cast<T*>(at + d), regs[u]);
+            }
+          }
+        }
+      }
+    }
+  }
+}
+
+// Offsets of row `row` of a fan-out unit; the unit's rows are (layer, token that reaches the unit's plane).
+__device__ __forceinline__ void fan_row_offsets(const TableCopyParams& p, const Unit& u, int row,
+                                                long long* src_off, long long* dst_off) {
+  const RegionParams& rg = p.region[u.g];
+  const int l_rel = row / u.n_sel;
+  const int tok = nth_set_bit(u.sel_mask, row - l_rel * u.n_sel);
+  const int layer = u.layer0 + l_rel;
+  const int t_abs = u.tok_lo + tok;
+  const bool deep_ok = p.deep_layer_mask == 0 || ((p.deep_layer_mask >> layer) & 1ull) != 0;
+  bool ok = u.plane == 0 || deep_ok;  // planes >= 1 carry only the deep layers
+  const int e = p.exit_planes[p.exit_offsets[u.r] + t_abs];
+  if (e < 0 || e >= p.src_planes) {
+    report(p.status, RLT_STATUS_BAD_PLANE, u.r, t_abs, e);
+    ok = false;
+  }
+  const long long in_block = layer * rg.layer_bytes + (t_abs - u.logical * p.block_size) * rg.token_bytes;
+  const int sb = p.src_tables[(static_cast<long long>(u.r) * p.src_planes + u.plane) * p.table_width + u.logical];
+  const int db = p.dst_tables[(static_cast<long long>(u.r) * p.dst_planes + u.plane) * p.table_width + u.logical];
+  if (sb < 0 || sb >= p.src_blocks) {
+    report(p.status, RLT_STATUS_BAD_BLOCK, u.r, u.logical, sb);
+    ok = false;
+  }
+  if (db < 0 || db >= p.dst_blocks) {
+    report(p.status, RLT_STATUS_BAD_BLOCK, u.r, u.logical, db);
+    ok = false;
+  }
+  long long dof = db * rg.block_bytes + in_block;
+  if (e == u.plane && u.plane + 1 < p.dst_planes && deep_ok) dof |= kFanBit;
+  *src_off = ok ? sb * rg.block_bytes + in_block : -1;
+  *dst_off = ok ? dof : -1;
+}
+
+template <int kUnroll>
+__global__ void __launch_bounds__(kThreads, 3) table_fan_kernel(const TableCopyParams p) {
+  extern __shared__ int dyn_smem[];
+  int* blk_off = dyn_smem;
+  int* tok_off = dyn_smem + p.num_requests + 1;
+  __shared__ long long row_src[2][kMaxRows];
+  __shared__ long long row_dst[2][kMaxRows];
+  __shared__ long long plane_delta[2][kFanMaxPlanes];
+
+  scan_requests<kThreads>(p, blk_off, tok_off);
+
+  const int per_plane = units_per_plane(p);
+  const int per_block = per_plane * p.plane_count;
+  const long long total_units = static_cast<long long>(blk_off[p.num_requests]) * per_block;
+
+  int parity = 0;
+  for (long long w = blockIdx.x; w < total_units; w += gridDim.x, parity ^= 1) {
+    const Unit u = decode_unit<true>(p, blk_off, w, per_plane, per_block);
+    const RegionParams& rg = p.region[u.g];
+    long long* rs = row_src[parity];
+    long long* rd = row_dst[parity];
+    long long* pd = plane_delta[parity];
+    if (threadIdx.x < u.rows) fan_row_offsets(p, u, threadIdx.x, &rs[threadIdx.x], &rd[threadIdx.x]);
+    // Threads of the back of the CTA fetch the deeper planes' blocks, as byte distances from this plane's block.
+    const int pl = kThreads - 1 - static_cast<int>(threadIdx.x);
+    if (u.rows > 0 && pl > u.plane && pl < p.dst_planes) {
+      const long long row_base = static_cast<long long>(u.r) * p.dst_planes;
+      const int here = p.dst_tables[(row_base + u.plane) * p.table_width + u.logical];
+      const int there = p.dst_tables[(row_base + pl) * p.table_width + u.logical];
+      long long d = kNoPlane;
+      if (there < 0 || there >= p.dst_blocks) {
+        report(p.status, RLT_STATUS_BAD_BLOCK, u.r, u.logical, there);
+      } else {
+        d = (static_cast<long long>(there) - here) * rg.block_bytes;
+      }
+      pd[pl] = d;
+    }
+    __syncthreads();  // one barrier per unit: all three tables are double buffered
+
+    const char* src = unit_src(p, u);
+    char* dst = unit_dst(p, u);
+    const int total_vecs = u.rows * rg.row_vecs;
+    if (rg.vec_bytes == 16) {
+      stream_rows_fan<uint4, kUnroll>(src, dst, rs, rd, pd, u.plane + 1, p.dst_planes, total_vecs, rg.row_vecs, rg.row_magic);
+    } else if (rg.vec_bytes == 4) {
+      stream_rows_fan<uint32_t, kUnroll>(src, dst, rs, rd, pd, u.plane + 1, p.dst_planes, total_vecs, rg.row_vecs, rg.row_magic);
+    } else {
+      stream_rows_fan<uint8_t, kUnroll>(src, dst, rs, rd, pd, u.plane + 1, p.dst_planes, total_vecs, rg.row_vecs, rg.row_magic);
     }
   }
 }
@@ -914,9 +1053,18 @@ int launch_table_copy(Direction dir, const RltPool* src, const RltPool* dst, con
     const int planned = plan_dedup(p, workspace, workspace_bytes, sms, smem, stream);
     if (planned != RLT_OK) return planned;
   }
-  const int flavour = opt->variant & 0xf;
-  if (flavour > 5) return RLT_E_INVALID;
-  if (flavour <= 2) {
+  int flavour = opt->variant & 0xf;
+  if (flavour > 6) return RLT_E_INVALID;
+  // Pool-to-pool dedup over every plane: read each row once and fan it out, unless flavour 6 asks for the
+  // walk over destination planes (kept for comparison; the bulk flavours 3 and 4 keep that walk too).
+  const bool fan = dir == kDirect && opt->mode == RLT_MODE_DEDUP && p.plane_begin == 0 &&
+                   p.plane_count == p.dst_planes && p.dst_planes > 1 && p.dst_planes <= kFanMaxPlanes &&
+                   flavour != 3 && flavour != 4 && flavour != 6;
+  if (flavour == 6) flavour = 0;
+  if (fan) {
+    p.fan = 1;
+    table_fan_kernel<4><<<grid, kThreads, smem, stream>>>(p);
+  } else if (flavour <= 2) {
     void (*kernel)(const TableCopyParams) = nullptr;
     if (dedup_wire) {
       kernel = flavour == 1 ? table_copy_kernel<8, true, true>

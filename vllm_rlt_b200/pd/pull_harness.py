@@ -23,6 +23,26 @@ import time
 import numpy as np
 
 
+def wire_bytes(w, requests, mode: str) -> int:
+    """Bytes of the given requests of a workload that the decode GPU loads from the prefill pool."""
+    from vllm_rlt_b200 import workloads
+
+    sub = workloads.subset(w, list(requests))
+    if mode != "dedup" or sub.exit_planes is None:
+        return sub.payload_bytes
+    deep = sub.extra.get("deep_layers")
+    s = sub.shape
+    per_layer = s.token_plane_bytes // s.num_layers
+    total = 0
+    for exits, (lo, hi) in zip(sub.exit_planes, sub.ranges):
+        reach = np.minimum(np.asarray(exits[lo:hi], dtype=np.int64) + 1, sub.dst_planes)  # planes read per token
+        if deep:
+            total += int((s.token_plane_bytes + (reach - 1) * len(deep) * per_layer).sum())
+        else:
+            total += int(reach.sum()) * s.token_plane_bytes
+    return total
+
+
 def run_pull(args, rank: int, world: int) -> None:
     import torch
     import torch.distributed as dist
@@ -128,6 +148,9 @@ def run_pull(args, rank: int, world: int) -> None:
             edges.append(dict(sv=sv, ready=flags.data_ptr() + 8 * slot, done_ptr=ptrs[4 + j], sub=sub, make_batch=make_batch,
                               batch=make_batch(), mine=mine, source=p, payload=workloads.subset(wp, mine).payload_bytes))
     my_payload = sum(e["payload"] for e in edges) if not is_prefill else 0
+    # bytes that cross the link: in dedup mode each row is read once (planes up to the token's exit plane) and the
+    # deeper planes are filled on the decode GPU from the same load
+    my_wire = sum(wire_bytes(per_source[e["source"]], e["mine"], args.mode) for e in edges) if not is_prefill else 0
     counter = 0
 
     def step(fresh_batches=False):
@@ -183,7 +206,7 @@ def run_pull(args, rank: int, world: int) -> None:
     dist.all_reduce(k_ms, op=dist.ReduceOp.MAX)
     n_launch = torch.tensor([launches], device=device)
     dist.all_reduce(n_launch)
-    payload_all = torch.tensor([float(my_payload)], device=device, dtype=torch.float64)
+    payload_all = torch.tensor([float(my_payload), float(my_wire)], device=device, dtype=torch.float64)
     dist.all_reduce(payload_all)
 
     # ---- verification: the source side gathers what some transferred tokens should hold, the decode side compares
@@ -272,10 +295,11 @@ def run_pull(args, rank: int, world: int) -> None:
 
     if rank == 0:
         ms_per_step = float(total_ms.item()) / args.steps
-        total_payload = float(payload_all.item())
+        total_payload, total_wire = (float(x) for x in payload_all.tolist())
         value = total_payload / (ms_per_step * 1e-3) / 1e9
         links = min(n_prefill, n_decode)
-        per_link = value / links
+        per_pair = value / links
+        per_link = per_pair * total_wire / total_payload  # what the link carries per pair
         line = {
             "metric": bench.METRIC, "value": value, "unit": bench.UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
@@ -287,14 +311,17 @@ def run_pull(args, rank: int, world: int) -> None:
             "roofline": {"bound": "nvlink", "achieved": per_link, "peak": bench.NVLINK_MEASURED_GBS, "unit": "GB/s",
                          "frac": per_link / bench.NVLINK_MEASURED_GBS, "traffic": None,
                          "peak_source": "measured peer copy on this pool, 770 GB/s per direction per GPU (nominal 900)",
-                         "kernel": "table_copy_kernel", "algorithmic_bytes_per_launch": w.payload_bytes,
+                         "kernel": "table_fan_kernel" if args.mode == "dedup" else "table_copy_kernel",
+                         "algorithmic_bytes_per_launch": total_wire / max(1, n_decode),
                          "kernel_ms": float(k_ms.item()), "frac_of_nominal_900": per_link / 900.0,
                          "raw_link_gbps": per_link * bench.NVLINK_READ_OVERHEAD,
                          "raw_link_frac_of_900": per_link * bench.NVLINK_READ_OVERHEAD / 900.0,
                          "raw_link_note": "read responses carry 12.5 % of protocol bytes on top of the payload (ncu nvlrx__bytes "
                                           "counters of this kernel); requests use the opposite direction",
-                         "what": "aggregate payload rate / min(prefill, decode) GPUs: the per-GPU link rate of the busier side"},
-            "per_pair_gbps": per_link,
+                         "what": "bytes that cross NVLink per second / min(prefill, decode) GPUs: the per-GPU link rate of the "
+                                 "busier side; equals the payload rate except in dedup mode, where only the rows up to each "
+                                 "token's exit plane cross the link and `value` counts every destination byte"},
+            "per_pair_gbps": per_pair, "link_bytes": total_wire, "link_gbps_per_pair": per_link,
             "e2e": {"value": total_payload / float(e2e_s.item()) / 1e9, "unit": bench.UNIT,
                     "h2d_bytes_per_step": int(staged_bytes.item()), "d2h_bytes_per_step": 16 * n_decode, "ms_per_step": float(e2e_s.item()) * 1e3,
                     "note": "tables, ranges and exit planes are staged from the host on the decode ranks every step"},
