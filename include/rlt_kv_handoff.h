@@ -124,8 +124,11 @@ typedef struct RltOptions {
   int32_t* status;     /* NULL or device/mapped int32[RLT_STATUS_WORDS], zeroed by the caller   */
   int32_t grid_limit;  /* 0 = one persistent wave (a few CTAs per SM); else cap on CTAs launched */
   int32_t variant;     /* low 4 bits pick the kernel flavour: 0 register path (default), 1 and 2 its
-                          deeper-unrolled forms, 3 and 4 cp.async.bulk rings; bits 4-11 = unit size in
-                          16 KiB steps and bits 12-15 = CTAs per SM are tuning knobs, 0 = default     */
+                          deeper-unrolled forms, 3 and 4 cp.async.bulk rings, 5 32-byte accesses, 6 the
+                          register path with rlt_kv_handoff's DEDUP walking destination planes (the
+                          default walks source planes: each row is read once and stored to every
+                          plane it fills); bits 4-11 = unit size in 16 KiB steps and bits 12-15 = CTAs
+                          per SM are tuning knobs, 0 = default                                      */
   void* workspace;     /* device scratch; needed only by pack/scatter in RLT_MODE_DEDUP          */
   int64_t workspace_bytes; /* at least rlt_kv_dedup_workspace_bytes(...) for those calls          */
   int32_t plane_begin; /* destination (or wire) plane slice [plane_begin, plane_end): lets a   */
