@@ -193,76 +193,77 @@ class HandoffBatch:
             raise ValueError(f"a handoff batch holds at most {_lib.MAX_REQUESTS} requests")
         self.num_requests = n
         self.block_size = block_size
-        self.ranges = [(int(s), int(e)) for s, e in ranges]
-        for s, e in self.ranges:
-            if not 0 <= s < e:
-                raise ValueError("invalid KV range")
-        self.total_tokens = sum(e - s for s, e in self.ranges)
-        arrays, width = [], 1
-        flats = []
+        bounds = np.asarray(ranges, dtype=np.int64).reshape(n, 2)
+        begin, end = bounds[:, 0], bounds[:, 1]
+        if ((begin < 0) | (begin >= end)).any():
+            raise ValueError("invalid KV range")
+        self.ranges = [(int(s), int(e)) for s, e in bounds]
+        self.total_tokens = int((end - begin).sum())
+        # Per side: every table row of every request, its length, and one flat int32 array of all entries in
+        # (request, plane, page) order. The checks are those of the reference's planner, done on whole arrays.
+        sides, width = [], 1
         for tables, limit in ((src_tables, src_blocks), (dst_tables, dst_blocks)):
             if tables is None:
-                flats.append(None)
+                sides.append(None)
                 continue
             if len(tables) != n:
                 raise ValueError("one table set per request is required")
             planes = len(tables[0])
-            pages = []
-            for req, (s, e) in zip(tables, self.ranges):
-                if len(req) != planes:
-                    raise ValueError("requests of one batch must have the same number of planes")
-                m = len(req[0])
-                for table in req:
-                    if e > len(table) * block_size:
-                        raise ValueError("KV range exceeds allocation")
-                    if len(table) != m:
-                        raise ValueError("the planes of one request must have tables of equal length")
-                pages.append(m)
-                width = max(width, m)
-            # one flat conversion of every table entry, in (request, plane, page) order
-            total = planes * sum(pages)
-            if isinstance(tables[0][0], np.ndarray):
-                flat = np.concatenate([t for req in tables for t in req]).astype(np.int32, copy=False)
+            if any(len(req) != planes for req in tables):
+                raise ValueError("requests of one batch must have the same number of planes")
+            rows = [table for req in tables for table in req]
+            lens = np.fromiter(map(len, rows), np.int64, count=n * planes).reshape(n, planes)
+            pages = lens[:, 0]
+            if (end > lens.min(axis=1) * block_size).any():
+                raise ValueError("KV range exceeds allocation")
+            if (lens != pages[:, None]).any():
+                raise ValueError("the planes of one request must have tables of equal length")
+            total = int(lens.sum())
+            if isinstance(rows[0], np.ndarray):
+                flat = np.concatenate(rows).astype(np.int32, copy=False)
             else:
-                flat = np.fromiter((b for req in tables for table in req for b in table), np.int32, count=total)
-            flats.append((flat, planes, pages, limit))
+                flat = np.fromiter((b for table in rows for b in table), np.int32, count=total)
+            width = max(width, int(pages.max()))
+            sides.append((flat, planes, lens.reshape(-1), limit))
         self.table_width = width
-        for side in flats:
+        arrays = []
+        first, last = begin // block_size, (end - 1) // block_size
+        used = None
+        for side in sides:
             if side is None:
                 arrays.append(None)
                 continue
-            flat, planes, pages, limit = side
+            flat, planes, row_len, limit = side
             a = np.zeros((n, planes, width), np.int32)
-            at = 0
-            for r, m in enumerate(pages):
-                a[r, :, :m] = flat[at : at + planes * m].reshape(planes, m)
-                at += planes * m
-                s, e = self.ranges[r]
-                used = a[r, :, s // block_size : (e - 1) // block_size + 1]
-                if used.min() < 0 or (limit is not None and used.max() >= limit):
+            # a boolean mask is filled in row-major order, which is the order of the flat array
+            a.reshape(n * planes, width)[np.arange(width) < row_len[:, None]] = flat
+            # negative ids compare as huge unsigned numbers; the padding (0) is a valid id, so the mask of
+            # pages that the ranges touch is only needed when something looks wrong
+            bad = a < 0 if limit is None else a.view(np.uint32) >= limit
+            if bad.any():
+                if used is None:
+                    cols = np.arange(width)
+                    used = (cols >= first[:, None]) & (cols <= last[:, None])
+                if (bad & used[:, None, :]).any():
                     raise ValueError("physical block outside registered pool")
             arrays.append(a)
         self.src_planes = arrays[0].shape[1] if arrays[0] is not None else 0
         self.dst_planes = arrays[1].shape[1] if arrays[1] is not None else 0
-        begin = np.array([s for s, _ in self.ranges], np.int32)
-        end = np.array([e for _, e in self.ranges], np.int32)
-        exits = offsets = None
+        exit_parts = offsets = None
+        exit_count = 0
         if exit_planes is not None:
             if len(exit_planes) != n:
                 raise ValueError("one exit-plane array per request is required")
-            offsets = np.zeros(n, np.int64)
-            parts, at = [], 0
-            for r, (e_r, (s, e)) in enumerate(zip(exit_planes, self.ranges)):
-                e_r = np.asarray(e_r, np.int32)
-                if e_r.ndim != 1 or len(e_r) < e:
-                    raise ValueError("exit planes must cover every token position up to the range end")
-                offsets[r] = at
-                at += len(e_r)
-                parts.append(e_r)
-            exits = np.concatenate(parts)
-        # One pinned staging buffer, one host-to-device copy; int64 data first for alignment.
+            exit_parts = [np.asarray(e, np.int32) for e in exit_planes]
+            counts = np.fromiter(map(len, exit_parts), np.int64, count=n)
+            if any(e.ndim != 1 for e in exit_parts) or (counts < end).any():
+                raise ValueError("exit planes must cover every token position up to the range end")
+            offsets = np.cumsum(counts) - counts
+            exit_count = int(counts.sum())
+        # One pinned staging buffer, one host-to-device copy; int64 data first for alignment. The exit planes,
+        # the largest piece, are gathered straight into the staging buffer.
         pieces = [("exit_offsets", offsets), ("src_tables", arrays[0]), ("dst_tables", arrays[1]),
-                  ("tok_begin", begin), ("tok_end", end), ("exit_planes", exits)]
+                  ("tok_begin", begin.astype(np.int32)), ("tok_end", end.astype(np.int32))]
         layout, size = {}, 0
         for name, a in pieces:
             if a is None:
@@ -270,16 +271,24 @@ class HandoffBatch:
             size = (size + 15) & ~15
             layout[name] = (size, a)
             size += a.nbytes
+        if exit_parts is not None:
+            size = (size + 15) & ~15
+            layout["exit_planes"] = (size, None)
+            size += 4 * exit_count
         self.metadata_bytes = size
         device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
         staging = _PINNED.acquire(size)
         host = staging.buffer.numpy()
         for name, (at, a) in layout.items():
-            host[at : at + a.nbytes] = a.reshape(-1).view(np.uint8)
+            if a is not None:
+                host[at : at + a.nbytes] = a.reshape(-1).view(np.uint8)
+            elif exit_count:
+                np.concatenate(exit_parts, out=host[at : at + 4 * exit_count].view(np.int32))
         self._dev = torch.empty(size, dtype=torch.uint8, device=device)
         with torch.cuda.device(device), torch.cuda.stream(stream if stream is not None else torch.cuda.current_stream(device)):
             self._dev.copy_(staging.buffer[:size], non_blocking=True)
             staging.release()
+        exits = exit_parts
         base = self._dev.data_ptr()
         self._ptr = {name: base + at for name, (at, _) in layout.items()}
         self.has_exit = exits is not None
