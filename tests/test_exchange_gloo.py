@@ -106,3 +106,26 @@ def test_a_worker_that_never_joins_ends_the_exchange_with_an_error_not_a_hang():
     got = out.get(timeout=90)
     proc.join(timeout=30)
     assert got != "joined"
+
+
+def test_pull_edges_agree_on_both_ends_for_every_split():
+    """Both ends of a P->D edge derive the same flag slots and request lists from the pairing alone, every request
+    of every prefill rank is on exactly one edge, and no two edges share a flag word."""
+    from vllm_rlt_b200.pd import exchange
+
+    for world in (2, 3, 4, 5, 8):
+        for prefill in range(1, world):
+            for num_requests in (1, 2, 7, 64):
+                plans = {r: exchange.pull_edges(r, world, prefill, num_requests) for r in range(world)}
+                fan = max(len(exchange.pairing(r, world, prefill)[2]) for r in range(world))
+                for p in range(prefill):
+                    sent = sorted(i for e in plans[p] for i in e["requests"])
+                    assert sent == list(range(num_requests))
+                    assert len({e["done_slot"] for e in plans[p]}) == len(plans[p])
+                    for e in plans[p]:
+                        assert e["prefill"] == p and 0 <= e["done_slot"] < fan and 0 <= e["ready_slot"] < fan
+                        assert e in plans[e["decode"]]  # the decode rank sees the very same edge
+                for d in range(prefill, world):
+                    assert len({e["ready_slot"] for e in plans[d]}) == len(plans[d])
+                    for e in plans[d]:
+                        assert e["decode"] == d and e in plans[e["prefill"]]

@@ -82,6 +82,34 @@ def pairing(rank: int, world: int, prefill: int | None = None):
     return is_prefill, index, partners
 
 
+def assigned_requests(p_rank: int, d_rank: int, world: int, prefill: int, num_requests: int) -> list[int]:
+    """Requests of prefill rank ``p_rank`` that go to decode rank ``d_rank``: round-robin over its partners."""
+    partners = pairing(p_rank, world, prefill)[2]
+    return [i for i in range(num_requests) if partners[i % len(partners)] == d_rank]
+
+
+def pull_edges(rank: int, world: int, prefill: int, num_requests: int) -> list[dict]:
+    """The P->D edges a rank takes part in when the decode side pulls, with the flag slot each end uses.
+
+    Every rank owns ``max fan`` flag words. A decode rank's word ``ready_slot`` is raised by the prefill
+    rank when its KV is written; a prefill rank's word ``done_slot`` is raised by the decode rank when it has
+    read the KV. Both ends compute the same ``(ready_slot, done_slot)`` for an edge from the pairing alone:
+    ``ready_slot`` = position of the prefill rank among the decode rank's partners, ``done_slot`` = position
+    of the decode rank among the prefill rank's partners. Edges without requests are left out.
+    """
+    is_prefill, _, partners = pairing(rank, world, prefill)
+    edges = []
+    for peer in partners:
+        p_rank, d_rank = (rank, peer) if is_prefill else (peer, rank)
+        requests = assigned_requests(p_rank, d_rank, world, prefill, num_requests)
+        if not requests:
+            continue
+        edges.append(dict(prefill=p_rank, decode=d_rank, requests=requests,
+                          ready_slot=pairing(d_rank, world, prefill)[2].index(p_rank),
+                          done_slot=pairing(p_rank, world, prefill)[2].index(d_rank)))
+    return edges
+
+
 def init_process_group_quietly(device):
     """Create the NCCL group with stdout pointed at stderr for the duration: NCCL prints its version banner to
     stdout when its debug level is VERSION or WARN, and rank 0 must print exactly one JSON line there."""

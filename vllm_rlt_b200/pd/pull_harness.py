@@ -70,8 +70,7 @@ def run_pull(args, rank: int, world: int) -> None:
         return exchange.pairing(r, world, n_prefill)[2]
 
     def assigned(p_rank: int, d_rank: int, w):
-        ps = partners_of(p_rank)
-        return [i for i in range(len(w.lengths)) if ps[i % len(ps)] == d_rank]
+        return exchange.assigned_requests(p_rank, d_rank, world, n_prefill, len(w.lengths))
 
     if is_prefill:
         w = make_workload(args, index)
@@ -117,23 +116,18 @@ def run_pull(args, rank: int, world: int) -> None:
     status = kh.new_status(device)
     mapping = peerlib.PeerMapping()
     edges = []
+    plan = exchange.pull_edges(rank, world, n_prefill, len(w.lengths))
     if is_prefill:
-        for j, d_rank in enumerate(partners):
-            mine = assigned(rank, d_rank, w)
-            if not mine:
-                continue
-            slot = partners_of(d_rank).index(rank)
-            ptrs = [mapping.pointer(e) for e in exchange.decode_handles(all_handles[d_rank])]
-            edges.append(dict(ready_ptr=ptrs[4 + slot], done=flags.data_ptr() + 8 * j, mine=mine,
+        for edge in plan:
+            ptrs = [mapping.pointer(e) for e in exchange.decode_handles(all_handles[edge["decode"]])]
+            mine = edge["requests"]
+            edges.append(dict(ready_ptr=ptrs[4 + edge["ready_slot"]], done=flags.data_ptr() + 8 * edge["done_slot"], mine=mine,
                               payload=workloads.subset(w, mine).payload_bytes))
     else:
         dv = kh.PoolView.from_cache(pool)
-        for slot, p in enumerate(partners):
+        for edge in plan:
+            p, mine = edge["prefill"], edge["requests"]
             wp = per_source[p]
-            mine = assigned(p, rank, wp)
-            if not mine:
-                continue
-            j = partners_of(p).index(rank)
             ptrs = [mapping.pointer(e) for e in exchange.decode_handles(all_handles[p])]
             scales = dv.scales.rebased(ptrs[2], ptrs[3]) if s.fp8 else None
             sv = kh.PoolView(dv.codes.rebased(ptrs[0], ptrs[1]), scales, wp.src_blocks, s.block_size, s.num_layers, s.planes, -1)
@@ -145,8 +139,9 @@ def run_pull(args, rank: int, world: int) -> None:
                 return kh.HandoffBatch(sub["src"], sub["dst"], sub["ranges"], block_size=s.block_size, exit_planes=sub["exits"],
                                        src_blocks=wp.src_blocks, dst_blocks=pool.num_blocks, device=device)
 
-            edges.append(dict(sv=sv, ready=flags.data_ptr() + 8 * slot, done_ptr=ptrs[4 + j], sub=sub, make_batch=make_batch,
-                              batch=make_batch(), mine=mine, source=p, payload=workloads.subset(wp, mine).payload_bytes))
+            edges.append(dict(sv=sv, ready=flags.data_ptr() + 8 * edge["ready_slot"], done_ptr=ptrs[4 + edge["done_slot"]], sub=sub,
+                              make_batch=make_batch, batch=make_batch(), mine=mine, source=p,
+                              payload=workloads.subset(wp, mine).payload_bytes))
     my_payload = sum(e["payload"] for e in edges) if not is_prefill else 0
     # bytes that cross the link: in dedup mode each row is read once (planes up to the token's exit plane) and the
     # deeper planes are filled on the decode GPU from the same load
