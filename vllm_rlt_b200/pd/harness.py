@@ -449,7 +449,10 @@ def run_multi(args, rank: int, world: int) -> None:
                 "per_prefill_worker": w.description, "payload_bytes": total_payload,
                 "transport": "peer stores over NVLink (CUDA IPC mapping), completion flag per step"}),
             "roofline": {"bound": "nvlink", "achieved": per_link, "peak": bench.NVLINK_MEASURED_GBS, "unit": "GB/s",
-                         "frac": per_link / bench.NVLINK_MEASURED_GBS, "traffic": None,
+                         "frac": per_link / bench.NVLINK_MEASURED_GBS,
+                         "traffic": w.payload_bytes * bench.NVLINK_WRITE_OVERHEAD,
+                         "traffic_source": "link bytes per launch: nvltx__bytes.sum / nvltx__bytes_data_user.sum = 1.1875 from an "
+                                           "ncu capture of the same kernel writing to a peer, scaled by the payload",
                          "peak_source": "measured peer copy on this pool, 770 GB/s per direction per GPU (nominal 900)",
                          "kernel": "table_copy_kernel", "algorithmic_bytes_per_launch": w.payload_bytes,
                          "kernel_ms": float(k_ms.item()), "frac_of_nominal_900": per_link / 900.0,

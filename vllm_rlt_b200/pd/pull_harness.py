@@ -304,7 +304,10 @@ def run_pull(args, rank: int, world: int) -> None:
                 "per_prefill_worker": w.description, "payload_bytes": total_payload,
                 "transport": "decode GPU pulls through peer pointers over NVLink (CUDA IPC mapping); ready and done flags per step"}),
             "roofline": {"bound": "nvlink", "achieved": per_link, "peak": bench.NVLINK_MEASURED_GBS, "unit": "GB/s",
-                         "frac": per_link / bench.NVLINK_MEASURED_GBS, "traffic": None,
+                         "frac": per_link / bench.NVLINK_MEASURED_GBS,
+                         "traffic": total_wire / max(1, n_decode) * bench.NVLINK_READ_OVERHEAD,
+                         "traffic_source": "link bytes per launch: nvlrx__bytes.sum / nvlrx__bytes_data_user.sum = 1.125 from an "
+                                           "ncu capture of the same kernel reading from a peer, scaled by the bytes read",
                          "peak_source": "measured peer copy on this pool, 770 GB/s per direction per GPU (nominal 900)",
                          "kernel": "table_fan_kernel" if args.mode == "dedup" else "table_copy_kernel",
                          "algorithmic_bytes_per_launch": total_wire / max(1, n_decode),
