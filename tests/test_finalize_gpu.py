@@ -93,3 +93,38 @@ def test_finalize_reports_rows_it_cannot_apply():
     assert_pools_equal(gp, P)
     with pytest.raises(ValueError, match="recurrent_layers"):
         kh.kv_finalize(full_view(gp), tables, rows, layers=[5])
+
+
+@pytest.mark.parametrize("planes", [2, 32, 64, 65])
+def test_finalize_with_many_planes_fills_every_deeper_plane(planes):
+    """Up to 64 planes one unit loads a row once and stores it to every deeper plane; beyond that the
+    unit-per-target kernel runs. Both must leave the pool the oracle's ``finalize_token`` leaves."""
+    import random
+
+    from vllm_rlt_b200.kernels import kv_handoff as kh
+
+    rng = random.Random(planes)
+    lengths = [9, 4, 1]
+    page = 4
+    blocks = sum(-(-n // page) for n in lengths) * planes + 2
+    P = oracle_pool("fp8", (3, 2, 16, blocks, page, planes))
+    P.fill_random(np.random.default_rng(planes))
+    P.shuffle_free_list(rng)
+    for i, n in enumerate(lengths):
+        assert P.allocate(f"r{i}", n)
+    gp = GpuPool(P)
+    width = max(-(-n // page) for n in lengths)
+    tables = np.zeros((len(lengths), planes, width), np.int32)
+    rows = []
+    for i, n in enumerate(lengths):
+        for p, t in enumerate(P.plane_block_tables(f"r{i}")):
+            tables[i, p, : len(t)] = t
+        for pos in range(n):
+            e = rng.choice([0, planes - 1, rng.randrange(planes)])
+            rows.append((i, e, pos))
+            P.finalize_token(f"r{i}", pos, e)
+    status = kh.new_status()
+    kh.kv_finalize(full_view(gp), torch.from_numpy(tables).cuda(), torch.tensor(rows, dtype=torch.int32, device="cuda"),
+                   status=status)
+    kh.raise_for_status(status)
+    assert_pools_equal(gp, P)

@@ -7,11 +7,12 @@
 // Triton kernel over (row, target plane, channel tile) plus a second launch for the scales
 // (finalize_kernel, vllm_rlt/kernels/routing.py:147-179; ModelRunner.finalize_many,
 // vllm_rlt/worker/model_runner.py:1349-1395). Here one launch covers K, V and both scale
-// tensors: a work unit is (row, target plane, tensor) and moves the token's row of every
-// selected layer with 16-byte streaming loads and stores.
+// tensors: a work unit is (row, tensor); it loads the token's row of every selected layer once
+// with 16-byte streaming loads and stores it to every deeper plane.
 //
-// HBM roofline: each selected (layer, tensor) row is read once per target plane (served by L2
-// after the first) and written once per target plane.
+// HBM roofline: each selected (layer, tensor) row is read once and written once per deeper
+// plane. Pools with more than kFanPlanes planes use the older kernel, whose unit is
+// (row, target plane, tensor) and which reads the row once per target.
 
 #include "common.cuh"
 
@@ -63,6 +64,100 @@ __device__ __forceinline__ void copy_layers(const char* src, char* dst, const in
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
       if (at[u] >= 0) st_stream(reinterpret_cast<T*>(dst + at[u]), regs[u]);
+    }
+  }
+}
+
+constexpr int kFanPlanes = 64;
+
+// One load, several stores: vector i of the flat (selected layers x row vectors) array goes to the same
+// in-block offset of every target plane whose block is valid (plane_base >= 0).
+template <typename T>
+__device__ __forceinline__ void copy_layers_fan(const char* src, char* pool, const long long* plane_base, int first,
+                                                int planes, const int* layer_of, int layers, int row_vecs,
+                                                unsigned row_magic, long long layer_bytes) {
+  const int total = layers * row_vecs;
+  for (int base = threadIdx.x; base < total; base += kThreads * kUnroll) {
+    T regs[kUnroll];
+    long long at[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const int i = base + u * kThreads;
+      at[u] = -1;
+      if (i < total) {
+        const int slot = row_magic ? static_cast<int>(__umulhi(static_cast<unsigned>(i), row_magic)) : i;
+        at[u] = layer_of[slot] * layer_bytes + static_cast<long long>(i - slot * row_vecs) * static_cast<long long>(sizeof(T));
+        regs[u] = ld_stream(reinterpret_cast<const T*>(src + at[u]));
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      if (at[u] >= 0) {
+        for (int t = first; t < planes; ++t) {
+          const long long pb = plane_base[t];
+          if (pb >= 0) st_stream(reinterpret_cast<T*>(pool + pb + at[u]), regs[u]);
+        }
+      }
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kThreads, 4) finalize_fan_kernel(const FinalizeParams p) {
+  __shared__ int layer_of[64];  // the selected layers, in order
+  __shared__ int n_selected;
+  __shared__ long long plane_base[2][kFanPlanes];  // per unit: byte offset of the token's row in each target plane
+  if (threadIdx.x == 0) {
+    int n = 0;
+    for (int layer = 0; layer < p.num_layers; ++layer) {
+      if ((p.layer_mask >> layer) & 1ull) layer_of[n++] = layer;
+    }
+    n_selected = n;
+  }
+  __syncthreads();
+  const int layers = n_selected;
+  const int tensors = 2 * p.num_regions;
+  const long long units = static_cast<long long>(p.n) * tensors;
+  int parity = 0;  // flipped only by units that reach the barrier, so two such units in a row never share a table
+  for (long long w = blockIdx.x; w < units; w += gridDim.x) {
+    const int tensor = static_cast<int>(w % tensors);
+    const int row = static_cast<int>(w / tensors);
+    const int request = p.rows[3 * row], exit_plane = p.rows[3 * row + 1], position = p.rows[3 * row + 2];
+    if (request < 0 || request >= p.num_requests || exit_plane < 0 || exit_plane >= p.planes || position < 0 ||
+        position >= p.table_width * p.block_size) {
+      if (threadIdx.x == 0 && tensor == 0) report(p.status, RLT_STATUS_BAD_PLANE, row, position, exit_plane);
+      continue;
+    }
+    if (exit_plane + 1 >= p.planes) continue;  // the deepest plane was computed: nothing to fill
+    const int page = position / p.block_size, offset = position - page * p.block_size;
+    const long long base = (static_cast<long long>(request) * p.planes) * p.table_width + page;
+    const int sb = p.tables[base + static_cast<long long>(exit_plane) * p.table_width];
+    if (sb < 0 || sb >= p.num_blocks) {
+      if (threadIdx.x == 0) report(p.status, RLT_STATUS_BAD_BLOCK, request, page, sb);
+      continue;
+    }
+    const FinalizeRegion& rg = p.region[tensor >> 1];
+    long long* pb = plane_base[parity];
+    const int t = static_cast<int>(threadIdx.x);
+    if (t > exit_plane && t < p.planes) {
+      const int db = p.tables[base + static_cast<long long>(t) * p.table_width];
+      long long at = -1;
+      if (db < 0 || db >= p.num_blocks) {
+        report(p.status, RLT_STATUS_BAD_BLOCK, request, page, db);
+      } else {
+        at = db * rg.block_bytes + offset * rg.token_bytes;
+      }
+      pb[t] = at;
+    }
+    __syncthreads();
+    parity ^= 1;
+    char* pool = (tensor & 1) ? rg.value : rg.key;
+    const char* src = pool + sb * rg.block_bytes + offset * rg.token_bytes;
+    if (rg.vec_bytes == 16) {
+      copy_layers_fan<uint4>(src, pool, pb, exit_plane + 1, p.planes, layer_of, layers, rg.row_vecs, rg.row_magic, rg.layer_bytes);
+    } else if (rg.vec_bytes == 4) {
+      copy_layers_fan<uint32_t>(src, pool, pb, exit_plane + 1, p.planes, layer_of, layers, rg.row_vecs, rg.row_magic, rg.layer_bytes);
+    } else {
+      copy_layers_fan<uint8_t>(src, pool, pb, exit_plane + 1, p.planes, layer_of, layers, rg.row_vecs, rg.row_magic, rg.layer_bytes);
     }
   }
 }
@@ -169,9 +264,14 @@ int rlt_kv_finalize(const RltPool* pool, const int32_t* tables, int32_t num_requ
   int sms = 0;
   const int rc = rlt::sm_count(&sms);
   if (rc != RLT_OK) return rc;
-  const long long units = static_cast<long long>(count) * (p.planes - 1) * 2 * p.num_regions;
+  const bool fan = p.planes <= rlt::kFanPlanes;
+  const long long units = static_cast<long long>(count) * (fan ? 1 : p.planes - 1) * 2 * p.num_regions;
   const int grid = static_cast<int>(units < sms * 4ll ? units : sms * 4ll);
-  rlt::finalize_kernel<<<grid, rlt::kThreads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(p);
+  if (fan) {
+    rlt::finalize_fan_kernel<<<grid, rlt::kThreads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(p);
+  } else {
+    rlt::finalize_kernel<<<grid, rlt::kThreads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(p);
+  }
   RLT_CUDA_TRY(cudaGetLastError());
   rlt::g_launches.fetch_add(1, std::memory_order_relaxed);
   return RLT_OK;

@@ -74,8 +74,9 @@ def main() -> None:
         for i, e in enumerate(w.exit_planes)])).to(dev)
     copies = int((s.planes - 1 - exits).sum())
     ms = timed(lambda: kh.kv_finalize(sv, tables, rows, status=status))
-    report("finalize_kernel", 2 * copies * ptb, ms, rows=len(rows), copied_rows=copies,
-           note="reads of one exit row for several deeper planes are counted once per copy")
+    sources = int((exits < s.planes - 1).sum())
+    report("finalize_fan_kernel", (sources + copies) * ptb, ms, rows=len(rows), source_rows=sources, copied_rows=copies,
+           note="each exit row with deeper planes is read once and written once per deeper plane")
 
     full = kh.packed_bytes(sv, tokens, s.planes)
     packed = torch.empty(full, dtype=torch.uint8, device=dev)
