@@ -235,6 +235,7 @@ class CpuSample:
         self.payload = sum(ho.payload_bytes(self.P, n, s.planes) for n in lengths)
         self.plan_s = self.apply_s = 0.0
         self.reps = 0
+        self.single_s = None  # one repetition with one copy thread, as a stage worker of the reference runs
 
     def _real(self, address):
         for base, ptr, size in self.spans:
@@ -242,7 +243,7 @@ class CpuSample:
                 return ptr + (address - base)
         raise ValueError("address outside pools")
 
-    def run_once(self):
+    def run_once(self, threads=None):
         import numpy as np
 
         from oracle import cpu_apply
@@ -257,9 +258,12 @@ class CpuSample:
                 triples.extend((self._real(a), self._real(b), m) for (a, m, _), (b, _, _) in zip(local, remote))
         arr = np.array(triples, np.int64)
         t1 = time.perf_counter()
-        moved = cpu_apply.apply(arr, self.cores)
+        moved = cpu_apply.apply(arr, self.cores if threads is None else threads)
         t2 = time.perf_counter()
         assert moved == self.payload
+        if threads is not None:
+            self.single_s = t2 - t0
+            return t2 - t0
         self.plan_s += t1 - t0
         self.apply_s += t2 - t1
         self.reps += 1
@@ -277,6 +281,9 @@ class CpuSample:
             "unit": UNIT,
             "cores": self.cores,
             "kind": "port",
+            "single_thread_value": None if self.single_s is None else self.payload / self.single_s / 1e9,
+            "single_thread_note": "same sample with one copy thread: the reference's stage workers run with "
+                                  "torch.set_num_threads(1) (vllm_rlt/engine/worker.py:38)",
             "sample": (f"all-planes handoff of the first {len(self.lengths)} request(s) cut at {sum(self.lengths)} tokens "
                        f"({self.payload / 1e9:.2f} GB payload), {self.reps} repetitions; Python planner "
                        f"{self.plan_s / self.reps * 1e3:.1f} ms + {self.cores}-thread memcpy {self.apply_s / self.reps * 1e3:.1f} ms "
@@ -289,6 +296,7 @@ def cpu_baseline_sample(w, budget_s=10.0, max_tokens=1024):
     t_end = time.perf_counter() + budget_s
     while sample.reps < 3 or (time.perf_counter() < t_end and sample.reps < 200):
         sample.run_once()
+    sample.run_once(threads=1)
     return sample.result()
 
 
@@ -324,13 +332,14 @@ def run_reference(args, rank, world):
         dt = sample.run_once()
         if i >= args.warmup:
             times.append(dt)
+    sample.run_once(threads=1)
     last = sample.result()
     value = last["value"]
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": statistics.mean(times) * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "u8", "data": "synthetic",
-        "config": config_of(w, args), "cpu_baseline": {k: last[k] for k in ("value", "unit", "cores", "kind", "sample")},
+        "config": config_of(w, args), "cpu_baseline": last,
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }

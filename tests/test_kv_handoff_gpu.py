@@ -607,3 +607,32 @@ def test_dedup_fan_out_reports_bad_exit_planes_and_bad_deeper_blocks():
     for t in D.tensors():
         t.data[tables_d[2][0]] = 0xA5
     assert_pools_equal(gd, D)
+
+
+@pytest.mark.parametrize("variant", [0, 3])
+def test_dedup_scatter_reports_a_negative_exit_plane_and_skips_the_token(variant):
+    """A token whose exit plane is negative has no row on the wire: the scatter reports it, writes nothing for it and
+    touches no block outside the request's own."""
+    k = kh()
+    kind, shape = SHAPES["ouro_bf16_small"]
+    page, planes = shape[4], shape[5]
+    P, D, reqs, exits = dedup_case(kind, shape, 8, [2 * page + 3])
+    (rid, s, e), = reqs
+    gp, gd = GpuPool(P), GpuPool(D)
+    bad = [list(exits[0])]
+    bad[0][s] = -1
+    batch = k.HandoffBatch([P.plane_block_tables(rid)], [D.plane_block_tables(rid)], [(s, e)], block_size=page, exit_planes=bad)
+    packed = torch.zeros(k.packed_bytes(gp.view(), e - s, planes), dtype=torch.uint8, device="cuda")
+    status = k.new_status()
+    k.kv_scatter(packed, gd.view(), batch, mode=k.MODE_DEDUP, status=status, workspace=k.dedup_workspace(batch, planes),
+                 variant=variant)
+    with pytest.raises(ValueError, match="exit plane"):
+        k.raise_for_status(status)
+    assert status.tolist()[0] == 3 and status.tolist()[2] == s and status.tolist()[3] == -1
+    own = sorted(b for table in D.plane_block_tables(rid) for b in table)
+    others = np.setdiff1d(np.arange(D.num_blocks), own)
+    for t in gd.tensors():
+        assert (t.view(torch.uint8)[torch.from_numpy(others).cuda()] == 0xA5).all()
+    # the bad token's own rows kept the sentinel on every plane
+    for plane, table in enumerate(D.plane_block_tables(rid)):
+        assert (gd.key_cache.view(torch.uint8)[table[s // page], :, s % page] == 0xA5).all()

@@ -283,7 +283,12 @@ __device__ __forceinline__ void row_offsets(const TableCopyParams& p, const Unit
     if (p.dst_packed) {
       tok = nth_set_bit(u.sel_mask, rank);
     } else {
-      const int e = p.exit_planes[p.exit_offsets[u.r] + u.tok_lo + tok];
+      int e = p.exit_planes[p.exit_offsets[u.r] + u.tok_lo + tok];
+      if (e < 0) {  // such a token has no row on the wire; index as plane 0 and skip it
+        report(p.status, RLT_STATUS_BAD_PLANE, u.r, u.tok_lo + tok, e);
+        ok = false;
+        e = 0;
+      }
       wire_plane = min(u.plane, e);
       const unsigned long long mask = exit_mask(p, u.r, u.tok_lo, u.n_tok, wire_plane);
       carried = __popcll(mask);
