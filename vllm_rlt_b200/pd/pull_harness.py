@@ -255,17 +255,21 @@ def run_pull(args, rank: int, world: int) -> None:
     staged_bytes = torch.tensor([0 if is_prefill else sum(e["batch"].metadata_bytes for e in edges)], device=device)
     dist.all_reduce(staged_bytes)
 
-    # ---- per-request latency between rank 0 and its first partner: ready flag -> pull -> done flag, timed on the prefill stream
+    # ---- per-request latency between rank 0 and its first partner: ready flag -> pull -> done flag, timed on the prefill
+    # stream. The decode worker knows a request from its reservation on, so it queues wait -> pull -> done ahead of
+    # time; the prefill worker gives it a few milliseconds to do so before it raises the flag (the wait is bounded).
     lat = []
     first_d = partners_of(0)[0]
     probe = min(16, len(assigned(0, first_d, w if rank == 0 else (per_source.get(0) or w))))
     for r in range(probe):
         for repeat in range(2):
             dist.barrier()
+            torch.cuda.synchronize()
             counter += 1
             if rank == 0:
                 e = edges[0]
                 a, z = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                time.sleep(0.004)
                 a.record(stream)
                 kh.kv_signal(e["ready_ptr"], counter)
                 kh.kv_wait(e["done"], counter, kh._lib.MAX_WAIT_NS, status)
@@ -324,7 +328,8 @@ def run_pull(args, rank: int, world: int) -> None:
                     "h2d_bytes_per_step": int(staged_bytes.item()), "d2h_bytes_per_step": 16 * n_decode, "ms_per_step": float(e2e_s.item()) * 1e3,
                     "note": "tables, ranges and exit planes are staged from the host on the decode ranks every step"},
             "latency_ms": {"p50": statistics.median(lat), "max": max(lat), "min": min(lat),
-                           "what": "rank 0 -> its first decode partner: ready flag, pull, done flag; CUDA events on the prefill stream"},
+                           "what": "rank 0 -> its first decode partner: ready flag, pull, done flag; CUDA events on the prefill stream; "
+                                   "the decode side has its wait and pull queued before the flag is raised"},
             "gpu_launches": int(n_launch.item()), "clocks": clock_box[0], "verified": bool(ok.item() == 1.0),
         }
         print(json.dumps(line), flush=True)
