@@ -302,6 +302,9 @@ def run_pull(args, rank: int, world: int) -> None:
         line = {
             "metric": bench.METRIC, "value": value, "unit": bench.UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+            "scaling_note": "N=1 is the intra-device pool-to-pool handoff (HBM-bound); N>=2 moves the same per-pair workload "
+                            "between N/2 prefill and N/2 decode GPUs (NVLink-bound, 900 GB/s nominal per pair): N=2, 4, 8 "
+                            "scale with one another, N=1 is a different bound",
             "vs_baseline": None, "dtype": "u8", "data": "synthetic",
             "config": bench.config_of(w, args, {
                 "split": f"{n_prefill}P:{n_decode}D", "variant": args.variant, "workload_name": args.workload,
