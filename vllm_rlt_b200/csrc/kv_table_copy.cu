@@ -255,7 +255,7 @@ __device__ __forceinline__ Unit decode_unit(const TableCopyParams& p, const int*
   if (kDedup && (p.dst_packed || p.fan)) {
     u.sel_mask = exit_mask(p, u.r, u.tok_lo, u.n_tok, u.plane);
     // Fan-out: every token has a row on plane 0, so an exit plane below 0 is seen (and reported) there.
-    if (p.fan && u.plane == 0) u.sel_mask = u.n_tok >= 64 ? ~0ull : (1ull << u.n_tok) - 1ull;
+    if (p.fan && !p.src_packed && u.plane == 0) u.sel_mask = u.n_tok >= 64 ? ~0ull : (1ull << u.n_tok) - 1ull;
     u.n_sel = __popcll(u.sel_mask);
   }
   u.rows = u.n_layers * u.n_sel;
@@ -401,13 +401,14 @@ __global__ void __launch_bounds__(kThreads, 4) table_copy_kernel(const TableCopy
 }
 
 // ---------------------------------------------------------------------------------------------
-// Fan-out flavour of the pool-to-pool dedup handoff. The destination of RLT_MODE_DEDUP holds, on every
+// Fan-out flavour of the dedup handoff and of the dedup scatter. The destination of RLT_MODE_DEDUP holds, on every
 // plane deeper than a token's exit plane, a copy of the exit-plane row. The kernel above produces that by
 // walking destination planes, which reads the exit-plane row once per plane it fills. Here the walk is over
 // SOURCE planes: the unit of plane q loads the rows of the tokens that reach q (exit plane >= q) once,
 // stores them to plane q, and stores the rows of the tokens that stop at q to every deeper plane as well.
 // Bytes read = the dedup wire image, bytes written = the full destination; with the source behind a peer
-// pointer only the wire image crosses the link.
+// pointer only the wire image crosses the link. The scatter of a dedup wire image is the same walk with the
+// rows of plane q taken from the image (they are stored there compacted, plane by plane) instead of a pool.
 constexpr long long kFanBit = 1ll << 62;          // in a destination offset: the row also goes to the deeper planes
 constexpr long long kNoPlane = -(1ll << 62);      // in a plane delta: that plane's block is invalid, skip it
 constexpr int kFanMaxPlanes = 64;
@@ -457,7 +458,8 @@ __device__ __forceinline__ void fan_row_offsets(const TableCopyParams& p, const 
                                                 long long* src_off, long long* dst_off) {
   const RegionParams& rg = p.region[u.g];
   const int l_rel = row / u.n_sel;
-  const int tok = nth_set_bit(u.sel_mask, row - l_rel * u.n_sel);
+  const int rank = row - l_rel * u.n_sel;
+  const int tok = nth_set_bit(u.sel_mask, rank);
   const int layer = u.layer0 + l_rel;
   const int t_abs = u.tok_lo + tok;
   const bool deep_ok = p.deep_layer_mask == 0 || ((p.deep_layer_mask >> layer) & 1ull) != 0;
@@ -468,19 +470,35 @@ __device__ __forceinline__ void fan_row_offsets(const TableCopyParams& p, const 
     ok = false;
   }
   const long long in_block = layer * rg.layer_bytes + (t_abs - u.logical * p.block_size) * rg.token_bytes;
-  const int sb = p.src_tables[(static_cast<long long>(u.r) * p.src_planes + u.plane) * p.table_width + u.logical];
-  const int db = p.dst_tables[(static_cast<long long>(u.r) * p.dst_planes + u.plane) * p.table_width + u.logical];
-  if (sb < 0 || sb >= p.src_blocks) {
-    report(p.status, RLT_STATUS_BAD_BLOCK, u.r, u.logical, sb);
-    ok = false;
+  long long so;
+  if (p.src_packed) {
+    // The wire image holds this plane's rows of the block compacted: same walk order as the pack side.
+    const int slice_layers = p.layer_end - p.layer_begin;
+    const int entry = p.src_planes * u.blk_first + u.plane * u.n_blk + (u.logical - u.begin / p.block_size);
+    so = static_cast<long long>(p.dedup_prefix[entry]) * p.packed_token_bytes;
+    if (u.g == 1) so += 2ll * slice_layers * u.n_sel * p.region[0].token_bytes;
+    so += (static_cast<long long>(u.kv) * slice_layers * u.n_sel +
+           static_cast<long long>(layer - p.layer_begin) * u.n_sel + rank) * rg.token_bytes;
+    if (so + rg.token_bytes > p.packed_bytes) {
+      report(p.status, RLT_STATUS_BAD_RANGE, u.r, u.begin, u.end);
+      ok = false;
+    }
+  } else {
+    const int sb = p.src_tables[(static_cast<long long>(u.r) * p.src_planes + u.plane) * p.table_width + u.logical];
+    if (sb < 0 || sb >= p.src_blocks) {
+      report(p.status, RLT_STATUS_BAD_BLOCK, u.r, u.logical, sb);
+      ok = false;
+    }
+    so = sb * rg.block_bytes + in_block;
   }
+  const int db = p.dst_tables[(static_cast<long long>(u.r) * p.dst_planes + u.plane) * p.table_width + u.logical];
   if (db < 0 || db >= p.dst_blocks) {
     report(p.status, RLT_STATUS_BAD_BLOCK, u.r, u.logical, db);
     ok = false;
   }
   long long dof = db * rg.block_bytes + in_block;
   if (e == u.plane && u.plane + 1 < p.dst_planes && deep_ok) dof |= kFanBit;
-  *src_off = ok ? sb * rg.block_bytes + in_block : -1;
+  *src_off = ok ? so : -1;
   *dst_off = ok ? dof : -1;
 }
 
@@ -507,6 +525,13 @@ __global__ void __launch_bounds__(kThreads, 3) table_fan_kernel(const TableCopyP
     long long* rd = row_dst[parity];
     long long* pd = plane_delta[parity];
     if (threadIdx.x < u.rows) fan_row_offsets(p, u, threadIdx.x, &rs[threadIdx.x], &rd[threadIdx.x]);
+    // A token with a negative exit plane has no row in a wire image, so no row above sees it: one unit per block looks.
+    if (p.src_packed && u.plane == 0 && u.g == 0 && u.kv == 0 && u.layer0 == p.layer_begin &&
+        static_cast<int>(threadIdx.x) < u.n_tok) {
+      const int t_abs = u.tok_lo + static_cast<int>(threadIdx.x);
+      const int e = p.exit_planes[p.exit_offsets[u.r] + t_abs];
+      if (e < 0) report(p.status, RLT_STATUS_BAD_PLANE, u.r, t_abs, e);
+    }
     // Threads of the back of the CTA fetch the deeper planes' blocks, as byte distances from this plane's block.
     const int pl = kThreads - 1 - static_cast<int>(threadIdx.x);
     if (u.rows > 0 && pl > u.plane && pl < p.dst_planes) {
@@ -1060,9 +1085,10 @@ int launch_table_copy(Direction dir, const RltPool* src, const RltPool* dst, con
   }
   int flavour = opt->variant & 0xf;
   if (flavour > 6) return RLT_E_INVALID;
-  // Pool-to-pool dedup over every plane: read each row once and fan it out, unless flavour 6 asks for the
-  // walk over destination planes (kept for comparison; the bulk flavours 3 and 4 keep that walk too).
-  const bool fan = dir == kDirect && opt->mode == RLT_MODE_DEDUP && p.plane_begin == 0 &&
+  // Dedup into a pool (from a pool or from the wire image) over every plane: read each row once and fan it out,
+  // unless flavour 6 asks for the walk over destination planes (kept for comparison; the bulk flavours 3 and 4
+  // keep that walk too).
+  const bool fan = (dir == kDirect || dir == kScatter) && opt->mode == RLT_MODE_DEDUP && p.plane_begin == 0 &&
                    p.plane_count == p.dst_planes && p.dst_planes > 1 && p.dst_planes <= kFanMaxPlanes &&
                    flavour != 3 && flavour != 4 && flavour != 6;
   if (flavour == 6) flavour = 0;

@@ -89,8 +89,8 @@ def main() -> None:
     ms = timed(lambda: kh.kv_pack(sv, batch, packed, mode=kh.MODE_DEDUP, status=status, workspace=ws))
     report("dedup plan (3 kernels) + table_copy_kernel pack dedup", 2 * wire, ms, wire_fraction=round(wire / full, 3))
     ms = timed(lambda: kh.kv_scatter(packed[:wire], dv, batch, mode=kh.MODE_DEDUP, status=status, workspace=ws))
-    report("dedup plan (3 kernels) + table_copy_kernel scatter dedup", wire + full, ms,
-           note="reads the wire image once per destination plane it feeds (re-reads come from L2), writes every plane")
+    report("dedup plan (3 kernels) + table_fan_kernel scatter dedup", wire + full, ms,
+           note="reads the wire image once, writes every plane")
     kh.raise_for_status(status)
 
     # explicit ranges
