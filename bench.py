@@ -480,7 +480,7 @@ def run_single(args):
         "gpu_launches": launches, "clocks": clocks, "verified": verified,
     }
     if cpu is not None:
-        line["cpu_baseline"] = {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")}
+        line["cpu_baseline"] = cpu
     print(json.dumps(line), flush=True)
 
 
