@@ -572,7 +572,7 @@ __global__ void __launch_bounds__(kThreads, 3) table_fan_kernel(const TableCopyP
 // so kBulkLag loads are in flight per warp while earlier stores drain. A stage is reused only
 // after cp.async.bulk.wait_group.read has confirmed that the store which last used it has read
 // it. Regions whose rows are too small or not 16-byte multiples (scale rows) are copied by the
-// warp with ordinary loads and stores. No multicast qualifier is used anywhere, and every wait
+// warp with ordinary loads and stores. Every bulk copy is a plain one-CTA copy, and every wait
 // on an mbarrier is bounded: if a load never lands the warp records RLT_STATUS_STALL and stops.
 constexpr int kBulkWarps = 6;
 constexpr int kBulkThreads = kBulkWarps * 32;
