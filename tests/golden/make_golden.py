@@ -406,17 +406,20 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", default=os.environ.get("VLLM_RLT_REFERENCE", str(HERE.parents[2] / "reference")),
                     help="path of the vllm-rlt checkout (default: $VLLM_RLT_REFERENCE or a sibling of this repository)")
+    ap.add_argument("--out", default=str(HERE), help="directory the fixtures are written to (default: beside this script)")
     args = ap.parse_args()
     sys.path.insert(0, args.reference)
     import torch
 
     torch.set_num_threads(1)
-    (HERE / "segments.json").write_text(json.dumps(segment_cases(), indent=0))
-    (HERE / "partition.json").write_text(json.dumps(partition_cases(), indent=0))
-    (HERE / "handoff.json").write_text(json.dumps(handoff_cases(HERE), indent=0))
-    (HERE / "finalize.json").write_text(json.dumps(finalize_cases(HERE), indent=0))
-    (HERE / "allocation.json").write_text(json.dumps(allocation_cases(), indent=0))
-    print("golden fixtures written to", HERE)
+    out = Path(args.out)
+    out.mkdir(parents=True, exist_ok=True)
+    (out / "segments.json").write_text(json.dumps(segment_cases(), indent=0))
+    (out / "partition.json").write_text(json.dumps(partition_cases(), indent=0))
+    (out / "handoff.json").write_text(json.dumps(handoff_cases(out), indent=0))
+    (out / "finalize.json").write_text(json.dumps(finalize_cases(out), indent=0))
+    (out / "allocation.json").write_text(json.dumps(allocation_cases(), indent=0))
+    print("golden fixtures written to", out)
 
 
 if __name__ == "__main__":

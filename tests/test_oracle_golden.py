@@ -226,3 +226,34 @@ def test_finalize_and_exit_modes_match_reference(case):
                     a.data[one[0][t // D1.block_size], :, t % D1.block_size],
                     b.data[req["dst_tables"][e][t // D1.block_size], :, t % D1.block_size],
                 )
+
+
+def test_committed_fixtures_are_what_the_reference_produces_today(tmp_path):
+    """Re-runs the generator against the reference checkout (where present) and compares every fixture with the
+    committed one: JSON documents as parsed values, pool dumps array by array."""
+    import json
+    import os
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    import numpy as np
+    import pytest
+
+    golden = Path(__file__).resolve().parent / "golden"
+    reference = Path(os.environ.get("VLLM_RLT_REFERENCE", str(golden.parents[2] / "reference")))
+    if not (reference / "vllm_rlt" / "pd" / "transport.py").is_file():
+        pytest.skip("reference checkout not present")
+    done = subprocess.run([sys.executable, str(golden / "make_golden.py"), "--reference", str(reference), "--out", str(tmp_path)],
+                          capture_output=True, text=True, timeout=600)
+    assert done.returncode == 0, done.stderr[-2000:]
+    names = sorted(p.name for p in golden.iterdir() if p.suffix in (".json", ".npz"))
+    assert names == sorted(p.name for p in tmp_path.iterdir())
+    for name in names:
+        if name.endswith(".json"):
+            assert json.loads((golden / name).read_text()) == json.loads((tmp_path / name).read_text()), name
+        else:
+            with np.load(golden / name) as a, np.load(tmp_path / name) as b:
+                assert sorted(a.files) == sorted(b.files), name
+                for key in a.files:
+                    assert np.array_equal(a[key], b[key]), (name, key)
