@@ -9,11 +9,9 @@ from contextlib import nullcontext
 from dataclasses import dataclass
 from types import SimpleNamespace
 
-import numpy as np
 import pytest
 import torch
 
-from oracle import handoff_oracle as ho
 from tests.fakes import FakeBackend, FakeEngine, FakeEvent
 from vllm_rlt_b200.core.kv_pool import KVPool
 from vllm_rlt_b200.pd.config import PDConfig

@@ -83,7 +83,6 @@ def run_pull(args, rank: int, world: int) -> None:
     deep = w.extra.get("deep_layers")
     kw = dict(device=device, kv_cache_dtype="fp8_e4m3" if s.fp8 else "auto")
     fan = max(len(partners_of(r)) for r in range(world))
-    n_pool = 4 if s.fp8 else 2
 
     # ---- set-up: pools, reservation on the decode side, handles of pools and flags to everyone --------------
     handle_msg = torch.zeros((4 + fan, exchange.HANDLE_ROW), dtype=torch.uint8, device=device)

@@ -17,7 +17,6 @@ from __future__ import annotations
 import json
 import os
 import random
-import statistics
 
 import numpy as np
 

@@ -10,7 +10,6 @@ CUDA tensors and host sources must be pinned.
 
 from __future__ import annotations
 
-import numpy as np
 import torch
 
 from .. import _lib
