@@ -18,7 +18,7 @@ def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--requests", type=int, default=2)
     ap.add_argument("--steps", type=int, default=3)
-    ap.add_argument("--mode", default="exit_only", choices=["exit_only", "all"])
+    ap.add_argument("--mode", default="exit_only", choices=["exit_only", "all", "dedup"])
     ap.add_argument("--variant", type=int, default=0, help="kernel flavour (RltOptions.variant)")
     ap.add_argument("--pull", action="store_true", help="run the kernel on the destination GPU and read the source over the link")
     args = ap.parse_args()
@@ -51,7 +51,7 @@ def main() -> None:
     batch = kh.HandoffBatch(w.src_tables, w.dst_tables, w.ranges, block_size=s.block_size, exit_planes=w.exit_planes,
                             device=f"cuda:{run_on}")
     status = kh.new_status(f"cuda:{run_on}")
-    mode = kh.MODE_EXIT_ONLY if args.mode == "exit_only" else kh.MODE_ALL_PLANES
+    mode = {"exit_only": kh.MODE_EXIT_ONLY, "all": kh.MODE_ALL_PLANES, "dedup": kh.MODE_DEDUP}[args.mode]
     times = []
     for i in range(1 + args.steps):
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -71,14 +71,18 @@ def main() -> None:
     e = torch.tensor(np.asarray(w.exit_planes[0][:n]), device="cuda:0").long() if w.exit_planes is not None else None
     ok = True
     for plane in range(w.dst_planes):
-        sp = e if args.mode == "exit_only" else torch.full((n,), plane, device="cuda:0")
+        sp = e if args.mode == "exit_only" else torch.clamp(e, max=plane) if args.mode == "dedup" else torch.full((n,), plane, device="cuda:0")
         st = torch.tensor(np.stack([np.asarray(t) for t in w.src_tables[0]]), device="cuda:0").long()
         want = src.key_cache[st[sp, pos // s.block_size], :, pos % s.block_size].to("cuda:1")
         db = torch.tensor(np.asarray(w.dst_tables[0][plane]), device="cuda:1").long()[(pos // s.block_size).to("cuda:1")]
         got = dst.key_cache[db, :, (pos % s.block_size).to("cuda:1")]
         ok = ok and bool(torch.equal(want.view(torch.int16), got.view(torch.int16)))
     ms = statistics.median(times)
-    print(json.dumps({"direction": "pull (kernel on the destination GPU)" if args.pull else "push (kernel on the source GPU)",
+    # bytes that must cross the link: in dedup mode with the kernel on the destination GPU, rows up to each exit plane
+    link = w.payload_bytes
+    if args.mode == "dedup" and args.pull:
+        link = sum(int(np.minimum(np.asarray(x[lo:hi]) + 1, w.dst_planes).sum()) for x, (lo, hi) in zip(w.exit_planes, w.ranges)) * s.token_plane_bytes
+    print(json.dumps({"link_bytes": link, "direction": "pull (kernel on the destination GPU)" if args.pull else "push (kernel on the source GPU)",
                       "payload_bytes": w.payload_bytes, "ms": ms, "gbps": w.payload_bytes / ms / 1e6, "verified": ok}), flush=True)
 
 
