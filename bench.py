@@ -7,6 +7,13 @@ whole synthetic batch. At N=1 the workload is the intra-device pool-to-pool
 handoff of a LAST_EXITED Ouro-1.4B-shaped source (64 requests, per-token exit
 planes, exit-only into a single-plane pool). Inputs are synthetic and larger
 than L2, so no cache flush is needed between iterations.
+
+Other measurements share the workloads and helpers of this file and print their own JSON lines; they are
+not the benchmark line:
+
+    python bench.py --suite kernels [--requests 8]      every other kernel of the library on one GPU
+    python bench.py --suite peer [--pull] [--mode ...]  one process, two GPUs: the handoff kernel over NVLink
+    python bench.py --suite deployment [...]            a vllm-rlt 1P:1D deployment with this connector swapped in
 """
 
 from __future__ import annotations
@@ -27,7 +34,10 @@ sys.path.insert(0, str(ROOT))
 METRIC = "kv_handoff_gbps"
 UNIT = "GB/s"
 FALLBACK_HBM_GBS = 6650.0
-NVLINK_MEASURED_GBS = 770.0
+# NVLink 5, one direction, per GPU. The nominal figure is what the fractions are quoted against; the other is one
+# builder-run peer-to-peer memcpy on a B200 pair, kept for context only (it is not a driver-written peak).
+NVLINK_NOMINAL_GBS = 900.0
+NVLINK_PEER_MEMCPY_GBS = 770.0
 # link bytes per payload byte for writes over NVLink (ncu: nvltx__bytes.sum / nvltx__bytes_data_user.sum of the handoff kernel)
 NVLINK_WRITE_OVERHEAD = 1.1875
 # the same for read responses when the destination GPU pulls (ncu: nvlrx__bytes.sum / nvlrx__bytes_data_user.sum)
@@ -47,7 +57,7 @@ def measured_peaks():
             return float(data["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
         except Exception:
             pass
-    return FALLBACK_HBM_GBS, "fallback (6.65 TB/s, earlier measurement on this pool)"
+    return FALLBACK_HBM_GBS, "fallback (6.65 TB/s, an earlier STREAM-style copy measurement on B200)"
 
 
 class ClockSampler:
@@ -194,14 +204,48 @@ def spot_check(w, src, dst, requests=None):
 # ------------------------------------------------------------------------------- CPU baseline (oracle)
 
 
+def reference_checkout():
+    """A vllm-rlt source tree that travelled with this repository, or None.
+
+    ``$VLLM_RLT_REFERENCE`` if set (and nothing else then), else ``baseline/_ref/src`` under this file (a
+    git-ignored, unmodified copy). Only its planner is imported (plain Python, no NIXL, no GPU).
+    """
+    candidate = os.environ.get("VLLM_RLT_REFERENCE") or str(ROOT / "baseline" / "_ref" / "src")
+    if (Path(candidate) / "vllm_rlt" / "pd" / "transport.py").is_file():
+        return Path(candidate)
+    return None
+
+
+def cpu_planner():
+    """(kv_segments, partition_segments, kind, what): the reference's own planner when a checkout is present
+    (vllm_rlt/pd/transport.py:29-112), else the restatement of it under ``oracle/``."""
+    checkout = reference_checkout()
+    if checkout is not None:
+        sys.path.insert(0, str(checkout))
+        try:
+            from vllm_rlt.pd.transport import kv_segments, partition_segments
+
+            return kv_segments, partition_segments, "reference", "the reference's kv_segments / partition_segments (imported from its source tree)"
+        except Exception as exc:  # a broken checkout must not take the baseline down with it
+            note = f"reference checkout found but not importable ({type(exc).__name__}); "
+        finally:
+            sys.path.remove(str(checkout))
+    else:
+        note = ""
+    from oracle import handoff_oracle as ho
+
+    return ho.kv_segments, ho.partition_segments, "port", note + "the restatement of kv_segments / partition_segments under oracle/"
+
+
 class CpuSample:
-    """The CPU restatement of the reference path on a bounded slice of the workload.
+    """The reference's CPU path on a bounded slice of the workload.
 
     The reference always sends every plane of a prompt (it has no exit-plane selection), so the
     sample is the all-planes handoff of the workload's first requests, cut off at ``max_tokens``
-    tokens in total: Python planner (kv_segments on both sides + partition_segments, as the
-    reference runs it) and a threaded memcpy of the resulting descriptors. Pools are touched
-    once at set-up so that first-touch page faults stay out of the timing.
+    tokens in total: the Python planner as the reference runs it (kv_segments on both sides +
+    partition_segments at the reference's limits of 256 MiB and 256 descriptors) and a threaded
+    memcpy of the resulting descriptors, which stands in for the NIXL WRITE (third-party, absent).
+    Pools are touched once at set-up so that first-touch page faults stay out of the timing.
     """
 
     def __init__(self, w, max_tokens=1024):
@@ -210,7 +254,9 @@ class CpuSample:
         from oracle import handoff_oracle as ho
 
         self.ho = ho
+        self.kv_segments, self.partition_segments, self.kind, self.planner_note = cpu_planner()
         s = w.shape
+        self.shape = s
         self.cores = len(os.sched_getaffinity(0))
         lengths, left = [], max_tokens
         for n in w.lengths:
@@ -248,13 +294,13 @@ class CpuSample:
 
         from oracle import cpu_apply
 
-        ho, P, D = self.ho, self.P, self.D
+        P, D = self.P, self.D
         t0 = time.perf_counter()
         triples = []
         for i, n in enumerate(self.lengths):
-            src = ho.kv_segments(P.info(), P.plane_block_tables(f"r{i}"), 0, n)
-            dst = ho.kv_segments(D.info(), D.plane_block_tables(f"r{i}"), 0, n)
-            for local, remote, _ in ho.partition_segments(src, dst, 256 * 1024**2, 256):
+            src = self.kv_segments(P.info(), P.plane_block_tables(f"r{i}"), 0, n)
+            dst = self.kv_segments(D.info(), D.plane_block_tables(f"r{i}"), 0, n)
+            for local, remote, _ in self.partition_segments(src, dst, 256 * 1024**2, 256):
                 triples.extend((self._real(a), self._real(b), m) for (a, m, _), (b, _, _) in zip(local, remote))
         arr = np.array(triples, np.int64)
         t1 = time.perf_counter()
@@ -269,6 +315,24 @@ class CpuSample:
         self.reps += 1
         return t2 - t0
 
+    def description(self) -> str:
+        return (f"all planes (the reference carries every plane), the first {len(self.lengths)} request(s) of the workload "
+                f"cut at {sum(self.lengths)} tokens")
+
+    def config(self, w) -> dict:
+        """What this arm really moved per step, with the full workload it was cut from beside it."""
+        return {
+            "workload": w.description,
+            "sample": self.description(),
+            "requests": len(self.lengths),
+            "tokens": sum(self.lengths),
+            "payload_bytes": self.payload,
+            "mode": "all",
+            "l2": "sample larger than the host caches",
+            "cut_from": {"requests": len(w.lengths), "tokens": w.tokens, "payload_bytes": w.payload_bytes,
+                         "mode": w.extra.get("mode")},
+        }
+
     def result(self):
         import numpy as np
 
@@ -276,18 +340,22 @@ class CpuSample:
         first_dst = self.D.plane_block_tables("r0")[0][0]
         ok = all(np.array_equal(a.data[first_src], b.data[first_dst]) for a, b in zip(self.P.tensors(), self.D.tensors()))
         total = self.plan_s + self.apply_s
+        single = None if self.single_s is None else self.payload / self.single_s / 1e9
         return {
             "value": self.payload * self.reps / total / 1e9,
             "unit": UNIT,
             "cores": self.cores,
-            "kind": "port",
-            "single_thread_value": None if self.single_s is None else self.payload / self.single_s / 1e9,
-            "single_thread_note": "same sample with one copy thread: the reference's stage workers run with "
-                                  "torch.set_num_threads(1) (vllm_rlt/engine/worker.py:38)",
-            "sample": (f"all-planes handoff of the first {len(self.lengths)} request(s) cut at {sum(self.lengths)} tokens "
-                       f"({self.payload / 1e9:.2f} GB payload), {self.reps} repetitions; Python planner "
+            "kind": self.kind,
+            "planner": self.planner_note,
+            "sample_bytes": self.payload,
+            "single_thread_value": single,
+            "reference_worker_setting": "single_thread_value: a stage worker of the reference runs with "
+                                        "torch.set_num_threads(1) (vllm_rlt/engine/worker.py:38); `value` gives the CPU "
+                                        f"every host core ({self.cores} copy threads), which the reference never does, so "
+                                        "ratios against `value` are a floor",
+            "sample": (f"{self.description()} ({self.payload / 1e9:.2f} GB payload), {self.reps} repetitions; Python planner "
                        f"{self.plan_s / self.reps * 1e3:.1f} ms + {self.cores}-thread memcpy {self.apply_s / self.reps * 1e3:.1f} ms "
-                       f"per repetition; pools pre-touched; byte-exact: {ok}"),
+                       f"per repetition; the memcpy stands in for the NIXL WRITE; pools pre-touched; byte-exact: {ok}"),
         }
 
 
@@ -339,7 +407,7 @@ def run_reference(args, rank, world):
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": statistics.mean(times) * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "u8", "data": "synthetic",
-        "config": config_of(w, args), "cpu_baseline": last,
+        "config": sample.config(w), "cpu_baseline": last,
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -484,6 +552,297 @@ def run_single(args):
     print(json.dumps(line), flush=True)
 
 
+# ------------------------------------------------------------------------------- other measurements
+
+
+def _timed(fn, reps=7, warm=2):
+    import torch
+
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    out = []
+    for _ in range(reps):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        out.append(a.elapsed_time(b))
+    return statistics.median(out)
+
+
+def suite_kernels(args):
+    """Every kernel of the library other than the headline handoff, on one GPU: one JSON line each.
+
+    Bytes are the algorithmic bytes a kernel must move (read + written); ``frac`` is that rate over the HBM
+    copy peak. Inputs are far larger than L2, timings are CUDA events (median of 7 after 2 warm-ups).
+    """
+    import numpy as np
+    import torch
+
+    from vllm_rlt_b200 import workloads
+    from vllm_rlt_b200.core.kv_pool import KVPool
+    from vllm_rlt_b200.kernels import kv_handoff as kh
+    from vllm_rlt_b200.worker.tensors import TensorTransfer, copy_tensor
+
+    peak, peak_note = measured_peaks()
+    only = set(args.only.split(",")) if args.only else None
+
+    def wanted(tag):
+        return only is None or tag in only
+
+    def report(tag, name, nbytes, ms, **extra):
+        gbps = nbytes / ms / 1e6
+        print(json.dumps(dict(suite="kernels", tag=tag, kernel=name, algorithmic_bytes=int(nbytes), ms=round(ms, 4),
+                              gbps=round(gbps, 1), frac=round(gbps / peak, 4), peak=peak, peak_source=peak_note, **extra)),
+              flush=True)
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    w = workloads.last_exited_exit_only(requests=args.requests if args.requests != 64 else 8, mode="dedup")
+    s = w.shape
+    src = KVPool(s.num_layers, s.num_kv_heads, s.head_dim, w.src_blocks, s.block_size, s.planes, device=dev)
+    dst = KVPool(s.num_layers, s.num_kv_heads, s.head_dim, w.dst_blocks, s.block_size, s.planes, device=dev)
+    src.key_cache.normal_()
+    src.value_cache.normal_()
+    sv, dv = kh.PoolView.from_cache(src), kh.PoolView.from_cache(dst)
+    status = kh.new_status(dev)
+    batch = kh.HandoffBatch(w.src_tables, w.dst_tables, w.ranges, block_size=s.block_size, exit_planes=w.exit_planes, device=dev)
+    tokens, ptb = w.tokens, s.token_plane_bytes
+    exits = np.concatenate(w.exit_planes)
+    pairs = int((exits + 1).sum())
+
+    # finalize first: it makes the planes beyond each exit plane copies, which dedup relies on
+    width = batch.table_width
+    tables = torch.zeros((len(w.lengths), s.planes, width), dtype=torch.int32)
+    for i, r in enumerate(w.src_tables):
+        for plane, t in enumerate(r):
+            tables[i, plane, : len(t)] = torch.from_numpy(np.asarray(t))
+    tables = tables.to(dev)
+    rows = torch.from_numpy(np.concatenate([
+        np.stack([np.full(len(e), i, np.int32), np.asarray(e, np.int32), np.arange(len(e), dtype=np.int32)], 1)
+        for i, e in enumerate(w.exit_planes)])).to(dev)
+    copies = int((s.planes - 1 - exits).sum())
+    sources = int((exits < s.planes - 1).sum())
+    if wanted("finalize"):
+        ms = _timed(lambda: kh.kv_finalize(sv, tables, rows, status=status))
+        report("finalize", "finalize_fan_kernel", (sources + copies) * ptb, ms, rows=len(rows), source_rows=sources,
+               copied_rows=copies, note="each exit row with deeper planes is read once and written once per deeper plane")
+        few = rows[:256].contiguous()  # what one decode step finalizes
+        ms = _timed(lambda: kh.kv_finalize(sv, tables, few, status=status))
+        fe = exits[:256]
+        report("finalize", "finalize_fan_kernel (256 rows, one decode step)",
+               (int((fe < s.planes - 1).sum()) + int((s.planes - 1 - fe).sum())) * ptb, ms, rows=256)
+    else:
+        kh.kv_finalize(sv, tables, rows, status=status)
+
+    full = kh.packed_bytes(sv, tokens, s.planes)
+    packed = torch.empty(full, dtype=torch.uint8, device=dev)
+    wire = pairs * ptb
+    if wanted("pack"):
+        ms = _timed(lambda: kh.kv_pack(sv, batch, packed, status=status))
+        report("pack", "table_copy_kernel pack all planes", 2 * full, ms)
+        ms = _timed(lambda: kh.kv_scatter(packed, dv, batch, status=status))
+        report("pack", "table_copy_kernel scatter all planes", 2 * full, ms)
+        ws = kh.dedup_workspace(batch, s.planes, dev)
+        ms = _timed(lambda: kh.kv_pack(sv, batch, packed, mode=kh.MODE_DEDUP, status=status, workspace=ws))
+        report("pack", "dedup plan (3 kernels) + table_copy_kernel pack dedup", 2 * wire, ms, wire_fraction=round(wire / full, 3))
+        ms = _timed(lambda: kh.kv_scatter(packed[:wire], dv, batch, mode=kh.MODE_DEDUP, status=status, workspace=ws))
+        report("pack", "dedup plan (3 kernels) + table_fan_kernel scatter dedup", wire + full, ms,
+               note="reads the wire image once, writes every plane")
+    kh.raise_for_status(status)
+
+    if wanted("segments"):
+        block = src.key_cache.stride(0) * 2
+        blocks = min(256, w.src_blocks, w.dst_blocks)
+        segs = torch.tensor([(src.key_cache.data_ptr() + i * block, dst.key_cache.data_ptr() + (blocks - 1 - i) * block, block)
+                             for i in range(blocks)], dtype=torch.int64, device=dev)
+        ms = _timed(lambda: kh.kv_copy_segments(segs))
+        report("segments", "segment_copy_kernel (256 block-sized ranges)", 2 * blocks * block, ms)
+        # the reference planner's mix for a request that ends mid-block: full blocks next to per-layer partial rows
+        mixed = []
+        for i in range(blocks):
+            a, b = src.key_cache.data_ptr() + i * block, dst.key_cache.data_ptr() + (blocks - 1 - i) * block
+            if i % 8 == 7:
+                layer = block // s.num_layers
+                mixed += [(a + l * layer, b + l * layer, 5 * s.num_kv_heads * s.head_dim * 2) for l in range(s.num_layers)]
+            else:
+                mixed.append((a, b, block))
+        mixed = mixed[: kh._lib.MAX_SEGMENTS]
+        mseg = torch.tensor(mixed, dtype=torch.int64, device=dev)
+        ms = _timed(lambda: kh.kv_copy_segments(mseg))
+        report("segments", f"segment_copy_kernel ({len(mixed)} ranges, 1.5 MiB blocks mixed with 20 KiB partial rows)",
+               2 * sum(m[2] for m in mixed), ms)
+        n = min(1 << 30, src.key_cache.numel() * 2)
+        ms = _timed(lambda: kh.kv_push(src.key_cache.data_ptr(), dst.key_cache.data_ptr(), n))
+        report("segments", "push_kernel (one range)", 2 * n, ms)
+
+    if wanted("tensors"):
+        ids = torch.randint(0, 2**40, (1 << 26,), dtype=torch.int64, device=dev)
+        out32 = torch.empty(1 << 26, dtype=torch.int32, device=dev)
+        ms = _timed(lambda: copy_tensor(ids, out32))
+        report("tensors", "flat_transfer_kernel int64 -> int32", (8 + 4) << 26, ms)
+        h = torch.randn(1 << 28, device=dev, dtype=torch.bfloat16)
+        h2 = torch.empty_like(h)
+        ms = _timed(lambda: copy_tensor(h, h2))
+        report("tensors", "flat_transfer_kernel bf16 -> bf16", 4 << 28, ms)
+        hidden = torch.randn(4096, 2048, device=dev, dtype=torch.bfloat16)
+        staged = torch.empty(4096, 2048, device=dev, dtype=torch.bfloat16)
+        tt = TensorTransfer(64, torch.bfloat16, dev)
+        for i in range(64):
+            tt.append(hidden[i * 64 : (i + 1) * 64], staged[(63 - i) * 64 : (64 - i) * 64])
+        ms = _timed(tt.submit)
+        report("tensors", "segmented_transfer_kernel (64 copies of 64 x 2048 bf16)", 2 * hidden.numel() * 2, ms,
+               note="metadata-sized: launch latency, not bandwidth")
+
+
+def suite_peer(args):
+    """One process, two GPUs: a small batch from a pool on cuda:0 to a pool on cuda:1 over NVLink.
+
+    The smallest cross-GPU use of the library (peer access enabled inside one process, no IPC, no flags); also the
+    program to put under a profiler for the link counters of the handoff kernel, since it has a single rank and
+    nothing waits on anything. ``--pull`` runs the kernel on the destination GPU.
+    """
+    import numpy as np
+    import torch
+
+    from vllm_rlt_b200 import workloads
+    from vllm_rlt_b200.core.kv_pool import KVPool
+    from vllm_rlt_b200.kernels import kv_handoff as kh
+    from vllm_rlt_b200.pd import peer, verify
+
+    if torch.cuda.device_count() < 2:
+        raise SystemExit("needs two GPUs")
+    peer.enable_peer_access(0, 1)
+    peer.enable_peer_access(1, 0)
+    run_on = 1 if args.pull else 0
+    torch.cuda.set_device(0)
+    w = workloads.last_exited_exit_only(requests=args.requests if args.requests != 64 else 2, mode=args.mode)
+    s = w.shape
+    src = KVPool(s.num_layers, s.num_kv_heads, s.head_dim, w.src_blocks, s.block_size, s.planes, device="cuda:0")
+    dst = KVPool(s.num_layers, s.num_kv_heads, s.head_dim, w.dst_blocks, s.block_size, w.dst_planes, device="cuda:1")
+    fill_source(src, s, 3)
+    for t in (dst.key_cache, dst.value_cache):
+        t.view(torch.uint8).fill_(0xA5)
+    torch.cuda.synchronize(1)
+    sv, dv = kh.PoolView.from_cache(src), kh.PoolView.from_cache(dst)
+    torch.cuda.synchronize(0)
+    torch.cuda.set_device(run_on)
+    batch = kh.HandoffBatch(w.src_tables, w.dst_tables, w.ranges, block_size=s.block_size, exit_planes=w.exit_planes,
+                            device=f"cuda:{run_on}")
+    status = kh.new_status(f"cuda:{run_on}")
+    mode = {"exit_only": kh.MODE_EXIT_ONLY, "all": kh.MODE_ALL_PLANES, "dedup": kh.MODE_DEDUP}[args.mode]
+    times = []
+    for i in range(1 + max(args.steps, 3)):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        kh.kv_handoff(sv, dv, batch, mode=mode, status=status, variant=args.variant)
+        b.record()
+        torch.cuda.synchronize(run_on)
+        if i:
+            times.append(a.elapsed_time(b))
+    kh.raise_for_status(status)
+    # every row of every request: checksums of the selected source rows on cuda:0 against the destination's on cuda:1
+    torch.cuda.set_device(0)
+    want = verify.source_checksums(src, w, range(len(w.lengths)), args.mode)
+    torch.cuda.set_device(1)
+    got, clean = verify.destination_checksums(dst, w, range(len(w.lengths)), [w.dst_tables[i] for i in range(len(w.lengths))])
+    ok = bool(torch.equal(want.cpu(), got.cpu())) and clean
+    ms = statistics.median(times)
+    link = w.payload_bytes
+    if args.mode == "dedup" and args.pull:
+        link = sum(int(np.minimum(np.asarray(x[lo:hi]) + 1, w.dst_planes).sum()) for x, (lo, hi) in zip(w.exit_planes, w.ranges)) * s.token_plane_bytes
+    print(json.dumps({"suite": "peer", "link_bytes": link,
+                      "direction": "pull (kernel on the destination GPU)" if args.pull else "push (kernel on the source GPU)",
+                      "payload_bytes": w.payload_bytes, "ms": ms, "gbps": w.payload_bytes / ms / 1e6,
+                      "link_gbps": link / ms / 1e6, "frac_of_nominal_900": link / ms / 1e6 / NVLINK_NOMINAL_GBS,
+                      "verified": ok, "verified_bytes": verify.checked_bytes(w, range(len(w.lengths)))}), flush=True)
+
+
+def suite_deployment(args):
+    """A real vllm-rlt 1P:1D deployment with this handoff swapped in; reports per-request handoff latency.
+
+    The deployment is the reference's own ``PDEngine`` (coordinator, stage workers, scheduler, model runner, a
+    random-initialised Ouro-1.4B-shaped model); only the connector is replaced (``dropin.install()``). The
+    vllm-rlt source tree must have travelled with this repository (see ``reference_checkout``); nothing of it is part
+    of this repository. Latencies come from the coordinator's timing marks (vllm_rlt/pd/engine.py:198-240):
+    tail = ``d_received - prefill_compute_completed``, total = ``d_received - prefill_started``.
+    """
+    import random
+
+    checkout = reference_checkout()
+    if checkout is None:
+        print(json.dumps({"suite": "deployment", "unavailable": "no vllm-rlt source tree travelled with the repository"}), flush=True)
+        return
+    sys.path.insert(0, str(checkout))
+    os.environ["PYTHONPATH"] = os.pathsep.join([str(checkout), str(ROOT), os.environ.get("PYTHONPATH", "")])
+    os.environ.setdefault("RLT_KV_DIRECTION", args.direction)
+    from vllm_rlt import CacheConfig, SamplingParams, SchedulerConfig
+    from vllm_rlt.models.ouro import OuroConfig
+    from vllm_rlt.pd.config import PDConfig
+
+    from vllm_rlt_b200.pd import dropin
+
+    dropin.install()
+    from vllm_rlt.pd.engine import PDEngine
+
+    config = OuroConfig()  # the defaults are the Ouro-1.4B shape: 24 layers, 16 KV heads, head_dim 128, 4 loops
+    cache = CacheConfig(args.blocks, 16, "last_exited", kv_cache_dtype=args.kv_dtype)
+    rng = random.Random(0)
+    started = time.monotonic()
+    with PDEngine(
+        config,
+        pd_config=PDConfig(prefill_devices=(0,), decode_devices=(1,), startup_timeout=600, request_timeout=600),
+        prefill_cache_config=cache,
+        decode_cache_config=cache,
+        prefill_scheduler_config=SchedulerConfig(max_num_seqs=8, max_num_batched_tokens=args.chunk, prefill_chunk_size=args.chunk),
+        decode_scheduler_config=SchedulerConfig(max_num_seqs=32, max_num_batched_tokens=32),
+        attention_backend="triton",
+        seed=1,
+    ) as engine:
+        startup = time.monotonic() - started
+        params = SamplingParams(max_tokens=2, ignore_eos=True)
+
+        def drain():
+            deadline = time.monotonic() + 600
+            while engine.has_unfinished_requests():
+                engine.step()
+                if time.monotonic() > deadline:
+                    raise TimeoutError("deployment did not finish")
+
+        engine.add_request("warm", [rng.randrange(config.vocab_size) for _ in range(args.tokens)], params)
+        drain()
+        engine.metrics.clear()
+        n_req = args.requests if args.requests != 64 else 8
+        for at in range(0, n_req, args.concurrency):
+            for i in range(at, min(n_req, at + args.concurrency)):
+                engine.add_request(f"r{i}", [rng.randrange(config.vocab_size) for _ in range(args.tokens)], params)
+            drain()
+        marks = [m["timings"] for m in engine.metrics if not m["cancelled"]]
+    worker_metrics = engine.worker_metrics
+    tail = [(t["d_received"] - t["prefill_compute_completed"]) * 1e3 for t in marks]
+    total = [(t["d_received"] - t["prefill_started"]) * 1e3 for t in marks]
+    prefill = [(t["prefill_compute_completed"] - t["prefill_started"]) * 1e3 for t in marks]
+    sent = sum(m.get("bytes_sent", 0) for m in worker_metrics.values())
+    seconds = sum(m.get("transfer_seconds", 0.0) for m in worker_metrics.values())
+    per_request = args.tokens * config.total_ut_steps * 2 * config.num_hidden_layers * config.num_key_value_heads * config.head_dim * (
+        2 if args.kv_dtype == "auto" else 1)
+    print(json.dumps({
+        "suite": "deployment",
+        "deployment": "vllm-rlt PDEngine 1P:1D, Ouro-1.4B shape, random weights, B200 handoff connector, direction "
+                      + os.environ["RLT_KV_DIRECTION"],
+        "requests": len(marks), "prompt_tokens": args.tokens, "prefill_chunk": args.chunk, "concurrency": args.concurrency,
+        "kv_bytes_per_request": per_request,
+        "handoff_tail_ms": {"p50": statistics.median(tail), "max": max(tail), "min": min(tail)},
+        "handoff_total_ms": {"p50": statistics.median(total)},
+        "prefill_ms": {"p50": statistics.median(prefill)},
+        "bytes_sent": sent, "transfers": sum(m.get("transfers", 0) for m in worker_metrics.values()),
+        "transfer_seconds_sum": seconds,
+        "gbps_while_transferring": (sent / seconds / 1e9) if seconds else None, "startup_s": startup,
+    }), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -506,7 +865,19 @@ def main():
                     help="N >= 2, direct path: the prefill GPU writes into the decode pool, or the decode GPU reads the prefill pool")
     ap.add_argument("--path", default="direct", choices=["direct", "staged"],
                     help="N >= 2: one kernel that writes destination blocks over NVLink, or pack into peer staging + scatter")
+    ap.add_argument("--suite", default=None, choices=["kernels", "peer", "deployment"],
+                    help="another measurement instead of the benchmark line (see the module docstring)")
+    ap.add_argument("--only", default="", help="--suite kernels: comma-separated groups (finalize,pack,segments,tensors)")
+    ap.add_argument("--pull", action="store_true", help="--suite peer: run the kernel on the destination GPU")
+    ap.add_argument("--tokens", type=int, default=2048, help="--suite deployment: prompt length")
+    ap.add_argument("--blocks", type=int, default=8192, help="--suite deployment: pool blocks per worker")
+    ap.add_argument("--concurrency", type=int, default=1, help="--suite deployment: requests submitted at once")
+    ap.add_argument("--chunk", type=int, default=2048, help="--suite deployment: prefill chunk size")
+    ap.add_argument("--kv-dtype", default="auto", choices=["auto", "fp8_e4m3"], help="--suite deployment")
     args = ap.parse_args()
+    if args.suite is not None:
+        {"kernels": suite_kernels, "peer": suite_peer, "deployment": suite_deployment}[args.suite](args)
+        return
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

@@ -112,6 +112,9 @@ typedef struct RltBatch {
   const int32_t* tok_end;      /* [num_requests]; a request with end <= begin moves nothing     */
   const int32_t* exit_planes;  /* NULL, or per-token zero-based exit plane (DEDUP / EXIT_ONLY)  */
   const int64_t* exit_offsets; /* [num_requests]: index in exit_planes of the request's token 0 */
+  int64_t exit_count;          /* entries in exit_planes; a request whose exit_offsets[r] is negative or
+                                  whose exit_offsets[r] + tok_end[r] exceeds it is reported as
+                                  RLT_STATUS_BAD_RANGE and skipped, so no kernel reads past the array */
 } RltBatch;
 
 #define RLT_MAX_REQUESTS 4096

@@ -402,6 +402,88 @@ def allocation_cases():
     return out
 
 
+def reservation_cases():
+    """Traces of the reference's decode-side reservation hook: ``StageEngine.reserve_transfer`` (which plans the
+    admission, allocates and pins), ``accept_import`` (which publishes the imported prompt to the prefix cache) and
+    ``release_transfer``, on a real ``StageEngine`` with a tiny CPU model. Every step records what the connector
+    would see (tables, prefix hit) and the pool's free-block count, so an implementation of the hook can be replayed
+    against it. Prompts are lists of token ids below the tiny model's vocabulary of 64; ``max_tokens`` drives the
+    growth budget."""
+    import torch
+
+    from tests.helpers import tiny_ouro_config
+    from vllm_rlt import CacheConfig, SamplingParams, SchedulerConfig
+    from vllm_rlt.engine.stage_config import StageConfig
+    from vllm_rlt.engine.stage_engine import StageEngine
+    from vllm_rlt.models import OuroForCausalLM
+
+    scenarios = {
+        # D holds a 3-page prefix from an earlier import; the next prompts share 3, 1 and 0 pages of it
+        "prefix_hits": dict(
+            cache=dict(num_blocks=64, block_size=4, enable_prefix_caching=True), chunk=8, seqs=4,
+            steps=[("reserve", "a", list(range(1, 14)), 3), ("accept", "a"),
+                   ("reserve", "b", list(range(1, 13)) + [40, 41, 42], 2), ("reserve", "c", list(range(1, 6)) + [50, 51, 52, 53], 1),
+                   ("reserve", "d", [55, 56, 57, 58, 59], 4), ("accept", "b"), ("release", "a"), ("release", "c"),
+                   ("reserve", "e", list(range(1, 13)) + [40, 41, 42, 43, 44], 1), ("release", "b"), ("release", "d"), ("release", "e")]),
+        # a pool too small for two prompts at once: the second reservation is rejected whole and succeeds after a release
+        "rejection_leaves_nothing": dict(
+            cache=dict(num_blocks=24, block_size=4), chunk=8, seqs=4,
+            steps=[("reserve", "a", list(range(1, 16)), 2), ("reserve", "b", list(range(20, 31)), 2), ("release", "a"),
+                   ("reserve", "b", list(range(20, 31)), 2), ("release", "b")]),
+        # incremental allocation without preemption: an import's future decode growth stays budgeted
+        "growth_budget": dict(
+            cache=dict(num_blocks=16, block_size=2, incremental_allocation=True), chunk=2, seqs=2,
+            steps=[("reserve", "import", [1, 2], 7), ("reserve", "other", [3, 4], 1), ("release", "import"),
+                   ("reserve", "other", [3, 4], 1), ("release", "other")]),
+        # cached pages held only by the cache count as free, are budgeted when claimed, and are evicted oldest-first
+        "eviction": dict(
+            cache=dict(num_blocks=32, block_size=4, enable_prefix_caching=True), chunk=8, seqs=4,
+            steps=[("reserve", "a", list(range(1, 10)), 1), ("accept", "a"), ("release", "a"),
+                   ("reserve", "b", list(range(1, 10)), 1), ("release", "b"),
+                   ("reserve", "big", [(7 * i) % 61 + 2 for i in range(27)], 2), ("release", "big"),
+                   ("reserve", "c", list(range(1, 10)), 1), ("release", "c")]),
+    }
+    out = []
+    for name, sc in scenarios.items():
+        config = tiny_ouro_config()
+        torch.manual_seed(0)
+        engine = StageEngine(
+            OuroForCausalLM(config), stage_config=StageConfig(role="decode"),
+            cache_config=CacheConfig(sc["cache"]["num_blocks"], sc["cache"]["block_size"],
+                                     **{k: v for k, v in sc["cache"].items() if k not in ("num_blocks", "block_size")}),
+            scheduler_config=SchedulerConfig(max_num_seqs=sc["seqs"], prefill_chunk_size=sc["chunk"]),
+        )
+        cache = engine.cache_manager
+        live, trace = {}, []
+        try:
+            for step in sc["steps"]:
+                op, rid = step[0], step[1]
+                if op == "reserve":
+                    _, _, tokens, max_tokens = step
+                    request = engine.reserve_transfer(rid, tokens, SamplingParams(max_tokens=max_tokens, ignore_eos=True), receiving=True)
+                    row = dict(op=op, rid=rid, tokens=tokens, max_tokens=max_tokens, ok=request is not None)
+                    if request is not None:
+                        live[rid] = request
+                        row.update(cached_tokens=request.num_prefilled_tokens,
+                                   tables=[list(t) for t in cache.plane_block_tables(rid)])
+                    else:
+                        row.update(kept_request=engine.has_request(rid), kept_allocation=cache.has_allocation(rid))
+                elif op == "accept":
+                    ok = engine.accept_import(live[rid], torch.zeros(config.hidden_size), cached_tokens=live[rid].num_prefilled_tokens)
+                    row = dict(op=op, rid=rid, ok=bool(ok), cached_pages=[list(b) for b in cache._prefixes.values()])
+                else:
+                    engine.release_transfer(live.pop(rid))
+                    row = dict(op=op, rid=rid)
+                row["free"] = cache.num_free_blocks
+                row["free_list"] = len(cache._free_blocks)
+                trace.append(row)
+        finally:
+            engine.close()
+        out.append(dict(name=name, planes=cache.storage_depths, cache=sc["cache"], prefill_chunk_size=sc["chunk"],
+                        max_num_seqs=sc["seqs"], trace=trace))
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", default=os.environ.get("VLLM_RLT_REFERENCE", str(HERE.parents[2] / "reference")),
@@ -419,6 +501,7 @@ def main():
     (out / "handoff.json").write_text(json.dumps(handoff_cases(out), indent=0))
     (out / "finalize.json").write_text(json.dumps(finalize_cases(out), indent=0))
     (out / "allocation.json").write_text(json.dumps(allocation_cases(), indent=0))
+    (out / "reservation.json").write_text(json.dumps(reservation_cases(), indent=0))
     print("golden fixtures written to", out)
 
 

@@ -51,13 +51,13 @@ def test_struct_layouts_match_the_compiler(tmp_path):
     src.write_text(
         '#include <stdio.h>\n#include <stddef.h>\n#include "rlt_kv_handoff.h"\n'
         "int main(void){printf(\"%zu %zu %zu %zu %zu %zu %zu\\n\", sizeof(RltRegion), sizeof(RltPool), sizeof(RltBatch),"
-        " sizeof(RltOptions), offsetof(RltPool, num_blocks), offsetof(RltBatch, exit_offsets), offsetof(RltOptions, status));return 0;}\n"
+        " sizeof(RltOptions), offsetof(RltPool, num_blocks), offsetof(RltBatch, exit_count), offsetof(RltOptions, status));return 0;}\n"
     )
     exe = tmp_path / "s"
     subprocess.run(["gcc", f"-I{HEADER.parent}", str(src), "-o", str(exe)], check=True)
     got = list(map(int, subprocess.run([str(exe)], capture_output=True, text=True, check=True).stdout.split()))
     want = [C.sizeof(_lib.RltRegion), C.sizeof(_lib.RltPool), C.sizeof(_lib.RltBatch), C.sizeof(_lib.RltOptions),
-            _lib.RltPool.num_blocks.offset, _lib.RltBatch.exit_offsets.offset, _lib.RltOptions.status.offset]
+            _lib.RltPool.num_blocks.offset, _lib.RltBatch.exit_count.offset, _lib.RltOptions.status.offset]
     assert got == want
 
 
@@ -81,6 +81,9 @@ def test_argument_errors_are_found_on_the_host_before_any_launch(lib):
     assert lib.rlt_kv_handoff(C.byref(pool), C.byref(pool), C.byref(batch), C.byref(opts), None) == _lib.RLT_E_INVALID
     opts.mode = _lib.MODE_DEDUP  # needs exit planes
     assert lib.rlt_kv_handoff(C.byref(pool), C.byref(pool), C.byref(batch), C.byref(opts), None) == _lib.RLT_E_INVALID
+    batch.exit_planes, batch.exit_offsets, batch.exit_count = 0x8000, 0x9000, 0  # an exit array of unknown length
+    assert lib.rlt_kv_handoff(C.byref(pool), C.byref(pool), C.byref(batch), C.byref(opts), None) == _lib.RLT_E_INVALID
+    batch.exit_planes = batch.exit_offsets = None
     opts.mode = _lib.MODE_ALL_PLANES
     opts.layer_begin, opts.layer_end = 1, 1
     assert lib.rlt_kv_handoff(C.byref(pool), C.byref(pool), C.byref(batch), C.byref(opts), None) == _lib.RLT_E_INVALID
@@ -145,33 +148,25 @@ def test_torch_ops_are_registered_in_the_reference_namespace():
         torch.ops.vllm_rlt.kv_handoff(k, k, None, None, k.clone(), k.clone(), None, None, t, t, r, r, None, None, 0, 0, 0, None)
 
 
-def test_extension_loader_reports_and_caches_like_the_reference(monkeypatch):
-    import importlib
+def test_op_loader_registers_the_ops_once_and_fails_loudly_when_unbuilt(monkeypatch, tmp_path):
+    import torch
 
-    from vllm_rlt_b200.kernels import _extension
+    from vllm_rlt_b200 import _build, _lib
 
-    _extension.try_load_extension.cache_clear()
-    assert _extension.try_load_extension() is True
-    _extension.load_extension()
-    calls = []
-
-    def missing(name):
-        calls.append(name)
-        raise ModuleNotFoundError("nope", name="vllm_rlt_b200._C")
-
-    _extension.try_load_extension.cache_clear()
-    monkeypatch.setattr(_extension, "import_module", missing)
-    assert _extension.try_load_extension() is False and _extension.try_load_extension() is False
-    assert calls == ["vllm_rlt_b200._C"]  # the negative answer is cached
-    with pytest.raises(RuntimeError, match="not built"):
-        _extension.load_extension()
-
-    def broken(name):
-        raise ModuleNotFoundError("torch gone", name="torch")
-
-    _extension.try_load_extension.cache_clear()
-    monkeypatch.setattr(_extension, "import_module", broken)
-    with pytest.raises(ModuleNotFoundError):
-        _extension.try_load_extension()
-    _extension.try_load_extension.cache_clear()
-    importlib.reload(_extension)
+    _build.build_all()
+    _lib.load_ops.cache_clear()
+    ops = _lib.load_ops()
+    assert ops is torch.ops.vllm_rlt and hasattr(ops, "kv_handoff")
+    assert _lib.load_ops() is ops  # remembered
+    # never built: a clear error, and the failure is not remembered
+    _lib.load_ops.cache_clear()
+    monkeypatch.setattr(_lib, "OPS_PATH", tmp_path / "_C.so")
+    assert not _lib.ops_built()
+    for _ in range(2):
+        with pytest.raises(RuntimeError, match="not built"):
+            _lib.load_ops()
+    # present but not loadable: the loader's own error comes through
+    (tmp_path / "_C.so").write_bytes(b"not a shared object")
+    with pytest.raises(OSError):
+        _lib.load_ops()
+    _lib.load_ops.cache_clear()

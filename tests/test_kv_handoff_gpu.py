@@ -636,3 +636,67 @@ def test_dedup_scatter_reports_a_negative_exit_plane_and_skips_the_token(variant
     # the bad token's own rows kept the sentinel on every plane
     for plane, table in enumerate(D.plane_block_tables(rid)):
         assert (gd.key_cache.view(torch.uint8)[table[s // page], :, s % page] == 0xA5).all()
+
+
+@pytest.mark.parametrize("variant", [0, 3])
+def test_dedup_pack_reports_a_negative_exit_plane_and_leaves_the_token_off_the_wire(variant):
+    """The pack side of the case above: the token has no row on any plane, so nothing that builds rows sees it; the
+    pack must still report it, and the image must hold exactly the other tokens' rows."""
+    k = kh()
+    kind, shape = SHAPES["ouro_bf16_small"]
+    page, planes = shape[4], shape[5]
+    P, D, reqs, exits = dedup_case(kind, shape, 8, [2 * page + 3])
+    (rid, s, e), = reqs
+    gp = GpuPool(P)
+    bad = [list(exits[0])]
+    bad[0][s] = -1
+    batch = k.HandoffBatch([P.plane_block_tables(rid)], None, [(s, e)], block_size=page, exit_planes=bad)
+    want = ho.pack_rows(P, P.plane_block_tables(rid), s, e, mode=ho.MODE_DEDUP, exit_planes=bad[0])
+    full = k.packed_bytes(gp.view(), e - s, planes)
+    packed = torch.full((full,), 0x5A, dtype=torch.uint8, device="cuda")
+    status = k.new_status()
+    k.kv_pack(gp.view(), batch, packed, mode=k.MODE_DEDUP, status=status, workspace=k.dedup_workspace(batch, planes),
+              variant=variant)
+    with pytest.raises(ValueError, match="exit plane"):
+        k.raise_for_status(status)
+    assert status.tolist() == [3, 0, s, -1]
+    got = packed.cpu().numpy()
+    assert np.array_equal(got[: want.size], want) and (got[want.size :] == 0x5A).all()
+
+
+@pytest.mark.parametrize("mode_name", ["exit_only", "dedup", "dedup_pack"])
+def test_an_exit_array_shorter_than_the_ranges_is_reported_and_never_read_past(mode_name):
+    """RltBatch.exit_count bounds every read of exit_planes: a request whose offset + range end runs past the
+    array is reported as a bad range and skipped as a whole; the requests before it arrive untouched by that."""
+    k = kh()
+    kind, shape = SHAPES["ouro_bf16_small"]
+    page, planes = shape[4], shape[5]
+    P, D, reqs, exits = dedup_case(kind, shape, 13, [page + 2, 2 * page + 1])
+    reqs = [(r, 0, e) for r, _, e in reqs]
+    if mode_name == "exit_only":
+        D = sentinel_destination(kind, shape, planes=1)
+        for (r, _, _), n in zip(reqs, [page + 2, 2 * page + 1]):
+            assert D.allocate(r, n)
+    gp, gd = GpuPool(P), GpuPool(D)
+    batch = k.HandoffBatch([P.plane_block_tables(r) for r, *_ in reqs], [D.plane_block_tables(r) for r, *_ in reqs],
+                           [(s, e) for _, s, e in reqs], block_size=page, exit_planes=exits)
+    assert batch.exit_count == len(exits[0]) + len(exits[1])
+    batch.exit_count = len(exits[0]) + reqs[1][2] - 1  # one entry short of the second request's range end
+    status = k.new_status()
+    if mode_name == "dedup_pack":
+        full = k.packed_bytes(gp.view(), batch.total_tokens, planes)
+        packed = torch.full((full,), 0x5A, dtype=torch.uint8, device="cuda")
+        k.kv_pack(gp.view(), batch, packed, mode=k.MODE_DEDUP, status=status, workspace=k.dedup_workspace(batch, planes))
+        want = ho.pack_rows(P, P.plane_block_tables(reqs[0][0]), 0, reqs[0][2], mode=ho.MODE_DEDUP, exit_planes=exits[0])
+        got = packed.cpu().numpy()
+        assert np.array_equal(got[: want.size], want) and (got[want.size :] == 0x5A).all()
+    else:
+        mode = k.MODE_EXIT_ONLY if mode_name == "exit_only" else k.MODE_DEDUP
+        k.kv_handoff(gp.view(), gd.view(), batch, mode=mode, status=status)
+        r, s, e = reqs[0]
+        ho.handoff_rows(P, D, P.plane_block_tables(r), D.plane_block_tables(r), s, e,
+                        mode=ho.MODE_EXIT_ONLY if mode_name == "exit_only" else ho.MODE_DEDUP, exit_planes=exits[0])
+        assert_pools_equal(gd, D)
+    with pytest.raises(ValueError, match="KV range exceeds allocation"):
+        k.raise_for_status(status)
+    assert status.tolist()[:2] == [1, 1]

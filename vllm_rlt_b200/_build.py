@@ -7,6 +7,7 @@ with a source snapshot. Nothing is cached outside the tree.
 
 from __future__ import annotations
 
+import hashlib
 import os
 import shutil
 import subprocess
@@ -36,17 +37,41 @@ def _nvcc() -> str:
     return found
 
 
-def _stale(target: Path, sources: list[Path]) -> bool:
-    if not target.is_file():
+def _fingerprint(command: list[str], inputs: list[Path]) -> str:
+    """Hash of everything a build step depends on: the command line and the bytes of every input file."""
+    h = hashlib.sha256()
+    h.update("\0".join(command).encode())
+    for path in inputs:
+        h.update(b"\0" + path.name.encode() + b"\0")
+        h.update(path.read_bytes())
+    return h.hexdigest()
+
+
+def _stamp(target: Path) -> Path:
+    return target.with_name(target.name + ".stamp")
+
+
+def _stale(target: Path, fingerprint: str) -> bool:
+    """A binary is reused only if the stamp written beside it by the build that made it carries the same
+    fingerprint and the binary's own hash: a binary compiled from other sources, with other flags, or
+    replaced since, is rebuilt whatever its modification time says."""
+    stamp = _stamp(target)
+    if not target.is_file() or not stamp.is_file():
         return True
-    newest = max(s.stat().st_mtime for s in sources)
-    return target.stat().st_mtime < newest
+    recorded = stamp.read_text().split()
+    return recorded != [fingerprint, hashlib.sha256(target.read_bytes()).hexdigest()]
 
 
-def _run(cmd: list[str]) -> None:
+def _record(target: Path, fingerprint: str) -> None:
+    _stamp(target).write_text(f"{fingerprint} {hashlib.sha256(target.read_bytes()).hexdigest()}\n")
+
+
+def _run(cmd: list[str], show: bool = False) -> None:
     proc = subprocess.run(cmd, capture_output=True, text=True)
     if proc.returncode != 0:
         raise RuntimeError(f"build step failed:\n{' '.join(cmd)}\n{proc.stdout}\n{proc.stderr}")
+    if show:
+        print(proc.stdout + proc.stderr)
 
 
 def build_library(force: bool = False, verbose: bool = False) -> Path:
@@ -54,12 +79,14 @@ def build_library(force: bool = False, verbose: bool = False) -> Path:
     target = PACKAGE / LIB_NAME
     sources = [CSRC / s for s in CUDA_SOURCES]
     deps = sources + [CSRC / "common.cuh", INCLUDE / "rlt_kv_handoff.h"]
-    if force or _stale(target, deps):
-        cmd = [_nvcc(), *ARCH, "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC,-fvisibility=hidden",
-               f"-I{INCLUDE}", "-shared", "-o", str(target), *map(str, sources), "-ldl"]
+    flags = [*ARCH, "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC,-fvisibility=hidden"]
+    fingerprint = _fingerprint(flags, deps)
+    if force or verbose or _stale(target, fingerprint):
+        cmd = [_nvcc(), *flags, f"-I{INCLUDE}", "-shared", "-o", str(target), *map(str, sources), "-ldl"]
         if verbose:
             cmd.insert(1, "-Xptxas=-v")
-        _run(cmd)
+        _run(cmd, show=verbose)
+        _record(target, fingerprint)
     return target
 
 
@@ -71,18 +98,21 @@ def build_ops(force: bool = False) -> Path:
     target = PACKAGE / OPS_NAME
     source = CSRC / "torch_bindings.cpp"
     deps = [source, CSRC / "ops.h", INCLUDE / "rlt_kv_handoff.h", PACKAGE / LIB_NAME]
-    if force or _stale(target, deps):
+    abi = int(torch._C._GLIBCXX_USE_CXX11_ABI)
+    flags = ["-O2", "-std=c++17", "-fPIC", "-shared", f"-D_GLIBCXX_USE_CXX11_ABI={abi}", "-DTORCH_EXTENSION_NAME=_C",
+             f"torch={torch.__version__}"]
+    fingerprint = _fingerprint(flags, deps)
+    if force or _stale(target, fingerprint):
         includes = [f"-I{p}" for p in cpp_extension.include_paths("cuda")] + [f"-I{INCLUDE}", f"-I{CSRC}"]
         import sysconfig
 
         includes.append(f"-I{sysconfig.get_paths()['include']}")
         torch_lib = Path(torch.__file__).parent / "lib"
-        abi = int(torch._C._GLIBCXX_USE_CXX11_ABI)
-        cmd = ["g++", "-O2", "-std=c++17", "-fPIC", "-shared", f"-D_GLIBCXX_USE_CXX11_ABI={abi}",
-               "-DTORCH_EXTENSION_NAME=_C", *includes, str(source), "-o", str(target),
+        cmd = ["g++", *flags[:-1], *includes, str(source), "-o", str(target),
                f"-L{PACKAGE}", "-l:" + LIB_NAME, f"-L{torch_lib}", "-ltorch", "-ltorch_cpu", "-lc10",
                "-ltorch_cuda", "-lc10_cuda", "-Wl,-rpath,$ORIGIN", f"-Wl,-rpath,{torch_lib}"]
         _run(cmd)
+        _record(target, fingerprint)
     return target
 
 

@@ -55,6 +55,7 @@ class RltBatch(C.Structure):
         ("tok_end", C.c_void_p),
         ("exit_planes", C.c_void_p),
         ("exit_offsets", C.c_void_p),
+        ("exit_count", C.c_int64),
     ]
 
 
@@ -120,6 +121,34 @@ def load() -> C.CDLL:
         fn.restype = restype
         fn.argtypes = argtypes
     return lib
+
+
+OPS_PATH = PACKAGE / "_C.so"
+
+
+def ops_built() -> bool:
+    """Whether the torch op library sits in the tree. Looks at the file only: nothing is loaded, no CUDA context."""
+    return OPS_PATH.is_file()
+
+
+@cache
+def load_ops():
+    """Register ``torch.ops.vllm_rlt.kv_*`` by loading the in-tree op library; returns the op namespace.
+
+    The reference finds its op library by importing ``vllm_rlt._C`` and treats a missing module as "optional
+    kernels absent" (vllm_rlt/kernels/_extension.py:8-23). These ops are not optional: a library that was never
+    built raises here, and a library that exists but cannot be loaded (wrong torch, missing symbol) lets the
+    loader's own error through. A successful load is remembered; a failure is not, so a later build is picked up.
+    """
+    if not ops_built():
+        raise RuntimeError(
+            f"{OPS_PATH.name} is not built: run `python -m vllm_rlt_b200._build`. "
+            "The KV-handoff ops have CUDA implementations only."
+        )
+    import torch
+
+    torch.ops.load_library(str(OPS_PATH))
+    return torch.ops.vllm_rlt
 
 
 class RltError(RuntimeError):

@@ -7,8 +7,8 @@
 // Triton kernel over (row, target plane, channel tile) plus a second launch for the scales
 // (finalize_kernel, vllm_rlt/kernels/routing.py:147-179; ModelRunner.finalize_many,
 // vllm_rlt/worker/model_runner.py:1349-1395). Here one launch covers K, V and both scale
-// tensors: a work unit is (row, tensor); it loads the token's row of every selected layer once
-// with 16-byte streaming loads and stores it to every deeper plane.
+// tensors: each row's K, V and scale rows of every selected layer are loaded once with 16-byte
+// streaming loads and stored to every deeper plane, and the rows are dealt to the CTAs by cost.
 //
 // HBM roofline: each selected (layer, tensor) row is read once and written once per deeper
 // plane. Pools with more than kFanPlanes planes use the older kernel, whose unit is
@@ -70,13 +70,39 @@ __device__ __forceinline__ void copy_layers(const char* src, char* dst, const in
 
 constexpr int kFanPlanes = 64;
 
-// One load, several stores: vector i of the flat (selected layers x row vectors) array goes to the same
-// in-block offset of every target plane whose block is valid (plane_base >= 0).
+// ---------------------------------------------------------------------------------------------
+// finalize_fan_kernel: one load, one store per deeper plane, work split by cost.
+//
+// A row that exits at plane e costs (1 + deeper planes) row copies: nothing for the deepest plane, four for plane 0
+// of a four-plane pool. Handing rows to CTAs round-robin leaves the CTAs with sums of a few dozen such costs, which
+// differ by +-10 %; the early finishers idle while HBM runs below its rate. So every CTA first derives the same
+// exclusive scan of the row costs (each thread sums a contiguous slice of rows; one block scan of the 256 sums),
+// cuts the total into gridDim.x equal shares and takes the contiguous run of rows - down to a fraction of the first
+// and last row, in whole (tensor, layer) pieces - that makes up its share. No atomics, no scratch memory, and two
+// neighbouring CTAs compute their common boundary from the same numbers.
+//
+// Inside its run a CTA walks rows in order, so the next row's block-table entries are fetched before the current
+// row is streamed and the only barrier per row finds them already there.
+
+// (1 + deeper planes) if the row is valid and has deeper planes, else 0. `say`: report an invalid row (one CTA does).
+__device__ __forceinline__ int row_cost(const FinalizeParams& p, int row, bool say) {
+  const int request = p.rows[3 * row], exit_plane = p.rows[3 * row + 1], position = p.rows[3 * row + 2];
+  if (request < 0 || request >= p.num_requests || exit_plane < 0 || exit_plane >= p.planes || position < 0 ||
+      position >= p.table_width * p.block_size) {
+    if (say) report(p.status, RLT_STATUS_BAD_PLANE, row, position, exit_plane);
+    return 0;
+  }
+  return exit_plane + 1 < p.planes ? p.planes - exit_plane : 0;
+}
+
+// Pieces [a, b) of one region of one row: piece = (K|V, selected layer). Vector i of the flat array belongs to piece
+// a + i / row_vecs. The vector is loaded once and stored to the same in-block offset of every deeper plane whose
+// block is valid (plane_off >= 0).
 template <typename T>
-__device__ __forceinline__ void copy_layers_fan(const char* src, char* pool, const long long* plane_base, int first,
-                                                int planes, const int* layer_of, int layers, int row_vecs,
-                                                unsigned row_magic, long long layer_bytes) {
-  const int total = layers * row_vecs;
+__device__ __forceinline__ void fan_pieces(const FinalizeRegion& rg, const long long* plane_off, int exit_plane, int planes,
+                                           const int* layer_of, int layers, int a, int b) {
+  const int total = (b - a) * rg.row_vecs;
+  const long long src_off = plane_off[exit_plane];
   for (int base = threadIdx.x; base < total; base += kThreads * kUnroll) {
     T regs[kUnroll];
     long long at[kUnroll];
@@ -85,80 +111,162 @@ __device__ __forceinline__ void copy_layers_fan(const char* src, char* pool, con
       const int i = base + u * kThreads;
       at[u] = -1;
       if (i < total) {
-        const int slot = row_magic ? static_cast<int>(__umulhi(static_cast<unsigned>(i), row_magic)) : i;
-        at[u] = layer_of[slot] * layer_bytes + static_cast<long long>(i - slot * row_vecs) * static_cast<long long>(sizeof(T));
-        regs[u] = ld_stream(reinterpret_cast<const T*>(src + at[u]));
+        const int q = rg.row_magic ? static_cast<int>(__umulhi(static_cast<unsigned>(i), rg.row_magic)) : i;
+        const int piece = a + q;
+        const int kv = piece >= layers;
+        const int slot = piece - kv * layers;
+        // bit 62 carries K|V so that the store loop needs no second table
+        at[u] = layer_of[slot] * rg.layer_bytes + static_cast<long long>(i - q * rg.row_vecs) * static_cast<long long>(sizeof(T));
+        const char* pool = kv ? rg.value : rg.key;
+        regs[u] = ld_stream(reinterpret_cast<const T*>(pool + src_off + at[u]));
+        at[u] |= static_cast<long long>(kv) << 62;
       }
     }
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
       if (at[u] >= 0) {
-        for (int t = first; t < planes; ++t) {
-          const long long pb = plane_base[t];
-          if (pb >= 0) st_stream(reinterpret_cast<T*>(pool + pb + at[u]), regs[u]);
+        char* pool = (at[u] >> 62) ? rg.value : rg.key;
+        const long long in_row = at[u] & ((1ll << 62) - 1);
+        for (int t = exit_plane + 1; t < planes; ++t) {
+          const long long pb = plane_off[t];
+          if (pb >= 0) st_stream(reinterpret_cast<T*>(pool + pb + in_row), regs[u]);
         }
       }
     }
   }
 }
 
-__global__ void __launch_bounds__(kThreads, 4) finalize_fan_kernel(const FinalizeParams p) {
+__global__ void __launch_bounds__(kThreads, 3) finalize_fan_kernel(const FinalizeParams p) {
   __shared__ int layer_of[64];  // the selected layers, in order
   __shared__ int n_selected;
-  __shared__ long long plane_base[2][kFanPlanes];  // per unit: byte offset of the token's row in each target plane
-  if (threadIdx.x == 0) {
+  __shared__ long long slice_start[kThreads + 1];  // cost of all rows before each thread's slice; [kThreads] = total
+  __shared__ long long warp_part[kThreads / 32];
+  __shared__ int cut_row[2];        // first row of this CTA's share, and the row its share ends in
+  __shared__ long long cut_rem[2];  // cost of that row that lies before the cut
+  // per row, double buffered: byte offset of the token's row in each plane, for either region; -1 = invalid block
+  __shared__ long long plane_off[2][2][kFanPlanes];
+  const int tid = static_cast<int>(threadIdx.x);
+  if (tid == 0) {
     int n = 0;
     for (int layer = 0; layer < p.num_layers; ++layer) {
       if ((p.layer_mask >> layer) & 1ull) layer_of[n++] = layer;
     }
     n_selected = n;
   }
-  __syncthreads();
-  const int layers = n_selected;
-  const int tensors = 2 * p.num_regions;
-  const long long units = static_cast<long long>(p.n) * tensors;
-  int parity = 0;  // flipped only by units that reach the barrier, so two such units in a row never share a table
-  for (long long w = blockIdx.x; w < units; w += gridDim.x) {
-    const int tensor = static_cast<int>(w % tensors);
-    const int row = static_cast<int>(w / tensors);
-    const int request = p.rows[3 * row], exit_plane = p.rows[3 * row + 1], position = p.rows[3 * row + 2];
-    if (request < 0 || request >= p.num_requests || exit_plane < 0 || exit_plane >= p.planes || position < 0 ||
-        position >= p.table_width * p.block_size) {
-      if (threadIdx.x == 0 && tensor == 0) report(p.status, RLT_STATUS_BAD_PLANE, row, position, exit_plane);
-      continue;
+
+  // ---- the same cost scan in every CTA ----
+  const int per = (p.n + kThreads - 1) / kThreads;
+  const int mine_lo = min(p.n, tid * per), mine_hi = min(p.n, mine_lo + per);
+  long long mine = 0;
+  for (int i = mine_lo; i < mine_hi; ++i) mine += row_cost(p, i, blockIdx.x == 0);
+  {
+    const int lane = tid & 31, warp = tid >> 5;
+    long long inc = mine;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const long long up = __shfl_up_sync(0xffffffffu, inc, d);
+      if (lane >= d) inc += up;
     }
-    if (exit_plane + 1 >= p.planes) continue;  // the deepest plane was computed: nothing to fill
-    const int page = position / p.block_size, offset = position - page * p.block_size;
-    const long long base = (static_cast<long long>(request) * p.planes) * p.table_width + page;
-    const int sb = p.tables[base + static_cast<long long>(exit_plane) * p.table_width];
-    if (sb < 0 || sb >= p.num_blocks) {
-      if (threadIdx.x == 0) report(p.status, RLT_STATUS_BAD_BLOCK, request, page, sb);
-      continue;
-    }
-    const FinalizeRegion& rg = p.region[tensor >> 1];
-    long long* pb = plane_base[parity];
-    const int t = static_cast<int>(threadIdx.x);
-    if (t > exit_plane && t < p.planes) {
-      const int db = p.tables[base + static_cast<long long>(t) * p.table_width];
-      long long at = -1;
-      if (db < 0 || db >= p.num_blocks) {
-        report(p.status, RLT_STATUS_BAD_BLOCK, request, page, db);
-      } else {
-        at = db * rg.block_bytes + offset * rg.token_bytes;
-      }
-      pb[t] = at;
-    }
+    if (lane == 31) warp_part[warp] = inc;
     __syncthreads();
-    parity ^= 1;
-    char* pool = (tensor & 1) ? rg.value : rg.key;
-    const char* src = pool + sb * rg.block_bytes + offset * rg.token_bytes;
-    if (rg.vec_bytes == 16) {
-      copy_layers_fan<uint4>(src, pool, pb, exit_plane + 1, p.planes, layer_of, layers, rg.row_vecs, rg.row_magic, rg.layer_bytes);
-    } else if (rg.vec_bytes == 4) {
-      copy_layers_fan<uint32_t>(src, pool, pb, exit_plane + 1, p.planes, layer_of, layers, rg.row_vecs, rg.row_magic, rg.layer_bytes);
-    } else {
-      copy_layers_fan<uint8_t>(src, pool, pb, exit_plane + 1, p.planes, layer_of, layers, rg.row_vecs, rg.row_magic, rg.layer_bytes);
+    long long before = 0;
+    for (int w = 0; w < warp; ++w) before += warp_part[w];
+    slice_start[tid] = before + inc - mine;
+    if (tid == kThreads - 1) slice_start[kThreads] = before + inc;
+  }
+  __syncthreads();
+  const long long total = slice_start[kThreads];
+  if (total == 0) return;
+  // Where this CTA's share begins and ends, in units of one (tensor, layer) piece of one row copy, then as
+  // (cost position, piece remainder). total * pieces * gridDim.x stays far below 2^63.
+  const int layers = n_selected;
+  const int pieces_per_region = 2 * layers;
+  const int pieces = pieces_per_region * p.num_regions;
+  const long long fine_total = total * pieces;
+  const long long fine[2] = {fine_total * blockIdx.x / gridDim.x, fine_total * (blockIdx.x + 1) / gridDim.x};
+  if (fine[0] == fine[1]) return;  // an empty share (fewer pieces than CTAs)
+#pragma unroll
+  for (int k = 0; k < 2; ++k) {
+    const long long c = fine[k] / pieces;
+    if (c >= total) {
+      if (tid == 0) {
+        cut_row[k] = p.n;
+        cut_rem[k] = 0;
+      }
+    } else if (slice_start[tid] <= c && c < slice_start[tid + 1]) {  // exactly one thread: the cut is in its slice
+      long long acc = slice_start[tid];
+      for (int i = mine_lo; i < mine_hi; ++i) {
+        const int cost = row_cost(p, i, false);
+        if (acc + cost > c) {
+          cut_row[k] = i;
+          cut_rem[k] = (c - acc) * pieces + fine[k] % pieces;  // pieces of this row's cost * pieces before the cut
+          break;
+        }
+        acc += cost;
+      }
     }
+  }
+  __syncthreads();
+  const int row_first = cut_row[0], row_last = min(cut_row[1], p.n - 1);
+
+  // Block-table entry of this thread's plane for `row` (threads exit plane .. planes - 1 take part): the load is
+  // issued here and its value is first used after the current row has been streamed.
+  auto lookup = [&](int row, int* page_offset) -> int {
+    *page_offset = -1;
+    if (row > row_last || tid >= p.planes) return 0;
+    const int request = p.rows[3 * row], exit_plane = p.rows[3 * row + 1], position = p.rows[3 * row + 2];
+    if (request < 0 || request >= p.num_requests || exit_plane < 0 || exit_plane + 1 >= p.planes || position < 0 ||
+        position >= p.table_width * p.block_size || tid < exit_plane)
+      return 0;
+    const int page = position / p.block_size;
+    *page_offset = position - page * p.block_size;
+    return p.tables[(static_cast<long long>(request) * p.planes + tid) * p.table_width + page];
+  };
+  auto publish = [&](int row, int block, int page_offset, long long (*out)[kFanPlanes]) {
+    if (page_offset < 0) return;
+    if (block < 0 || block >= p.num_blocks) {
+      report(p.status, RLT_STATUS_BAD_BLOCK, p.rows[3 * row], p.rows[3 * row + 2] / p.block_size, block);
+      out[0][tid] = out[1][tid] = -1;
+      return;
+    }
+    out[0][tid] = block * p.region[0].block_bytes + page_offset * p.region[0].token_bytes;
+    if (p.num_regions == 2) out[1][tid] = block * p.region[1].block_bytes + page_offset * p.region[1].token_bytes;
+  };
+
+  int parity = 0;
+  {
+    int page_offset;
+    const int block = lookup(row_first, &page_offset);
+    publish(row_first, block, page_offset, plane_off[0]);
+  }
+  __syncthreads();
+  for (int row = row_first; row <= row_last; ++row, parity ^= 1) {
+    int next_offset;
+    const int next_block = lookup(row + 1, &next_offset);  // in flight while this row streams
+    const int cost = row_cost(p, row, false);
+    if (cost > 0) {
+      // whole (tensor, layer) pieces of this row that fall inside the share
+      const int lo = row == row_first ? static_cast<int>(cut_rem[0] / cost) : 0;
+      const int hi = row == cut_row[1] ? static_cast<int>(cut_rem[1] / cost) : pieces;
+      const int exit_plane = p.planes - cost;
+      if (plane_off[parity][0][exit_plane] >= 0) {  // the source block is valid
+        for (int g = 0; g < p.num_regions; ++g) {
+          const int a = max(lo - g * pieces_per_region, 0), b = min(hi - g * pieces_per_region, pieces_per_region);
+          if (a >= b) continue;
+          const FinalizeRegion& rg = p.region[g];
+          const long long* off = plane_off[parity][g];
+          if (rg.vec_bytes == 16) {
+            fan_pieces<uint4>(rg, off, exit_plane, p.planes, layer_of, layers, a, b);
+          } else if (rg.vec_bytes == 4) {
+            fan_pieces<uint32_t>(rg, off, exit_plane, p.planes, layer_of, layers, a, b);
+          } else {
+            fan_pieces<uint8_t>(rg, off, exit_plane, p.planes, layer_of, layers, a, b);
+          }
+        }
+      }
+    }
+    publish(row + 1, next_block, next_offset, plane_off[parity ^ 1]);
+    __syncthreads();  // the next row's offsets are visible; this row's buffer is free for the row after
   }
 }
 
@@ -268,7 +376,9 @@ int rlt_kv_finalize(const RltPool* pool, const int32_t* tables, int32_t num_requ
   const long long units = static_cast<long long>(count) * (fan ? 1 : p.planes - 1) * 2 * p.num_regions;
   const int grid = static_cast<int>(units < sms * 4ll ? units : sms * 4ll);
   if (fan) {
-    rlt::finalize_fan_kernel<<<grid, rlt::kThreads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(p);
+    // one persistent wave of three CTAs per SM; a CTA's share may be a fraction of a row, so small batches
+    // still use every SM (a share of less than one (tensor, layer) piece is simply empty)
+    rlt::finalize_fan_kernel<<<sms * 3, rlt::kThreads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(p);
   } else {
     rlt::finalize_kernel<<<grid, rlt::kThreads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(p);
   }

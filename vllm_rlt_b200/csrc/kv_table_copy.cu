@@ -77,6 +77,7 @@ struct TableCopyParams {
   const int* tok_end;
   const int* exit_planes;
   const long long* exit_offsets;
+  long long exit_count;  // entries in exit_planes
   int plane_bias;   // 0: source plane = min(p, exit); src_planes: source plane = exit
   int layer_begin;
   int layer_end;
@@ -146,7 +147,12 @@ __device__ void scan_requests(const TableCopyParams& p, int* blk_off, int* tok_o
     if (r < p.num_requests) {
       const int b = p.tok_begin[r], e = p.tok_end[r];
       if (e > b) {
-        const bool ok = b >= 0 && e <= p.table_width * p.block_size;
+        bool ok = b >= 0 && e <= p.table_width * p.block_size;
+        if (ok && p.exit_planes != nullptr) {
+          // every later read of exit_planes for this request lies in [offset, offset + e)
+          const long long at = p.exit_offsets[r];
+          ok = at >= 0 && at + e <= p.exit_count;
+        }
         if (ok) {
           nb = (e - 1) / p.block_size - b / p.block_size + 1;
         } else {
@@ -381,6 +387,14 @@ __global__ void __launch_bounds__(kThreads, 4) table_copy_kernel(const TableCopy
     long long* rs = row_src[parity];
     long long* rd = row_dst[parity];
     if (threadIdx.x < u.rows) row_offsets<kDedup>(p, u, tok_off, threadIdx.x, &rs[threadIdx.x], &rd[threadIdx.x]);
+    // A token with a negative exit plane has no row in a dedup wire image, so no row above sees it: one unit per
+    // block looks (the scatter of such an image does the same in table_fan_kernel).
+    if (kDedup && p.dst_packed && u.plane == p.plane_begin && u.g == 0 && u.kv == 0 && u.layer0 == p.layer_begin &&
+        static_cast<int>(threadIdx.x) < u.n_tok) {
+      const int t_abs = u.tok_lo + static_cast<int>(threadIdx.x);
+      const int e = p.exit_planes[p.exit_offsets[u.r] + t_abs];
+      if (e < 0) report(p.status, RLT_STATUS_BAD_PLANE, u.r, t_abs, e);
+    }
     __syncthreads();  // one barrier per unit: the offset tables are double buffered
 
     const char* src = unit_src(p, u);
@@ -724,6 +738,12 @@ __global__ void __launch_bounds__(kBulkThreads, 1) table_bulk_kernel(const Table
     char* dst = unit_dst(p, u);
     const bool bulk = rg.vec_bytes == 16 && rg.token_bytes >= kBulkMinRow;
     const int row_bytes = static_cast<int>(rg.token_bytes);
+    if (kDedup && p.dst_packed && u.plane == p.plane_begin && u.g == 0 && u.kv == 0 && u.layer0 == p.layer_begin) {
+      for (int i = lane; i < u.n_tok; i += 32) {  // tokens without a row on the wire: see table_copy_kernel
+        const int e = p.exit_planes[p.exit_offsets[u.r] + u.tok_lo + i];
+        if (e < 0) report(p.status, RLT_STATUS_BAD_PLANE, u.r, u.tok_lo + i, e);
+      }
+    }
     long long run_s = 0, run_d = 0;
     int run_n = 0;
     for (int base = 0; base < u.rows; base += 32) {
@@ -942,6 +962,7 @@ int launch_table_copy(Direction dir, const RltPool* src, const RltPool* dst, con
     return RLT_E_INVALID;
   const bool dedup_wire = dir != kDirect && opt->mode == RLT_MODE_DEDUP;
   if (dedup_wire && (batch->exit_planes == nullptr || batch->exit_offsets == nullptr)) return RLT_E_INVALID;
+  if (batch->exit_planes != nullptr && batch->exit_count < 1) return RLT_E_INVALID;
 
   const int layer_begin = opt->layer_begin;
   const int layer_end = opt->layer_end == 0 ? any->num_layers : opt->layer_end;
@@ -974,6 +995,7 @@ int launch_table_copy(Direction dir, const RltPool* src, const RltPool* dst, con
   p.tok_end = batch->tok_end;
   p.exit_planes = opt->mode == RLT_MODE_ALL_PLANES ? nullptr : batch->exit_planes;
   p.exit_offsets = reinterpret_cast<const long long*>(batch->exit_offsets);
+  p.exit_count = batch->exit_count;
   p.layer_begin = layer_begin;
   p.layer_end = layer_end;
   p.status = opt->status;

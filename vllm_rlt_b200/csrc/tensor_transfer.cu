@@ -90,11 +90,81 @@ __global__ void __launch_bounds__(kTile) segmented_transfer_kernel(const long lo
   }
 }
 
+// Flat copy with conversion. When every pointer is 16-byte aligned a thread handles N consecutive elements per
+// step, N = 16 / (size of the widest of the three types): the widest side moves as one 16-byte access per thread
+// and the narrower sides as 8-, 4- or 2-byte accesses, all of them contiguous across the warp, with kFlatUnroll
+// steps in flight per thread. The last n % N elements, and unaligned tensors, go one element at a time.
+constexpr int kFlatUnroll = 4;
+
+template <int kBytes>
+struct Bits;
+template <>
+struct Bits<16> { using type = uint4; };
+template <>
+struct Bits<8> { using type = uint2; };
+template <>
+struct Bits<4> { using type = uint32_t; };
+template <>
+struct Bits<2> { using type = uint16_t; };
+
+template <typename T, int N>
+struct alignas(sizeof(T) * N) Pack {
+  T v[N];
+};
+
+template <typename T, int N>
+__device__ __forceinline__ Pack<T, N> load_pack(const T* p) {
+  using B = typename Bits<sizeof(T) * N>::type;
+  union { B bits; Pack<T, N> pack; } u;
+  u.bits = *reinterpret_cast<const B*>(p);
+  return u.pack;
+}
+
+template <typename T, int N>
+__device__ __forceinline__ void store_pack(T* p, const Pack<T, N>& pack) {
+  using B = typename Bits<sizeof(T) * N>::type;
+  union { B bits; Pack<T, N> pack; } u;
+  u.pack = pack;
+  *reinterpret_cast<B*>(p) = u.bits;
+}
+
 template <typename S, typename D, typename E>
 __global__ void __launch_bounds__(kTile) flat_transfer_kernel(const S* __restrict__ src, D* __restrict__ dst,
-                                                              E* __restrict__ secondary, long long n) {
-  for (long long i = static_cast<long long>(blockIdx.x) * kTile + threadIdx.x; i < n;
-       i += static_cast<long long>(gridDim.x) * kTile) {
+                                                              E* __restrict__ secondary, long long n, int vector_ok) {
+  constexpr int kWidest = sizeof(S) > sizeof(D) ? (sizeof(S) > sizeof(E) ? sizeof(S) : sizeof(E))
+                                                : (sizeof(D) > sizeof(E) ? sizeof(D) : sizeof(E));
+  constexpr int N = 16 / kWidest;
+  const long long first = static_cast<long long>(blockIdx.x) * kTile + threadIdx.x;
+  const long long stride = static_cast<long long>(gridDim.x) * kTile;
+  long long done = 0;
+  if (vector_ok) {
+    const long long groups = n / N;
+    for (long long base = first; base < groups; base += stride * kFlatUnroll) {
+      Pack<S, N> in[kFlatUnroll];
+#pragma unroll
+      for (int u = 0; u < kFlatUnroll; ++u) {
+        const long long g = base + u * stride;
+        if (g < groups) in[u] = load_pack<S, N>(src + g * N);
+      }
+#pragma unroll
+      for (int u = 0; u < kFlatUnroll; ++u) {
+        const long long g = base + u * stride;
+        if (g >= groups) continue;
+        Pack<D, N> out;
+#pragma unroll
+        for (int k = 0; k < N; ++k) out.v[k] = Convert<D, S>::run(in[u].v[k]);
+        store_pack<D, N>(dst + g * N, out);
+        if (secondary != nullptr) {
+          Pack<E, N> second;
+#pragma unroll
+          for (int k = 0; k < N; ++k) second.v[k] = Convert<E, S>::run(in[u].v[k]);
+          store_pack<E, N>(secondary + g * N, second);
+        }
+      }
+    }
+    done = groups * N;
+  }
+  for (long long i = done + first; i < n; i += stride) {
     const S v = src[i];
     dst[i] = Convert<D, S>::run(v);
     if (secondary != nullptr) secondary[i] = Convert<E, S>::run(v);
@@ -114,12 +184,18 @@ int launch_flat(const void* src, void* dst, void* secondary, long long n, int se
                 cudaStream_t stream) {
   const S* s = static_cast<const S*>(src);
   D* d = static_cast<D*>(dst);
-  switch (secondary == nullptr ? RLT_DTYPE_I32 : secondary_dtype) {
-    case RLT_DTYPE_I32: flat_transfer_kernel<S, D, int><<<grid, kTile, 0, stream>>>(s, d, static_cast<int*>(secondary), n); break;
-    case RLT_DTYPE_I64: flat_transfer_kernel<S, D, long long><<<grid, kTile, 0, stream>>>(s, d, static_cast<long long*>(secondary), n); break;
-    case RLT_DTYPE_F16: flat_transfer_kernel<S, D, __half><<<grid, kTile, 0, stream>>>(s, d, static_cast<__half*>(secondary), n); break;
-    case RLT_DTYPE_BF16: flat_transfer_kernel<S, D, __nv_bfloat16><<<grid, kTile, 0, stream>>>(s, d, static_cast<__nv_bfloat16*>(secondary), n); break;
-    case RLT_DTYPE_F32: flat_transfer_kernel<S, D, float><<<grid, kTile, 0, stream>>>(s, d, static_cast<float*>(secondary), n); break;
+  const int vec = ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst) |
+                    reinterpret_cast<uintptr_t>(secondary)) & 15u) == 0;
+  if (secondary == nullptr) {  // no second output: its type must not narrow the vector width
+    flat_transfer_kernel<S, D, D><<<grid, kTile, 0, stream>>>(s, d, static_cast<D*>(nullptr), n, vec);
+    return RLT_OK;
+  }
+  switch (secondary_dtype) {
+    case RLT_DTYPE_I32: flat_transfer_kernel<S, D, int><<<grid, kTile, 0, stream>>>(s, d, static_cast<int*>(secondary), n, vec); break;
+    case RLT_DTYPE_I64: flat_transfer_kernel<S, D, long long><<<grid, kTile, 0, stream>>>(s, d, static_cast<long long*>(secondary), n, vec); break;
+    case RLT_DTYPE_F16: flat_transfer_kernel<S, D, __half><<<grid, kTile, 0, stream>>>(s, d, static_cast<__half*>(secondary), n, vec); break;
+    case RLT_DTYPE_BF16: flat_transfer_kernel<S, D, __nv_bfloat16><<<grid, kTile, 0, stream>>>(s, d, static_cast<__nv_bfloat16*>(secondary), n, vec); break;
+    case RLT_DTYPE_F32: flat_transfer_kernel<S, D, float><<<grid, kTile, 0, stream>>>(s, d, static_cast<float*>(secondary), n, vec); break;
     default: return RLT_E_INVALID;
   }
   return RLT_OK;
@@ -192,7 +268,9 @@ int rlt_tensor_copy(const void* src, void* dst, void* secondary, int64_t count, 
   int sms = 0;
   const int rc0 = rlt::sm_count(&sms);
   if (rc0 != RLT_OK) return rc0;
-  const long long blocks = (count + rlt::kTile - 1) / rlt::kTile;
+  // a thread of the vector path covers kFlatUnroll groups of at least two elements per step
+  const long long per_block = static_cast<long long>(rlt::kTile) * 2 * rlt::kFlatUnroll;
+  const long long blocks = (count + per_block - 1) / per_block;
   const int grid = static_cast<int>(blocks < sms * 8ll ? blocks : sms * 8ll);
   const rlt::FlatCall call{src, dst, secondary, count, secondary_dtype, grid, reinterpret_cast<cudaStream_t>(stream)};
   const int rc = rlt::dispatch_pair(src_dtype, dst_dtype, call);

@@ -99,6 +99,7 @@ BatchArgs batch_of(const at::Tensor* src_tables, const at::Tensor* dst_tables, c
                     exit_offsets->is_contiguous() && exit_offsets->numel() == any.size(0),
                 "exit_offsets must be a contiguous int64 tensor with one entry per request");
     out.batch.exit_offsets = exit_offsets->data_ptr<int64_t>();
+    out.batch.exit_count = exit_planes->numel();  // lets the kernels refuse offsets that would run past the array
   }
   return out;
 }

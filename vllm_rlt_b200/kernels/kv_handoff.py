@@ -292,12 +292,13 @@ class HandoffBatch:
         base = self._dev.data_ptr()
         self._ptr = {name: base + at for name, (at, _) in layout.items()}
         self.has_exit = exits is not None
+        self.exit_count = exit_count
 
     def as_struct(self) -> _lib.RltBatch:
         g = self._ptr.get
         return _lib.RltBatch(
             self.num_requests, self.table_width, g("src_tables"), g("dst_tables"),
-            g("tok_begin"), g("tok_end"), g("exit_planes"), g("exit_offsets"),
+            g("tok_begin"), g("tok_end"), g("exit_planes"), g("exit_offsets"), self.exit_count,
         )
 
 

@@ -110,7 +110,28 @@ def run_pull(args, rank: int, world: int) -> None:
     handle_msg.copy_(exchange.encode_handles(rows))
     all_handles = [torch.zeros_like(handle_msg) for _ in range(world)]
     dist.all_gather(all_handles, handle_msg)
+    # The prefill workers' block tables and per-token exit planes travel to the decode workers over NCCL, as a
+    # deployment would send them on its control channel: a decode worker pulls with the tables it RECEIVED, not
+    # with ones it could rebuild from the seed. (All workers share the prompt lengths, so the messages are equal-sized.)
+    width = -(-max(w.lengths) // s.block_size)
+    src_msg = torch.zeros((len(w.lengths), s.planes, width), dtype=torch.int32, device=device)
+    exit_msg = torch.zeros(max(1, sum(w.lengths)), dtype=torch.int32, device=device)
+    if is_prefill:
+        src_msg.copy_(exchange.encode_tables(w.src_tables, s.planes, width))
+        if w.exit_planes is not None:
+            exit_msg.copy_(torch.from_numpy(np.concatenate([np.asarray(e, np.int32) for e in w.exit_planes])))
+    all_src, all_exits = exchange.all_gather_metadata(src_msg, exit_msg)
     torch.cuda.synchronize()
+    received = {}
+    if not is_prefill:
+        for p_rank, wp in per_source.items():
+            tables = exchange.decode_tables(all_src[p_rank], wp.lengths, s.block_size)
+            exits = None
+            if wp.exit_planes is not None:
+                flat = all_exits[p_rank].cpu().numpy()
+                ends = np.cumsum(wp.lengths)
+                exits = [flat[e - n : e] for e, n in zip(ends, wp.lengths)]
+            received[p_rank] = (tables, exits)
 
     status = kh.new_status(device)
     mapping = peerlib.PeerMapping()
@@ -130,9 +151,10 @@ def run_pull(args, rank: int, world: int) -> None:
             ptrs = [mapping.pointer(e) for e in exchange.decode_handles(all_handles[p])]
             scales = dv.scales.rebased(ptrs[2], ptrs[3]) if s.fp8 else None
             sv = kh.PoolView(dv.codes.rebased(ptrs[0], ptrs[1]), scales, wp.src_blocks, s.block_size, s.num_layers, s.planes, -1)
-            sub = dict(src=[wp.src_tables[i] for i in mine], dst=[reserved[(p, i)] for i in mine],
+            got_tables, got_exits = received[p]
+            sub = dict(src=[got_tables[i] for i in mine], dst=[reserved[(p, i)] for i in mine],
                        ranges=[wp.ranges[i] for i in mine],
-                       exits=None if wp.exit_planes is None else [wp.exit_planes[i] for i in mine])
+                       exits=None if got_exits is None else [got_exits[i] for i in mine])
 
             def make_batch(sub=sub, wp=wp):
                 return kh.HandoffBatch(sub["src"], sub["dst"], sub["ranges"], block_size=s.block_size, exit_planes=sub["exits"],
@@ -203,41 +225,14 @@ def run_pull(args, rank: int, world: int) -> None:
     payload_all = torch.tensor([float(my_payload), float(my_wire)], device=device, dtype=torch.float64)
     dist.all_reduce(payload_all)
 
-    # ---- verification: the source side gathers what some transferred tokens should hold, the decode side compares
-    ok = torch.ones(1, device=device)
-    for p in range(n_prefill):
-        for d_rank in partners_of(p):
-            if rank not in (p, d_rank):
-                continue
-            wp = w if rank == p else per_source[p]
-            mine = assigned(p, d_rank, wp)
-            if not mine:
-                continue
-            i = mine[-1]
-            lo, hi = wp.ranges[i]
-            n = min(48, hi - lo)
-            expect = torch.zeros((2, n, s.num_layers, s.num_kv_heads, s.head_dim * s.element), dtype=torch.uint8, device=device)
-            pos = torch.arange(lo, lo + n, device=device)
-            for plane in range(dst_planes):
-                if rank == p:
-                    if wp.exit_planes is None:
-                        sp = torch.full((n,), plane, device=device)
-                    else:
-                        e = torch.tensor(np.asarray(wp.exit_planes[i][lo : lo + n]), device=device).long()
-                        sp = e if args.mode == "exit_only" else torch.clamp(e, max=plane)
-                    st = torch.tensor(np.stack([np.asarray(t) for t in wp.src_tables[i]]), device=device).long()
-                    sb = st[sp, pos // s.block_size]
-                    expect[0] = pool.key_cache[sb, :, pos % s.block_size].view(torch.uint8)
-                    expect[1] = pool.value_cache[sb, :, pos % s.block_size].view(torch.uint8)
-                    dist.send(expect, d_rank)
-                else:
-                    dist.recv(expect, p)
-                    db = torch.tensor(list(reserved[(p, i)][plane]), device=device)[pos // s.block_size]
-                    carried = list(deep) if (deep and plane > 0) else list(range(s.num_layers))
-                    same = torch.equal(pool.key_cache[db, :, pos % s.block_size].view(torch.uint8)[:, carried], expect[0][:, carried]) and \
-                        torch.equal(pool.value_cache[db, :, pos % s.block_size].view(torch.uint8)[:, carried], expect[1][:, carried])
-                    ok *= float(same)
-    dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+    # ---- verification: every transferred row of every tensor (K, V, FP8 scales), by checksum over NCCL
+    from vllm_rlt_b200.pd import verify
+
+    if is_prefill:
+        checks = [(e["decode"], w, e["requests"], None) for e in plan]
+    else:
+        checks = [(e["source"], per_source[e["source"]], e["mine"], e["sub"]["dst"]) for e in edges]
+    verified, verified_bytes = verify.verify_over_group(pool, is_prefill, checks, mode=args.mode, deep=deep, device=device)
 
     # ---- end to end: the decode side stages tables from the host every step, launches, reads the status back
     e2e = []
@@ -308,16 +303,18 @@ def run_pull(args, rank: int, world: int) -> None:
             "config": bench.config_of(w, args, {
                 "split": f"{n_prefill}P:{n_decode}D", "variant": args.variant, "workload_name": args.workload,
                 "per_prefill_worker": w.description, "payload_bytes": total_payload,
-                "transport": "decode GPU pulls through peer pointers over NVLink (CUDA IPC mapping); ready and done flags per step"}),
-            "roofline": {"bound": "nvlink", "achieved": per_link, "peak": bench.NVLINK_MEASURED_GBS, "unit": "GB/s",
-                         "frac": per_link / bench.NVLINK_MEASURED_GBS,
+                "transport": "decode GPU pulls through peer pointers over NVLink (CUDA IPC mapping); ready and done flags per step; "
+                             "the prefill workers' block tables and exit planes reach the decode workers over NCCL"}),
+            "roofline": {"bound": "nvlink", "achieved": per_link, "peak": bench.NVLINK_NOMINAL_GBS, "unit": "GB/s",
+                         "frac": per_link / bench.NVLINK_NOMINAL_GBS,
                          "traffic": total_wire / max(1, n_decode) * bench.NVLINK_READ_OVERHEAD,
                          "traffic_source": "link bytes per launch: nvlrx__bytes.sum / nvlrx__bytes_data_user.sum = 1.125 from an "
                                            "ncu capture of the same kernel reading from a peer, scaled by the bytes read",
-                         "peak_source": "measured peer copy on this pool, 770 GB/s per direction per GPU (nominal 900)",
+                         "peak_source": "nominal NVLink 5 rate per direction per GPU (no driver-measured link peak exists); a plain peer-to-peer memcpy between two B200s reached 770 GB/s",
+                         "frac_of_peer_memcpy_770": per_link / bench.NVLINK_PEER_MEMCPY_GBS,
                          "kernel": "table_fan_kernel" if args.mode == "dedup" else "table_copy_kernel",
                          "algorithmic_bytes_per_launch": total_wire / max(1, n_decode),
-                         "kernel_ms": float(k_ms.item()), "frac_of_nominal_900": per_link / 900.0,
+                         "kernel_ms": float(k_ms.item()), "frac_of_nominal_900": per_link / bench.NVLINK_NOMINAL_GBS,
                          "raw_link_gbps": per_link * bench.NVLINK_READ_OVERHEAD,
                          "raw_link_frac_of_900": per_link * bench.NVLINK_READ_OVERHEAD / 900.0,
                          "raw_link_note": "read responses carry 12.5 % of protocol bytes on top of the payload (ncu nvlrx__bytes "
@@ -332,7 +329,12 @@ def run_pull(args, rank: int, world: int) -> None:
             "latency_ms": {"p50": statistics.median(lat), "max": max(lat), "min": min(lat),
                            "what": "rank 0 -> its first decode partner: ready flag, pull, done flag; CUDA events on the prefill stream; "
                                    "the decode side has its wait and pull queued before the flag is raised"},
-            "gpu_launches": int(n_launch.item()), "clocks": clock_box[0], "verified": bool(ok.item() == 1.0),
+            "gpu_launches": int(n_launch.item()), "clocks": clock_box[0],
+            "verified": verified and verified_bytes == int(total_payload), "verified_bytes": verified_bytes,
+            "verified_how": "64-bit position-weighted checksums of every transferred row of K, V and the FP8 scale tensors per "
+                            "(request, destination plane, tensor): source rows gathered with torch indexing on the prefill GPU, "
+                            "destination rows on the decode GPU, tables compared over NCCL; plus the fill byte in the unowned "
+                            "slots of partially filled blocks",
         }
         print(json.dumps(line), flush=True)
     dist.destroy_process_group()

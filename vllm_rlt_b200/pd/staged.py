@@ -144,30 +144,15 @@ def run_staged(args, rank: int, world: int) -> None:
     total_ms = torch.tensor([t0.elapsed_time(t1)], device=device)
     dist.all_reduce(total_ms, op=dist.ReduceOp.MAX)
 
-    # verification of the first tokens of request 0, every plane
-    ok = torch.ones(1, device=device)
-    n = min(48, w.lengths[0])
-    expect = torch.zeros((2, n, s.num_layers, s.num_kv_heads, s.head_dim * s.element), dtype=torch.uint8, device=device)
-    pos = torch.arange(n, device=device)
-    for plane in range(planes):
-        if is_prefill:
-            if w.exit_planes is None:
-                sp = torch.full((n,), plane, device=device)
-            else:
-                e = torch.tensor(np.asarray(w.exit_planes[0][:n]), device=device).long()
-                sp = e if args.mode == "exit_only" else torch.clamp(e, max=plane)
-            st = torch.tensor(np.stack([np.asarray(t) for t in w.src_tables[0]]), device=device).long()
-            sb = st[sp, pos // s.block_size]
-            expect[0] = src.key_cache[sb, :, pos % s.block_size].view(torch.uint8)
-            expect[1] = src.value_cache[sb, :, pos % s.block_size].view(torch.uint8)
-            dist.send(expect, partner)
-        else:
-            dist.recv(expect, partner)
-            db = torch.tensor(list(reserved[0][plane]), device=device)[pos // s.block_size]
-            same = torch.equal(dst.key_cache[db, :, pos % s.block_size].view(torch.uint8), expect[0]) and \
-                torch.equal(dst.value_cache[db, :, pos % s.block_size].view(torch.uint8), expect[1])
-            ok *= float(same)
-    dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+    # verification: every transferred row of every tensor, by checksum over NCCL
+    from vllm_rlt_b200.pd import verify
+
+    everything = list(range(len(w.lengths)))
+    if is_prefill:
+        verified, verified_bytes = verify.verify_over_group(src, True, [(partner, w, everything, None)], mode=args.mode, device=device)
+    else:
+        verified, verified_bytes = verify.verify_over_group(dst, False, [(partner, w, everything, reserved)], mode=args.mode,
+                                                            device=device)
     torch.cuda.synchronize()
     dist.barrier()
     mapping.close()
@@ -183,11 +168,13 @@ def run_staged(args, rank: int, world: int) -> None:
                 "split": f"{pairs}P:{pairs}D", "path": "pack into peer staging -> flag -> scatter (double buffered)",
                 "wire_bytes_per_pair": wire_bytes, "payload_bytes": payload,
                 "wire_fraction_of_payload": wire_bytes / w.payload_bytes}),
-            "roofline": {"bound": "nvlink", "achieved": wire_bytes / (ms * 1e-3) / 1e9, "peak": bench.NVLINK_MEASURED_GBS,
-                         "unit": "GB/s", "frac": wire_bytes / (ms * 1e-3) / 1e9 / bench.NVLINK_MEASURED_GBS, "traffic": None,
+            "roofline": {"bound": "nvlink", "achieved": wire_bytes / (ms * 1e-3) / 1e9, "peak": bench.NVLINK_NOMINAL_GBS,
+                         "unit": "GB/s", "frac": wire_bytes / (ms * 1e-3) / 1e9 / bench.NVLINK_NOMINAL_GBS, "traffic": None,
+                         "peak_source": "nominal NVLink 5 rate per direction per GPU",
                          "what": "bytes that actually cross NVLink per pair / time; `value` counts the destination bytes rebuilt"},
             "per_pair_gbps": w.payload_bytes / (ms * 1e-3) / 1e9, "e2e": None,
-            "gpu_launches": int(launches.item()), "verified": bool(ok.item() == 1.0),
+            "gpu_launches": int(launches.item()),
+            "verified": verified and verified_bytes == int(payload), "verified_bytes": verified_bytes,
         }
         print(json.dumps(line), flush=True)
     dist.destroy_process_group()
