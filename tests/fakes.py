@@ -19,9 +19,13 @@ class FakeEvent:
 class FakeBackend:
     """Backend of ``B200Transport`` over host memory: memmove for the copy, direct writes for the post."""
 
+    device_ordered = False
+
     def __init__(self):
         self.events = []
         self.complete_immediately = True
+        self.hold_start = False  # True: queued work has not begun (it waits behind a producer's event)
+        self.markers = []
         self.copies = []
         self.boxes = {}
 
@@ -53,8 +57,9 @@ class FakeBackend:
         return ()
 
     def handoff(self, cache, peer_info, translate, requests, *, mode=0, layer_begin=0, layer_end=0,
-                exit_planes=None, status=None):
-        """Row-by-row statement of the table-driven launch over host tensors (all-planes mode only)."""
+                plane_begin=0, plane_end=0, exit_planes=None, status=None, pull=False):
+        """Row-by-row statement of the table-driven launch over host tensors (all-planes mode only).
+        ``pull``: the peer's memory is the source and the local tensors the destination."""
         assert mode == 0 and exit_planes is None
         page, layers = cache.block_size, cache.num_layers
         layer_end = layer_end or layers
@@ -62,14 +67,19 @@ class FakeBackend:
         if peer_info.get("scale_region") is not None:
             pairs += [(cache.key_scale, "key_ptr", peer_info["scale_region"]), (cache.value_scale, "value_ptr", peer_info["scale_region"])]
         for source, target, start, end in requests:
-            for src_table, dst_table in zip(source, target, strict=True):
+            planes = list(zip(source, target, strict=True))
+            for src_table, dst_table in planes[plane_begin : plane_end or len(planes)]:
                 for t in range(start, end):
                     for tensor, key, region in pairs:
                         row = tensor.stride(2) * tensor.element_size()
                         for layer in range(layer_begin, layer_end):
                             off = layer * region["layer_bytes"] + (t % page) * region["token_bytes"]
-                            src = tensor.data_ptr() + src_table[t // page] * region["block_bytes"] + off
-                            dst = translate(region[key] + dst_table[t // page] * region["block_bytes"] + off, row)
+                            if pull:
+                                src = translate(region[key] + int(src_table[t // page]) * region["block_bytes"] + off, row)
+                                dst = tensor.data_ptr() + int(dst_table[t // page]) * region["block_bytes"] + off
+                            else:
+                                src = tensor.data_ptr() + int(src_table[t // page]) * region["block_bytes"] + off
+                                dst = translate(region[key] + int(dst_table[t // page]) * region["block_bytes"] + off, row)
                             ctypes.memmove(dst, src, row)
         self.copies.append(("tables", list(requests)))
         return ()
@@ -84,6 +94,14 @@ class FakeBackend:
         ev = FakeEvent(self.complete_immediately)
         self.events.append(ev)
         return ev
+
+    def marker(self):
+        ev = FakeEvent(not self.hold_start)
+        self.markers.append(ev)
+        return ev
+
+    def order_after(self, event):
+        pass
 
     def close(self):
         for box in self.boxes.values():

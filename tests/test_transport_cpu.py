@@ -163,3 +163,129 @@ def test_config_validation_matches_reference_rules():
             PDConfig(**bad)
     c = PDConfig()
     assert c.max_inflight_bytes >= 24 * 4 * 2 * 2048 * 16 * 128 * 2  # a 2048-token Ouro-1.4B prompt stays in flight whole
+
+
+# ----------------------------------------------------------------------------- pull direction
+
+
+def make_pull_pair(config=None, **cache_kw):
+    config = config or PDConfig()
+    pc, dc = cpu_cache(**cache_kw), cpu_cache(**cache_kw)
+    pc.key_cache.view(torch.uint8).random_(0, 256)
+    pc.value_cache.view(torch.uint8).random_(0, 256)
+    p = tr.B200Transport("p0", pc, torch.arange(32, dtype=torch.float32).reshape(2, 16), config, backend=FakeBackend(), direction="pull")
+    d = tr.B200Transport("d0", dc, torch.zeros(2, 16), config, backend=FakeBackend(), lane=1, direction="pull")
+    p.connect(d.info)
+    d.connect(p.info)
+    return p, d
+
+
+def test_an_offered_chunk_is_read_by_the_peer_and_completes_only_when_it_says_so():
+    p, d = make_pull_pair()
+    src_tables, dst_tables = ((3, 5), (7, 9), (11, 13), (2, 4)), ((1, 0), (6, 8), (10, 12), (14, 15))
+    hidden = (p.info["hidden_ptr"] + 64, d.info["hidden_ptr"], 64)
+    size = 6 * 4 * 2 * 3 * 32 + 64
+    assert p.submit_tables("tid", 0, "d0", [(src_tables, dst_tables, 1, 7)], size, extra=[hidden])
+    assert p.busy("tid") and p.inflight_bytes == size and not p.backend.copies  # nothing moved on the source
+    assert p.poll() == ([], []) and p.busy("tid")
+    assert not d.reading
+    _, notes = d.poll()  # finds the offer, reads the chunk (the fake copies at once), reports it, acknowledges
+    assert notes == [("p0", "tid", 0)] and d.bytes_received == size and not d.reading
+    assert [c[0] for c in d.backend.copies if isinstance(c, tuple)] == ["tables"]
+    finished, notes = p.poll()
+    assert [t.sequence for t in finished] == [0] and notes == [] and not p.busy("tid")
+    assert p.bytes_sent == size and p.inflight_bytes == 0 and p.transfers == 1
+    for plane in range(4):
+        for t in range(1, 7):
+            a = p.cache.key_cache[src_tables[plane][t // 4], :, t % 4].view(torch.uint8)
+            b = d.cache.key_cache[dst_tables[plane][t // 4], :, t % 4].view(torch.uint8)
+            assert torch.equal(a, b)
+    assert int(d.cache.key_cache[dst_tables[0][0], :, 0].view(torch.uint8).sum()) == 0  # token 0 was not in the range
+    assert torch.equal(d.storage[2][0], p.storage[2][1])  # the hidden row came along
+    for t in (p, d):
+        t.close()
+
+
+def test_a_reader_that_has_not_finished_keeps_the_source_busy_and_blocks_close():
+    p, d = make_pull_pair()
+    d.backend.complete_immediately = False
+    tables = ((0,), (1,), (2,), (3,))
+    assert p.submit_tables("t", 0, "d0", [(tables, tables, 0, 4)], 4 * 4 * 2 * 3 * 32)
+    assert d.poll() == ([], []) and d.reading
+    assert p.poll() == ([], []) and p.busy("t")
+    with pytest.raises(RuntimeError, match="in-flight"):
+        d.close()
+    d.backend.events[-1].done = True
+    assert d.poll()[1] == [("p0", "t", 0)] and not d.reading
+    assert len(p.poll()[0]) == 1
+    for t in (p, d):
+        t.close()
+
+
+def test_descriptors_are_cut_to_the_pages_of_the_chunk_and_round_trip():
+    source = (tuple(range(100, 140)), tuple(range(200, 240)))
+    target = (tuple(range(300, 340)), tuple(range(400, 440)))
+    s, t, lo, hi = tr.trim_request(source, target, 70, 101, 16)
+    assert (lo, hi) == (6, 37) and s == ((104, 105, 106), (204, 205, 206)) and t == ((304, 305, 306), (404, 405, 406))
+    raw = tr.encode_chunk([(s, t, lo, hi)], [(1 << 40, 1 << 41, 64)], mode=0, layer_begin=2, layer_end=5, plane_begin=1, plane_end=2)
+    assert len(raw) < 200
+    requests, extra, where = tr.decode_chunk(raw)
+    assert [[list(x) for x in side] for side in requests[0][:2]] == [[list(x) for x in s], [list(x) for x in t]]
+    assert requests[0][2:] == (6, 37) and extra == [(1 << 40, 1 << 41, 64)]
+    assert where == dict(mode=0, layer_begin=2, layer_end=5, plane_begin=1, plane_end=2)
+    with pytest.raises(ValueError, match="invalid KV range"):
+        tr.encode_chunk([(s, t, 5, 5)], [])
+
+
+def test_the_descriptor_ring_applies_back_pressure_and_reuses_space_in_order():
+    ring = tr._RingWriter(size=100)
+    assert ring.reserve(40, 1, 0) == 0 and ring.reserve(40, 2, 0) == 40
+    assert ring.reserve(40, 3, 0) is None          # 20 bytes at the end, nothing consumed: no room
+    assert ring.reserve(40, 3, 1) == 0             # message 1 consumed: its bytes are free again (wraps to the front)
+    assert ring.reserve(30, 4, 1) is None          # would run into message 2's bytes
+    assert ring.reserve(30, 4, 3) == 40            # everything consumed: continues after the last region
+    with pytest.raises(ValueError, match="larger than the descriptor ring"):
+        ring.reserve(101, 5, 4)
+    p, d = make_pull_pair()
+    wide = tuple(tuple(range(i, i + 4)) for i in (0, 4, 8, 12))
+    sent = 0
+    while p.submit_tables("t", sent, "d0", [(wide, wide, 0, 16)], 16 * 4 * 2 * 3 * 32):
+        sent += 1
+        assert sent <= tr.SLOTS  # the message ring fills first with descriptors this small
+    assert sent == tr.SLOTS
+    assert len(d.poll()[1]) == sent
+    assert p.submit_tables("t", sent, "d0", [(wide, wide, 0, 16)], 16 * 4 * 2 * 3 * 32)
+    d.poll()
+    assert d.reading      # the source has not read its 256 "pulled" messages yet: the 257th waits for a slot
+    p.poll()
+    d.poll()
+    assert not d.reading
+    p.poll()
+    assert not p.pending
+    for t in (p, d):
+        t.close()
+
+
+def test_time_outs_and_transfer_time_count_from_when_the_copy_could_begin():
+    """A chunk queued behind a long prefill is not a slow transfer: the clock starts when the transfer stream gets
+    to it, not when it was queued."""
+    import time
+
+    config = PDConfig(request_timeout=0.05)
+    p, d = make_pair(config)
+    p.backend.hold_start = True
+    p.backend.complete_immediately = False
+    assert p.submit("t", 0, "d0", [block_range(p.info, 0, 64)], [block_range(d.info, 0, 64)], 64)
+    time.sleep(0.12)
+    assert p.poll() == ([], [])                    # twice the time-out has passed, but the copy has not begun
+    p.backend.markers[-1].done = True
+    assert p.poll() == ([], [])                    # begun now: the clock starts here
+    p.backend.events[-1].done = True
+    finished, _ = p.poll()
+    assert len(finished) == 1 and p.transfer_seconds < 0.05
+    assert p.submit("t", 1, "d0", [block_range(p.info, 0, 64)], [block_range(d.info, 0, 64)], 64)
+    p.backend.markers[-1].done = True
+    p.poll()
+    time.sleep(0.12)
+    with pytest.raises(TimeoutError, match="quarantined"):
+        p.poll()

@@ -7,12 +7,29 @@ verbs (``connect, reserve, prefill, cancel, cancel_safe, commit, ack, abort``) a
 (``connected, reserved, prefill_started, prefill_complete, commit, received, activated, released,
 rejected``) are the reference's, as are the error messages callers match on.
 
-What changes is what a queued chunk is. The reference turns a token range into two Python lists of
-byte descriptors (``kv_segments`` on both sides, ``partition_segments``) and submits them one list at
-a time. Here a chunk is a ``TableChunk``: block tables of both sides plus a token range, cut so that
-its payload stays under ``transfer_chunk_bytes``. One chunk is one ``rlt_kv_handoff`` launch in which
-the GPU walks the tables itself, and one ``(transfer id, sequence)`` notification. Sequence numbers,
-one notification per submitted chunk and ``commit.count == next_sequence`` are kept.
+How it is built. Every transfer generation is a ``RequestTransfer`` record whose fields are the reference's
+(its tests and the coordinator read and set them). What a record is *doing* is a ``Stage``, derived from those
+fields, and each of the two roles owns a table ``{Stage: step}``:
+
+* ``Exporter`` (a prefill worker's outgoing transfers): COMPUTING -> DRAINING -> COMMITTED -> retired, with
+  UNWINDING for a cancelled export that must outlive its last local and remote reader;
+* ``Importer`` (a decode worker's incoming transfers): COLLECTING -> LANDED -> SERVING -> retired, with
+  ABANDONED for a cancelled import that waits for the coordinator's "writers have stopped".
+
+``progress()`` polls the transport once, lets the importer book the arrivals, gives every transfer one step of
+its role's table in a rotating order, then lets the exporter fill the in-flight budget round-robin and settle
+commits and retirements.
+
+What a queued chunk is. The reference turns a token range into two Python lists of byte descriptors
+(``kv_segments`` on both sides, ``partition_segments``) and submits them one list at a time. Here a chunk is a
+``TableChunk``: block tables of both sides plus a token range (optionally one layer group of one plane), cut so
+that its payload stays under ``transfer_chunk_bytes``. One chunk is one ``rlt_kv_handoff`` launch in which the
+GPU walks the tables itself, and one ``(transfer id, sequence)`` notification. Sequence numbers, one notification
+per submitted chunk and ``commit.count == next_sequence`` are kept.
+
+Layer streaming. ``layer_written(request, plane=, layer=, event=)`` is an optional producer hook beside the
+protocol: a model runner that calls it after queuing a layer's KV writes lets the slice leave while later layers
+still compute; ``prefill_submitted`` then only sends what is left. Nobody calling it changes nothing.
 
 The object asks the engine to change request, compute or KV state (``reserve_transfer``,
 ``accept_import``, ``release_transfer_compute``, ``release_transfer``, ``suspend_transfer``); it owns
@@ -21,6 +38,7 @@ only transfer bookkeeping and the hidden-state staging rows.
 
 from __future__ import annotations
 
+import enum
 import hashlib
 import json
 import time
@@ -30,7 +48,7 @@ from dataclasses import asdict, dataclass, field, is_dataclass, replace
 
 @dataclass
 class TableChunk:
-    """One bounded submission: tokens ``[start, end)`` of every plane, by block table."""
+    """One bounded submission: tokens ``[start, end)`` by block table, of every plane and layer unless sliced."""
 
     event: object
     sequence: int
@@ -40,11 +58,14 @@ class TableChunk:
     end: int
     size: int
     hidden: tuple | None = None  # (source address, target address, bytes) of the final hidden row
+    planes: tuple[int, int] | None = None  # destination plane slice [begin, end), None = every plane
+    layers: tuple[int, int] | None = None  # layer slice [begin, end), None = every layer
 
 
 @dataclass
 class RequestTransfer:
-    """Bookkeeping of one transfer generation; field names follow vllm_rlt/pd/connector.py:17-46."""
+    """Bookkeeping of one transfer generation. The fields up to ``started`` are those of the reference's record
+    (vllm_rlt/pd/connector.py:17-46), which its tests and tools construct and poke directly."""
 
     tid: str
     request: object
@@ -74,13 +95,52 @@ class RequestTransfer:
     last_event: object = None
     acknowledged: bool = False
     started: float = field(default_factory=time.monotonic)
+    # layer streaming: per destination plane, how many layers of the current prefill window have left already
+    streamed_layers: dict = field(default_factory=dict)
+    streamed_window: tuple | None = None
+
+    def note_range(self, start: int, end: int) -> None:
+        """Remember the first and last token range put on the wire, and how many there were."""
+        if self.transfer_boundary_first is None:
+            self.transfer_boundary_first = (start, end)
+        self.transfer_boundary_last = (start, end)
+        self.transfer_boundary_count += 1
+
+
+class Stage(enum.Enum):
+    """What a transfer generation is doing, as far as this worker is concerned."""
+
+    # outgoing
+    COMPUTING = "prompt still being computed; finished ranges leave as they are queued"
+    DRAINING = "prompt computed; queued chunks are still going out"
+    COMMITTED = "every chunk is out and the count is announced; waits for ack, compute release, last reader"
+    UNWINDING = "cancelled export: waits for its local and remote readers to finish"
+    # incoming
+    COLLECTING = "reserved; notifications are being counted against the announced total"
+    LANDED = "complete and handed to the engine; waits for a compute slot"
+    SERVING = "admitted to compute; the record lives until the request leaves the scheduler"
+    ABANDONED = "cancelled import: waits for proof that no writer is left"
+
+
+def stage_of(t: RequestTransfer) -> Stage:
+    if t.outgoing:
+        if t.cancelled:
+            return Stage.UNWINDING
+        if t.committed:
+            return Stage.COMMITTED
+        return Stage.DRAINING if t.compute_done else Stage.COMPUTING
+    if t.cancelled:
+        return Stage.ABANDONED
+    if not t.ready:
+        return Stage.COLLECTING
+    return Stage.SERVING if t.active else Stage.LANDED
 
 
 def _phase_name(phase) -> str:
     return str(getattr(phase, "name", phase)).upper()
 
 
-def _event_done(event) -> bool:
+def _fired(event) -> bool:
     return event is None or bool(event.query())
 
 
@@ -93,13 +153,16 @@ class PDStageConnector:
         self.config = config
         self.notify = notify
         self.transfers: dict[str, RequestTransfer] = {}
-        self.free_slots = list(range(len(hidden) - 1, -1, -1))
+        self.free_slots = [*range(len(hidden))][::-1]
         self.transfer_cursor = 0
         self.prefill_tokens = 0
-        self._verbs = {
-            "connect": self._on_connect,
-            "reserve": self._on_reserve,
-            "prefill": self._on_reserve,
+        self.stream_layers = 4  # layers per slice that ``layer_written`` lets go at once
+        self.exporter = Exporter(self)
+        self.importer = Importer(self)
+        self._control = {
+            "connect": lambda c: self._connect(c["peers"]),
+            "reserve": lambda c: self._reserve_from(c, receiving=True),
+            "prefill": lambda c: self._reserve_from(c, receiving=False),
             "cancel": lambda c: self.cancel(c["tid"]),
             "cancel_safe": lambda c: self.cancel_safe(c["tid"]),
             "commit": lambda c: self.commit(c["tid"], c["count"]),
@@ -121,183 +184,119 @@ class PDStageConnector:
 
         stage = engine.stage_config
         rows = engine.scheduler.config.max_num_seqs
-        if stage.produces_tokens:
-            rows += config.max_receiving_requests
-        if stage.accepts_prompt:
-            rows += config.max_draining_requests
+        rows += config.max_receiving_requests if stage.produces_tokens else 0
+        rows += config.max_draining_requests if stage.accepts_prompt else 0
         anchor = next(engine.model.parameters())
         hidden = torch.empty((rows, engine.model.config.hidden_size), device=anchor.device, dtype=anchor.dtype)
-        factory = transport_factory or B200Transport
-        return cls(engine, hidden, factory(stage.stage_id, engine.cache_manager, hidden, config), config, notify=notify)
+        make = transport_factory or B200Transport
+        return cls(engine, hidden, make(stage.stage_id, engine.cache_manager, hidden, config), config, notify=notify)
 
     def startup_info(self):
         """Transport info plus a fingerprint of model config, weights, dtype, layout and attention
         (vllm_rlt/pd/connector.py:78-98); the coordinator refuses workers whose fingerprints differ."""
         import torch
 
+        model = self.engine.model
         weights = hashlib.sha256()
-        for tensor in self.engine.model.state_dict().values():
+        for tensor in model.state_dict().values():
             weights.update(tensor.detach().contiguous().view(torch.uint8).cpu().numpy().tobytes())
-        anchor = next(self.engine.model.parameters())
-        model_config = self.engine.model.config
-        described = dict(
-            model=asdict(model_config) if is_dataclass(model_config) else dict(vars(model_config)),
-            weights=weights.hexdigest(),
-            dtype=str(anchor.dtype).removeprefix("torch."),
-            layout=self.cache.layout,
-            attention=self.cache.attention_info,
-        )
-        fingerprint = hashlib.sha256(json.dumps(described, sort_keys=True).encode()).hexdigest()
-        return dict(info=self.transport.info, fingerprint=fingerprint, transfer_slots=len(self.hidden))
+        settings = model.config
+        identity = {
+            "model": asdict(settings) if is_dataclass(settings) else dict(vars(settings)),
+            "weights": weights.hexdigest(),
+            "dtype": str(next(model.parameters()).dtype).removeprefix("torch."),
+            "layout": self.cache.layout,
+            "attention": self.cache.attention_info,
+        }
+        fingerprint = hashlib.sha256(json.dumps(identity, sort_keys=True).encode()).hexdigest()
+        return {"info": self.transport.info, "fingerprint": fingerprint, "transfer_slots": len(self.hidden)}
 
     @property
     def has_pending(self):
-        return bool(self.transfers or self.transport.pending)
+        return bool(self.transfers or self.transport.pending or getattr(self.transport, "reading", False) is True)
 
     # ------------------------------------------------------------------ control verbs
 
     def command(self, command):
         kind = command["kind"]
-        handler = self._verbs.get(kind)
-        if handler is not None:
-            handler(command)
+        if kind in self._control:
+            self._control[kind](command)
             return True
         if kind == "abort" and command["request_id"] in self.transfers:
             raise ValueError("transferred requests must use the transfer cancellation protocol")
         return False
 
-    def _on_connect(self, command):
-        for peer in command["peers"]:
+    def _connect(self, peers):
+        for peer in peers:
             self.transport.connect(peer)
         self.notify("connected")
 
-    def _on_reserve(self, command):
-        self.reserve(
-            command["tid"], command["tokens"], command["params"],
-            receiving=command["kind"] == "reserve",
-            peer=command["peer"],
-            trace_id=command.get("trace_id"),
-            target_tables=command.get("tables", ()),
-            target_slot=command.get("slot", 0),
-            target_cached_tokens=command.get("cached_tokens", 0),
-        )
+    def _reserve_from(self, command, *, receiving):
+        self.reserve(command["tid"], command["tokens"], command["params"], receiving=receiving, peer=command["peer"],
+                     trace_id=command.get("trace_id"), target_tables=command.get("tables", ()),
+                     target_slot=command.get("slot", 0), target_cached_tokens=command.get("cached_tokens", 0))
 
     def close(self):
         if self.has_pending:
             raise RuntimeError("cannot close a connector with pending transfers")
         self.transport.close()
-        return dict(
-            prefill_tokens=self.prefill_tokens,
-            bytes_sent=self.transport.bytes_sent,
-            transfers=self.transport.transfers,
-            transfer_seconds=self.transport.transfer_seconds,
-        )
+        t = self.transport
+        return {"prefill_tokens": self.prefill_tokens, "bytes_sent": t.bytes_sent, "transfers": t.transfers,
+                "transfer_seconds": t.transfer_seconds}
 
     # ------------------------------------------------------------------ StageConnector part
 
-    def exports(self, request):
+    def _export_of(self, request):
         t = self.transfers.get(request.request_id)
-        return t is not None and t.request is request and t.outgoing
+        return t if t is not None and t.outgoing and t.request is request else None
+
+    def exports(self, request):
+        return self._export_of(request) is not None
 
     def can_schedule(self, request):
-        """Back-pressure for an exporting request: its queue is drained, its last event has fired, and the
-        in-flight budget has room (vllm_rlt/pd/connector.py:175-186). Never mutates anything."""
-        if not self.exports(request):
+        """Back-pressure for an exporting request (vllm_rlt/pd/connector.py:175-186): it may compute again once
+        nothing of it is queued, its last event has fired and the in-flight budget has room. Mutates nothing."""
+        t = self._export_of(request)
+        if t is None:
             return True
-        t = self.transfers[request.request_id]
-        return bool(
-            not t.cancelled
-            and not t.chunks
-            and _event_done(t.last_event)
-            and self.transport.inflight_bytes < self.config.max_inflight_bytes
-        )
+        if t.cancelled or t.chunks or not _fired(t.last_event):
+            return False
+        return self.transport.inflight_bytes < self.config.max_inflight_bytes
 
     def prefill_submitted(self, request, *, phase, start, progress, event, stream):
-        import torch
-
+        """The engine has queued one prefill step of an exporting request
+        (vllm_rlt/engine/connector.py:18-33, vllm_rlt/pd/connector.py:188-218)."""
         t = self.transfers[request.request_id]
         if t.request is not request:
             raise RuntimeError("stale transfer generation")
-        name = _phase_name(phase)
-        wavefront = getattr(self.engine.scheduler.config, "wavefront_chunked_prefill", False)
-        if name == "PREFILLING_PRELUDE" or (name == "PREFILLING_RECURRENT" and wavefront):
-            # The transfer overlapped this compute step if it is on the wire now or went out since the last one.
-            t.transfer_overlaps += bool(self.transport.busy(t.tid) or t.submitted_since_compute)
-        t.submitted_since_compute = False
-        if not progress.chunk_complete:
-            t.last_event = event
-            return
-        stream = stream or torch.cuda.current_stream(self.cache.device)
-        with torch.cuda.stream(stream):
-            if event is not None:
-                stream.wait_event(event)
-            if progress.prompt_complete:
-                self.hidden[t.slot].copy_(request.hidden_state)
-            ready = torch.cuda.Event()
-            ready.record(stream)
-        t.last_event = ready
-        self.prefill_tokens += request.num_prefilled_tokens - start
-        self.queue_chunk(t, start, request.num_prefilled_tokens, ready, progress.prompt_complete)
-        t.compute_done = progress.prompt_complete
+        self.exporter.step_submitted(t, _phase_name(phase), start, progress, event, stream)
+
+    def layer_written(self, request, *, plane, layer, event=None, start=None, end=None):
+        """Optional producer hook: the KV writes of ``layer`` at destination plane ``plane`` for the tokens
+        ``[start, end)`` of the request's current prefill window have been queued, all earlier layers of that plane
+        too, and ``event`` (recorded by the caller after them) covers them. Returns True if a slice was queued.
+
+        ``start`` / ``end`` default to the window ``[num_prefilled_tokens, ...)`` the engine reports with the next
+        ``prefill_submitted``; callers that know the window pass it. Slices are cut at ``stream_layers`` layers.
+        """
+        t = self._export_of(request)
+        if t is None or t.cancelled:
+            return False
+        return self.exporter.layer_written(t, plane, layer, event, start, end)
 
     # ------------------------------------------------------------------ planning
 
-    def _token_plane_bytes(self) -> int:
+    def _row_bytes(self) -> int:
+        """Bytes of one token of one layer of K or V, scales included when they travel."""
         info = self.transport.info
-        per = info["token_bytes"]
-        if info.get("scale_region") is not None:
-            per += info["scale_region"]["token_bytes"]
-        return 2 * info["num_layers"] * per
+        scales = info.get("scale_region")
+        return info["token_bytes"] + (scales["token_bytes"] if scales is not None else 0)
 
     def queue_chunk(self, transfer, start, end, event, final):
-        """Cut tokens ``[start, end)`` into table chunks no larger than ``transfer_chunk_bytes``.
-
-        The prefix skip (``start = max(start, target_cached_tokens)``) and the boundary
-        bookkeeping are those of vllm_rlt/pd/connector.py:220-229; the hidden row rides with the
-        last chunk when ``final`` (:232-241).
-        """
-        info = self.transport.info
-        peer = self.transport.peers[transfer.peer]
-        tables = self.cache.plane_block_tables(transfer.tid)
-        start = max(start, transfer.target_cached_tokens)
-        pieces = []
-        if start < end:
-            span = (start, end)
-            if transfer.transfer_boundary_first is None:
-                transfer.transfer_boundary_first = span
-            transfer.transfer_boundary_last = span
-            transfer.transfer_boundary_count += 1
-            if len(tables) != len(transfer.target_tables):
-                raise ValueError("incompatible source/target KV geometry")
-            page = info["block_size"]
-            for table, target in zip(tables, transfer.target_tables):
-                if end > len(table) * page or end > len(target) * page:
-                    raise ValueError("KV range exceeds allocation")
-            per_token = self._token_plane_bytes() * len(tables)
-            step = max(1, self.config.transfer_chunk_bytes // per_token)
-            at = start
-            while at < end:
-                stop = min(end, at + step)
-                pieces.append((at, stop, (stop - at) * per_token))
-                at = stop
-        hidden = None
-        if final:
-            size = info["hidden_bytes"]
-            hidden = (info["hidden_ptr"] + transfer.slot * size, peer["hidden_ptr"] + transfer.target_slot * size, size)
-            if not pieces or pieces[-1][2] + size > self.config.transfer_chunk_bytes:
-                pieces.append((end, end, 0))
-        for index, (lo, hi, size) in enumerate(pieces):
-            last = index == len(pieces) - 1
-            transfer.chunks.append(TableChunk(
-                event, transfer.next_sequence, tuple(tables), tuple(transfer.target_tables), lo, hi,
-                size + (hidden[2] if hidden and last else 0), hidden if last else None,
-            ))
-            transfer.next_sequence += 1
-        if self._device_ordered():
-            # No need to wait for the next progress() pass: queue the copies now, behind the producer's event
-            # on the device, for as long as the in-flight budget admits them.
-            while transfer.chunks and not transfer.cancelled and self._submit_chunk(transfer):
-                pass
+        """Queue tokens ``[start, end)`` of every plane behind ``event``; with ``final`` the hidden row rides on the
+        last chunk. Same contract as vllm_rlt/pd/connector.py:220-246: the decode side's cached prefix is skipped
+        and every chunk gets the next sequence number."""
+        self.exporter.queue_range(transfer, start, end, event, final)
 
     def _device_ordered(self) -> bool:
         return getattr(self.transport, "device_ordered", False) is True
@@ -310,31 +309,18 @@ class PDStageConnector:
         if tid in self.transfers:
             raise RuntimeError("duplicate transfer generation")
         role = self.engine.stage_config.role
-        if not self.free_slots:
-            self.notify("rejected", tid=tid, role=role)
-            return
-        # The prefill side only produces prompt KV and never samples; the decode side owns sampling.
-        effective = params if receiving else replace(params, max_tokens=1)
-        request = self.engine.reserve_transfer(tid, tokens, effective, receiving=receiving, trace_id=trace_id)
+        request = None
+        if self.free_slots:
+            # a prefill worker only produces prompt KV and never samples: one token of budget is all it needs
+            wanted = params if receiving else replace(params, max_tokens=1)
+            request = self.engine.reserve_transfer(tid, tokens, wanted, receiving=receiving, trace_id=trace_id)
         if request is None:
             self.notify("rejected", tid=tid, role=role)
             return
-        t = RequestTransfer(tid, request, self.free_slots.pop(), peer, outgoing=not receiving, trace_id=trace_id)
-        t.cached_tokens = request.num_prefilled_tokens
+        t = RequestTransfer(tid, request, self.free_slots.pop(), peer, outgoing=not receiving, trace_id=trace_id,
+                            cached_tokens=request.num_prefilled_tokens)
         self.transfers[tid] = t
-        if receiving:
-            self.notify("reserved", tid=tid, tables=self.cache.plane_block_tables(tid), slot=t.slot,
-                        cached_tokens=t.cached_tokens)
-            return
-        t.target_tables, t.target_slot, t.target_cached_tokens = target_tables, target_slot, target_cached_tokens
-        if t.cached_tokens > target_cached_tokens:
-            # The prefill side already holds more of the prompt than the decode side: send that part now.
-            import torch
-
-            event = torch.cuda.Event()
-            event.record(torch.cuda.current_stream(self.cache.device))
-            self.queue_chunk(t, target_cached_tokens, t.cached_tokens, event, False)
-        self.notify("prefill_started", tid=tid)
+        (self.importer if receiving else self.exporter).opened(t, target_tables, target_slot, target_cached_tokens)
 
     def _forget(self, t):
         self.free_slots.append(t.slot)
@@ -342,21 +328,24 @@ class PDStageConnector:
         self.notify("released", tid=t.tid, role=self.engine.stage_config.role)
 
     def _remove(self, t):
-        if t.tid not in self.engine.scheduler.requests or self.engine.release_transfer(t.request):
-            self._forget(t)
+        """Retire a generation: the engine lets go of request and KV first, unless it no longer knows the request."""
+        if t.tid in self.engine.scheduler.requests and not self.engine.release_transfer(t.request):
+            return
+        self._forget(t)
+
+    def _announce_active(self, t):
+        if t.active:
+            return
+        t.active = True
+        self.notify("activated", tid=t.tid, seconds=time.monotonic() - t.started)
 
     def output_finished(self, request_id):
         t = self.transfers.get(request_id)
         if t is None:
             return
-        self._mark_active(t)
+        self._announce_active(t)
         if request_id not in self.engine.scheduler.requests:
             self._forget(t)
-
-    def _mark_active(self, t):
-        if not t.active:
-            t.active = True
-            self.notify("activated", tid=t.tid, seconds=time.monotonic() - t.started)
 
     def cancel(self, transfer_id):
         t = self.transfers.get(transfer_id)
@@ -364,11 +353,7 @@ class PDStageConnector:
             self.notify("released", tid=transfer_id, role=self.engine.stage_config.role)
             return
         t.cancelled = True
-        if t.outgoing:
-            t.chunks.clear()
-            self.engine.suspend_transfer(t.request)
-        elif t.ready:
-            self._remove(t)  # every expected write was seen, so no remote writer is left
+        (self.exporter if t.outgoing else self.importer).cancelled(t)
 
     def cancel_safe(self, transfer_id):
         t = self.transfers.get(transfer_id)
@@ -405,107 +390,320 @@ class PDStageConnector:
 
     def progress(self):
         self.cache.poll_prefixes()
-        self._take_notifications()
-        order = list(self.transfers.values())
-        if order:
-            pivot = self.transfer_cursor % len(order)
-            order = order[pivot:] + order[:pivot]
+        _, arrivals = self.transport.poll()
+        self.importer.book(arrivals)
+        turn = list(self.transfers.values())
+        if turn:
+            first = self.transfer_cursor % len(turn)
+            turn = turn[first:] + turn[:first]
             self.transfer_cursor += 1
-        for t in order:
-            if t.outgoing:
-                self._advance_outgoing(t)
-            else:
-                self._advance_incoming(t)
-        # Fill the in-flight budget: further round-robin passes while any transfer still gets a chunk out.
-        live = [t for t in order if t.outgoing and not t.cancelled]
-        while live:
-            sent = [self._submit_chunk(t) for t in live]
-            if not any(sent):
-                break
-            live = [t for t in live if t.chunks]
-        for t in order:
-            if not t.outgoing or t.cancelled:
-                continue
-            if t.compute_done and not t.chunks and not t.committed:
-                t.committed = True
-                self.notify("commit", tid=t.tid, count=t.next_sequence)
-            if t.acknowledged and t.committed and t.request.compute_released and not self.transport.busy(t.tid):
-                self._remove(t)
+        for t in turn:
+            role = self.exporter if t.outgoing else self.importer
+            role.table[stage_of(t)](t)
+        self.exporter.fill_budget(turn)
+        self.exporter.settle(turn)
 
-    def _take_notifications(self):
-        _, notifications = self.transport.poll()
-        for peer, tid, sequence in notifications:
-            t = self.transfers.get(tid)
+    def _submit_chunk(self, t):
+        """Put the transfer's next chunk on the wire once its event allows; True if one went out."""
+        return self.exporter.send_next(t)
+
+
+class Exporter:
+    """Outgoing side: ranges of a prompt leave as the prefill finishes them; the source is retired in two steps."""
+
+    def __init__(self, connector: PDStageConnector):
+        self.c = connector
+        self.table = {
+            Stage.COMPUTING: self.send_next,
+            Stage.DRAINING: self.drain,
+            Stage.COMMITTED: self.drain,
+            Stage.UNWINDING: self.unwind,
+        }
+
+    # -- opening and cancelling
+
+    def opened(self, t, target_tables, target_slot, target_cached_tokens):
+        c = self.c
+        t.target_tables, t.target_slot, t.target_cached_tokens = target_tables, target_slot, target_cached_tokens
+        if t.cached_tokens > target_cached_tokens:
+            # this worker already holds more of the prompt than the decode side (its own prefix cache): that part
+            # can leave at once, behind whatever the compute stream has queued so far
+            import torch
+
+            marker = torch.cuda.Event()
+            marker.record(torch.cuda.current_stream(c.cache.device))
+            c.queue_chunk(t, target_cached_tokens, t.cached_tokens, marker, False)
+        c.notify("prefill_started", tid=t.tid)
+
+    def cancelled(self, t):
+        t.chunks.clear()
+        self.c.engine.suspend_transfer(t.request)
+
+    # -- the engine's reports
+
+    def step_submitted(self, t, phase, start, progress, event, stream):
+        import torch
+
+        c = self.c
+        wavefront = getattr(c.engine.scheduler.config, "wavefront_chunked_prefill", False)
+        if phase == "PREFILLING_PRELUDE" or (wavefront and phase == "PREFILLING_RECURRENT"):
+            # the transfer overlapped this compute step if it is on the wire now or went out since the last one
+            t.transfer_overlaps += bool(c.transport.busy(t.tid) or t.submitted_since_compute)
+        t.submitted_since_compute = False
+        if not progress.chunk_complete:
+            t.last_event = event
+            return
+        request = t.request
+        lane = stream or torch.cuda.current_stream(c.cache.device)
+        with torch.cuda.stream(lane):
+            if event is not None:
+                lane.wait_event(event)
+            if progress.prompt_complete:
+                c.hidden[t.slot].copy_(request.hidden_state)
+            ready = torch.cuda.Event()
+            ready.record(lane)
+        t.last_event = ready
+        end = request.num_prefilled_tokens
+        c.prefill_tokens += end - start
+        c.queue_chunk(t, start, end, ready, progress.prompt_complete)
+        t.compute_done = progress.prompt_complete
+
+    def layer_written(self, t, plane, layer, event, start, end):
+        c = self.c
+        info = c.transport.info
+        layers_total = info["num_layers"]
+        if not 0 <= layer < layers_total or not 0 <= plane < len(t.target_tables):
+            raise ValueError("layer or plane outside the pool")
+        request = t.request
+        lo = request.num_prefilled_tokens if start is None else start
+        hi = len(request.prompt_token_ids) if end is None else end
+        lo = max(lo, t.target_cached_tokens)
+        if lo >= hi:
+            return False
+        if t.streamed_window != (lo, hi):
+            t.streamed_window, t.streamed_layers = (lo, hi), {}
+        sent = t.streamed_layers.get(plane, 0)
+        if layer + 1 <= sent:
+            raise ValueError("layers of a plane must be reported in increasing order")
+        group = max(1, int(c.stream_layers))
+        if layer + 1 - sent < group and layer + 1 < layers_total:
+            return False
+        if event is None:
+            import torch
+
+            event = torch.cuda.Event()
+            event.record(torch.cuda.current_stream(c.cache.device))
+        tables = c.cache.plane_block_tables(t.tid)
+        self._enqueue(t, tables, lo, hi, event, planes=(plane, plane + 1), layers=(sent, layer + 1))
+        t.streamed_layers[plane] = layer + 1
+        t.last_event = event
+        self.flush(t)
+        return True
+
+    # -- planning
+
+    def queue_range(self, t, start, end, event, final):
+        c = self.c
+        info = c.transport.info
+        start = max(start, t.target_cached_tokens)
+        tables = c.cache.plane_block_tables(t.tid)
+        if start < end:
+            t.note_range(start, end)
+            if len(tables) != len(t.target_tables):
+                raise ValueError("incompatible source/target KV geometry")
+            if t.streamed_window == (start, end):
+                # layer_written already sent part of this window: only the layers it did not reach are left
+                for plane in range(len(tables)):
+                    sent = t.streamed_layers.get(plane, 0)
+                    if sent < info["num_layers"]:
+                        self._enqueue(t, tables, start, end, event, planes=(plane, plane + 1),
+                                      layers=(sent, info["num_layers"]))
+                t.streamed_window, t.streamed_layers = None, {}
+            else:
+                self._enqueue(t, tables, start, end, event)
+        if final:
+            self._attach_hidden(t, tables, end, event)
+        self.flush(t)
+
+    def _enqueue(self, t, tables, start, end, event, *, planes=None, layers=None):
+        """Cut ``[start, end)`` (of a plane / layer slice, if given) into chunks under ``transfer_chunk_bytes``:
+        by tokens while one token fits, by plane and then by layer group when even one token is too large."""
+        c = self.c
+        info = c.transport.info
+        page = info["block_size"]
+        for table in (*tables, *t.target_tables):
+            if end > len(table) * page:
+                raise ValueError("KV range exceeds allocation")
+        limit = c.config.transfer_chunk_bytes
+        plane_lo, plane_hi = planes or (0, len(tables))
+        layer_lo, layer_hi = layers or (0, info["num_layers"])
+        row = 2 * c._row_bytes()  # K and V of one token of one layer
+        slices = [(planes, layers)]
+        if (plane_hi - plane_lo) * (layer_hi - layer_lo) * row > limit:
+            if row > limit:
+                raise ValueError("transfer_chunk_bytes is smaller than one token row of one layer")
+            per_layer_group = limit // row
+            slices = [((plane, plane + 1), (at, min(layer_hi, at + per_layer_group)))
+                      for plane in range(plane_lo, plane_hi) for at in range(layer_lo, layer_hi, per_layer_group)]
+        for plane_slice, layer_slice in slices:
+            p0, p1 = plane_slice or (0, len(tables))
+            l0, l1 = layer_slice or (0, info["num_layers"])
+            per_token = (p1 - p0) * (l1 - l0) * row
+            step = max(1, limit // per_token)
+            for at in range(start, end, step):
+                stop = min(end, at + step)
+                t.chunks.append(TableChunk(event, t.next_sequence, tuple(tables), tuple(t.target_tables), at, stop,
+                                           (stop - at) * per_token, None, plane_slice, layer_slice))
+                t.next_sequence += 1
+
+    def _attach_hidden(self, t, tables, end, event):
+        """The final hidden-state row rides on the last queued chunk if it fits, else goes alone."""
+        c = self.c
+        info, peer = c.transport.info, c.transport.peers[t.peer]
+        size = info["hidden_bytes"]
+        row = (info["hidden_ptr"] + t.slot * size, peer["hidden_ptr"] + t.target_slot * size, size)
+        last = t.chunks[-1] if t.chunks else None
+        if isinstance(last, TableChunk) and last.event is event and last.size + size <= c.config.transfer_chunk_bytes:
+            last.hidden, last.size = row, last.size + size
+            return
+        t.chunks.append(TableChunk(event, t.next_sequence, tuple(tables), tuple(t.target_tables), end, end, size, row))
+        t.next_sequence += 1
+
+    # -- sending
+
+    def flush(self, t):
+        """With a device-ordered transport nothing waits for the next ``progress()``: queue the copies now, behind
+        the producer's event on the device, for as long as the in-flight budget admits them."""
+        if self.c._device_ordered():
+            while t.chunks and not t.cancelled and self.send_next(t):
+                pass
+
+    def send_next(self, t):
+        if not t.chunks:
+            return False
+        chunk = t.chunks[0]
+        sent = self._send_table_chunk(t, chunk) if isinstance(chunk, TableChunk) else self._send_descriptors(t, chunk)
+        if sent:
+            t.chunks.popleft()
+            t.submitted_since_compute = True
+        return bool(sent)
+
+    def _send_descriptors(self, t, chunk):
+        """A caller-built descriptor chunk, the reference's form: (event, sequence, local, remote, size)."""
+        event, sequence, local, remote, size = chunk
+        return event.query() and self.c.transport.submit(t.tid, sequence, t.peer, local, remote, size)
+
+    def _send_table_chunk(self, t, chunk):
+        transport = self.c.transport
+        behind = {}
+        if self.c._device_ordered():
+            behind["after"] = chunk.event
+        elif not chunk.event.query():
+            return False
+        riders = [chunk.hidden] if chunk.hidden is not None else []
+        if chunk.start >= chunk.end:  # nothing but the hidden row
+            here, there = transport.info["device"], transport.peers[t.peer]["device"]
+            return transport.submit(t.tid, chunk.sequence, t.peer, [(s, n, here) for s, _, n in riders],
+                                    [(d, n, there) for _, d, n in riders], chunk.size, **behind)
+        where = {}
+        if chunk.planes is not None:
+            where.update(plane_begin=chunk.planes[0], plane_end=chunk.planes[1])
+        if chunk.layers is not None:
+            where.update(layer_begin=chunk.layers[0], layer_end=chunk.layers[1])
+        return transport.submit_tables(t.tid, chunk.sequence, t.peer,
+                                       [(chunk.source_tables, chunk.target_tables, chunk.start, chunk.end)], chunk.size,
+                                       extra=riders, **where, **behind)
+
+    # -- table steps
+
+    def drain(self, t):
+        c = self.c
+        if (t.compute_done and not t.request.compute_released
+                and c.engine.release_transfer_compute(t.request, ready_event=t.last_event)):
+            c.notify("prefill_complete", tid=t.tid, overlaps=t.transfer_overlaps,
+                     boundaries=(t.transfer_boundary_first, t.transfer_boundary_last, t.transfer_boundary_count))
+        self.send_next(t)
+
+    def unwind(self, t):
+        # the staging row may still be read by a queued copy, the KV by the peer: both must be over
+        if not self.c.transport.busy(t.tid) and _fired(t.last_event):
+            self.c._remove(t)
+
+    # -- after everyone has had a turn
+
+    def fill_budget(self, turn):
+        """Further round-robin passes over the live exports while any of them still gets a chunk out."""
+        live = [t for t in turn if t.outgoing and not t.cancelled and t.tid in self.c.transfers]
+        while live:
+            went = [self.send_next(t) for t in live]
+            if True not in went:
+                return
+            live = [t for t in live if t.chunks]
+
+    def settle(self, turn):
+        c = self.c
+        for t in turn:
+            if not t.outgoing or t.cancelled or t.tid not in c.transfers:
+                continue
+            if not t.committed and t.compute_done and not t.chunks:
+                t.committed = True
+                c.notify("commit", tid=t.tid, count=t.next_sequence)
+            if t.committed and t.acknowledged and t.request.compute_released and not c.transport.busy(t.tid):
+                c._remove(t)
+
+
+class Importer:
+    """Incoming side: count arrivals against the announced total, hand the request to the engine, keep the record
+    until the request has left the scheduler."""
+
+    def __init__(self, connector: PDStageConnector):
+        self.c = connector
+        self.table = {
+            Stage.COLLECTING: self.collect,
+            Stage.LANDED: self.watch,
+            Stage.SERVING: self.watch,
+            Stage.ABANDONED: self.abandon,
+        }
+
+    def opened(self, t, *_):
+        c = self.c
+        c.notify("reserved", tid=t.tid, tables=c.cache.plane_block_tables(t.tid), slot=t.slot, cached_tokens=t.cached_tokens)
+
+    def cancelled(self, t):
+        if t.ready:
+            self.c._remove(t)  # every expected write was seen, so no remote writer is left
+
+    def book(self, arrivals):
+        for peer, tid, sequence in arrivals:
+            t = self.c.transfers.get(tid)
             if t is None or t.cancelled:
-                continue  # an old generation must not activate a reused request id
+                continue  # a generation that is gone must not activate whoever reuses its request id
             if t.outgoing or peer != t.peer or type(sequence) is not int or sequence < 0:
                 raise RuntimeError("invalid transfer completion")
             if t.ready and sequence not in t.received:
                 raise RuntimeError("late KV write after decode activation")
             t.received.add(sequence)
 
-    def _advance_outgoing(self, t):
-        if t.cancelled:
-            # The staging row may still be read by a queued copy: wait for local and remote users.
-            if not self.transport.busy(t.tid) and _event_done(t.last_event):
-                self._remove(t)
-            return
-        if (t.compute_done and not t.request.compute_released
-                and self.engine.release_transfer_compute(t.request, ready_event=t.last_event)):
-            self.notify(
-                "prefill_complete", tid=t.tid,
-                boundaries=(t.transfer_boundary_first, t.transfer_boundary_last, t.transfer_boundary_count),
-                overlaps=t.transfer_overlaps,
-            )
-        self._submit_chunk(t)
-
-    def _advance_incoming(self, t):
-        if t.cancelled:
-            if t.ready or t.cancel_confirmed:
-                self._remove(t)
-            return
-        if t.ready:
-            if t.request.request_id not in self.engine.scheduler.requests:
-                self._forget(t)
-            elif not t.active and _phase_name(t.request.phase) != "RECEIVING":
-                self._mark_active(t)
-            return
+    def collect(self, t):
+        c = self.c
         if t.expected is None:
             return
-        if any(seq >= t.expected for seq in t.received):
+        if t.received and max(t.received) >= t.expected:
             raise RuntimeError("unexpected transfer sequence")
-        if len(t.received) == t.expected:
-            if not self.engine.accept_import(t.request, self.hidden[t.slot], cached_tokens=t.cached_tokens):
-                raise RuntimeError("stale import activation")
-            t.ready = True
-            self.notify("received", tid=t.tid)
+        if len(t.received) < t.expected:
+            return
+        if not c.engine.accept_import(t.request, c.hidden[t.slot], cached_tokens=t.cached_tokens):
+            raise RuntimeError("stale import activation")
+        t.ready = True
+        c.notify("received", tid=t.tid)
 
-    def _submit_chunk(self, t):
-        """Put the transfer's next chunk on the wire once its event has fired; True if one went out."""
-        if not t.chunks:
-            return False
-        chunk = t.chunks[0]
-        if isinstance(chunk, TableChunk):
-            ordered = self._device_ordered()
-            if not ordered and not chunk.event.query():
-                return False
-            sent = self._submit_tables(t, chunk, after=chunk.event if ordered else None)
-        else:
-            # a caller-built descriptor chunk: (event, sequence, local, remote, size)
-            event, sequence, local, remote, size = chunk
-            sent = event.query() and self.transport.submit(t.tid, sequence, t.peer, local, remote, size)
-        if not sent:
-            return False
-        t.chunks.popleft()
-        t.submitted_since_compute = True
-        return True
+    def watch(self, t):
+        c = self.c
+        if t.request.request_id not in c.engine.scheduler.requests:
+            c._forget(t)
+        elif not t.active and _phase_name(t.request.phase) != "RECEIVING":
+            c._announce_active(t)
 
-    def _submit_tables(self, t, chunk, after=None):
-        extra = [chunk.hidden] if chunk.hidden is not None else []
-        ordered = {} if after is None else {"after": after}
-        if chunk.start >= chunk.end:  # nothing but the hidden row
-            local = [(s, n, self.transport.info["device"]) for s, _, n in extra]
-            remote = [(d, n, self.transport.peers[t.peer]["device"]) for _, d, n in extra]
-            return self.transport.submit(t.tid, chunk.sequence, t.peer, local, remote, chunk.size, **ordered)
-        requests = [(chunk.source_tables, chunk.target_tables, chunk.start, chunk.end)]
-        return self.transport.submit_tables(t.tid, chunk.sequence, t.peer, requests, chunk.size, extra=extra, **ordered)
+    def abandon(self, t):
+        if t.ready or t.cancel_confirmed:
+            self.c._remove(t)

