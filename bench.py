@@ -555,7 +555,10 @@ def run_single(args):
 # ------------------------------------------------------------------------------- other measurements
 
 
-def _timed(fn, reps=7, warm=2):
+def _timed(fn, reps=5, warm=2, inner=8):
+    """Median device time of one ``fn()`` launch. ``inner`` launches are queued back to back behind a short
+    sleep kernel, so the GPU is never waiting for the host: a Python wrapper takes tens of microseconds per call,
+    which would otherwise be billed to a kernel that runs for a hundred."""
     import torch
 
     for _ in range(warm):
@@ -564,11 +567,13 @@ def _timed(fn, reps=7, warm=2):
     out = []
     for _ in range(reps):
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda._sleep(600_000)
         a.record()
-        fn()
+        for _ in range(inner):
+            fn()
         b.record()
         torch.cuda.synchronize()
-        out.append(a.elapsed_time(b))
+        out.append(a.elapsed_time(b) / inner)
     return statistics.median(out)
 
 
@@ -576,7 +581,8 @@ def suite_kernels(args):
     """Every kernel of the library other than the headline handoff, on one GPU: one JSON line each.
 
     Bytes are the algorithmic bytes a kernel must move (read + written); ``frac`` is that rate over the HBM
-    copy peak. Inputs are far larger than L2, timings are CUDA events (median of 7 after 2 warm-ups).
+    copy peak. Inputs are far larger than L2; timings are CUDA events around eight back-to-back launches
+    (median of 5 such groups after 2 warm-ups).
     """
     import numpy as np
     import torch

@@ -34,8 +34,12 @@ def no_cuda(monkeypatch):
 
 
 class Worker:
-    def __init__(self, role, config, lane, *, blocks=64, fp8=False, seed=0, device="cpu", direction="push"):
-        self.pool = KVPool(3, 2, 8, blocks, 4, 2, device=device, kv_cache_dtype="fp8_e4m3" if fp8 else "auto")
+    """One stage worker: pool, engine stand-in (or the real ``TransferStage``), transport, connector."""
+
+    def __init__(self, role, config, lane, *, blocks=64, fp8=False, seed=0, device="cpu", direction="push",
+                 stage=False, prefix_caching=False, shape=(3, 2, 8), page=4, planes=2, hidden_size=16):
+        self.pool = KVPool(*shape, blocks, page, planes, device=device, kv_cache_dtype="fp8_e4m3" if fp8 else "auto",
+                           enable_prefix_caching=prefix_caching)
         gen = torch.Generator().manual_seed(seed)
         for t in (self.pool.key_cache, self.pool.value_cache):
             raw = t.view(torch.uint8)
@@ -46,9 +50,16 @@ class Worker:
         import random
 
         random.Random(seed).shuffle(self.pool._free_blocks)
-        self.engine = FakeEngine(role, self.pool)
+        if stage:
+            from vllm_rlt_b200.core.admission import StageSettings, TransferStage
+
+            self.pool.layout, self.pool.attention_info = "last_exited", {"backend": "torch"}
+            self.engine = TransferStage(role, self.pool, settings=StageSettings(max_num_seqs=4, prefill_chunk_size=2 * page),
+                                        hidden_size=hidden_size)
+        else:
+            self.engine = FakeEngine(role, self.pool, hidden_size=hidden_size)
         self.messages = []
-        hidden = torch.zeros(6, 16, device=device)
+        hidden = torch.zeros(6, hidden_size, device=device)
         backend = FakeBackend() if device == "cpu" else None
         self.transport = B200Transport(f"{role}-0", self.pool, hidden, config, backend=backend, lane=lane, direction=direction)
         self.connector = PDStageConnector(self.engine, hidden, self.transport, config,
@@ -350,28 +361,12 @@ def test_decode_side_prefix_hit_travels_with_the_reservation_and_is_skipped_by_t
     """The real admission hook on both sides: D imported a prompt earlier and cached its pages; a second prompt that
     shares two pages is reserved with cached_tokens = 8, the source skips those tokens, bytes_sent drops by the prefix
     and the shared blocks keep their bytes."""
-    from vllm_rlt_b200.core.admission import StageSettings, TransferStage
-
     config = PDConfig()
-
-    def worker(role, lane, seed, **pool_kw):
-        w = Worker(role, config, lane, seed=seed, direction=direction)
-        w.pool = KVPool(3, 2, 8, 64, 4, 2, device="cpu", **pool_kw)
-        gen = torch.Generator().manual_seed(seed)
-        for t in (w.pool.key_cache, w.pool.value_cache):
-            raw = t.view(torch.uint8)
-            raw.copy_(torch.randint(0, 256, raw.shape, dtype=torch.uint8, generator=gen) if role == "prefill"
-                      else torch.full(raw.shape, 0xA5, dtype=torch.uint8))
-        w.pool.layout, w.pool.attention_info = "last_exited", {"backend": "torch"}
-        w.engine = TransferStage(role, w.pool, settings=StageSettings(max_num_seqs=4, prefill_chunk_size=8))
-        hidden = torch.zeros(6, 16)
-        w.transport.close()
-        w.transport = B200Transport(f"{role}-0", w.pool, hidden, config, backend=FakeBackend(), lane=lane, direction=direction)
-        w.connector = PDStageConnector(w.engine, hidden, w.transport, config,
-                                       notify=lambda kind, **f: w.messages.append(dict(kind=kind, **f)))
-        return w
-
-    p, d = worker("prefill", 0, 1), worker("decode", 1, 2, enable_prefix_caching=True)
+    p = Worker("prefill", config, 0, seed=1, direction=direction, stage=True)
+    d = Worker("decode", config, 1, seed=2, direction=direction, stage=True, prefix_caching=True)
+    # a fresh pool hands out ascending block ids, which makes the shared blocks easy to recognise below
+    for w in (p, d):
+        w.pool._free_blocks.sort(reverse=True)
     assert p.connector.command(dict(kind="connect", peers=[d.transport.info]))
     assert d.connector.command(dict(kind="connect", peers=[p.transport.info]))
 

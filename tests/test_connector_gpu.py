@@ -11,7 +11,7 @@ from types import SimpleNamespace
 import pytest
 import torch
 
-from tests.test_connector_cpu import Params, Worker, pool_rows
+from tests.test_connector_cpu import DIRECTIONS, Params, Worker, pool_rows
 
 pytestmark = pytest.mark.gpu
 
@@ -24,14 +24,15 @@ def pump(p, d, until, limit=20.0):
     assert until()
 
 
+@pytest.mark.parametrize("direction", DIRECTIONS)
 @pytest.mark.parametrize("fp8", [False, True])
-def test_handoff_through_connector_transport_and_kernels(fp8):
+def test_handoff_through_connector_transport_and_kernels(fp8, direction):
     from vllm_rlt_b200.pd.config import PDConfig
 
     per_token = 2 * 3 * (2 * 8 * (1 if fp8 else 2) + (2 * 4 if fp8 else 0)) * 2
     config = PDConfig(transfer_chunk_bytes=5 * per_token + 100, max_inflight_bytes=16 * per_token)
-    p = Worker("prefill", config, 0, seed=1, fp8=fp8, device="cuda:0")
-    d = Worker("decode", config, 1, seed=2, fp8=fp8, device="cuda:0")
+    p = Worker("prefill", config, 0, seed=1, fp8=fp8, device="cuda:0", direction=direction)
+    d = Worker("decode", config, 1, seed=2, fp8=fp8, device="cuda:0", direction=direction)
     p.connector.command(dict(kind="connect", peers=[d.transport.info]))
     d.connector.command(dict(kind="connect", peers=[p.transport.info]))
     tokens = 23
@@ -77,7 +78,8 @@ def test_handoff_through_connector_transport_and_kernels(fp8):
     d.connector.close()
 
 
-def test_chunks_leave_behind_the_producer_event_without_another_progress_pass():
+@pytest.mark.parametrize("direction", DIRECTIONS)
+def test_chunks_leave_behind_the_producer_event_without_another_progress_pass(direction):
     """The reference submits a chunk only when a later ``progress()`` pass finds its event fired (the commit tail,
     vllm_rlt/pd/config.py:10-15). Here the copies are queued at once behind the event on the device: the decode
     side receives every notification although the prefill worker's host never runs ``progress()`` again."""
@@ -85,8 +87,8 @@ def test_chunks_leave_behind_the_producer_event_without_another_progress_pass():
 
     per_token = 2 * 3 * (2 * 8 * 2) * 2
     config = PDConfig(transfer_chunk_bytes=6 * per_token, max_inflight_bytes=64 * per_token)
-    p = Worker("prefill", config, 0, seed=1, device="cuda:0")
-    d = Worker("decode", config, 1, seed=2, device="cuda:0")
+    p = Worker("prefill", config, 0, seed=1, device="cuda:0", direction=direction)
+    d = Worker("decode", config, 1, seed=2, device="cuda:0", direction=direction)
     p.connector.command(dict(kind="connect", peers=[d.transport.info]))
     d.connector.command(dict(kind="connect", peers=[p.transport.info]))
     tokens = 20
@@ -129,3 +131,136 @@ def test_chunks_leave_behind_the_producer_event_without_another_progress_pass():
     d.connector.output_finished("req")
     p.connector.close()
     d.connector.close()
+
+
+def oracle_of(worker, base):
+    """An ``OraclePool`` holding the same bytes and block tables as a worker's device pool."""
+    from oracle import handoff_oracle as ho
+
+    pool = worker.pool
+    o = ho.OraclePool(pool.num_layers, pool.num_kv_heads, pool.head_dim, pool.num_blocks, pool.block_size, pool.storage_depths,
+                      element=2, base=base)
+    o.key.data[...] = pool.key_cache.view(torch.uint8).cpu().numpy().reshape(o.key.data.shape)
+    o.value.data[...] = pool.value_cache.view(torch.uint8).cpu().numpy().reshape(o.value.data.shape)
+    return o
+
+
+def device_bytes(pool):
+    return [t.contiguous().view(torch.uint8).reshape(-1).cpu().numpy() for t in (pool.key_cache, pool.value_cache)]
+
+
+@pytest.mark.parametrize("direction", DIRECTIONS)
+def test_layers_reported_by_the_producer_stream_through_the_connector_and_the_tail_is_one_slice(direction):
+    """A stand-in model runner reports every (plane, layer) as it "writes" it (a timed sleep per layer on the compute
+    stream). Slices leave behind each report's event while later layers still run; when the last layer's report is in,
+    one slice per plane is all that is left, and the destination pool equals the oracle's byte for byte."""
+    import numpy as np
+
+    from oracle import handoff_oracle as ho
+    from vllm_rlt_b200.pd.config import PDConfig
+
+    config = PDConfig()
+    shape = dict(shape=(8, 4, 64), page=16, planes=2, blocks=48)
+    p = Worker("prefill", config, 0, seed=1, device="cuda:0", direction=direction, **shape)
+    d = Worker("decode", config, 1, seed=2, device="cuda:0", direction=direction, **shape)
+    p.connector.command(dict(kind="connect", peers=[d.transport.info]))
+    d.connector.command(dict(kind="connect", peers=[p.transport.info]))
+    tokens = 70
+    d.connector.command(dict(kind="reserve", tid="req", tokens=list(range(tokens)), params=Params(), peer="prefill-0"))
+    (reserved,) = d.take("reserved")
+    p.connector.command(dict(kind="prefill", tid="req", tokens=list(range(tokens)), params=Params(), peer="decode-0",
+                             tables=reserved["tables"], slot=reserved["slot"], cached_tokens=0))
+    request = p.engine.scheduler.requests["req"]
+    P, D = oracle_of(p, 1 << 30), oracle_of(d, 1 << 40)
+    ho.handoff_rows(P, D, p.pool.plane_block_tables("req"), reserved["tables"], 0, tokens)
+    p.connector.stream_layers = 3
+    compute = torch.cuda.Stream()
+    transfer = p.connector.transfers["req"]
+    launched = []
+    with torch.cuda.stream(compute):
+        for plane in range(2):
+            for layer in range(8):
+                torch.cuda._sleep(int(0.004 * 1.9e9))  # one layer of "prefill" at this depth
+                event = torch.cuda.Event()
+                event.record(compute)
+                launched.append(p.connector.layer_written(request, plane=plane, layer=layer, event=event, start=0, end=tokens))
+        end_of_compute = torch.cuda.Event()
+        end_of_compute.record(compute)
+    # layers 0-2, 3-5 and the last group 6-7 of either plane: six slices, the last of them queued with the last layer
+    assert launched == [False, False, True, False, False, True, False, True] * 2 and transfer.next_sequence == 6
+    assert not transfer.chunks  # each slice was handed to the transport at once, behind its event
+    request.num_prefilled_tokens, request.hidden_state = tokens, torch.full((16,), 2.0, device="cuda:0")
+    p.connector.prefill_submitted(request, phase="PREFILLING_RECURRENT", start=0,
+                                  progress=SimpleNamespace(chunk_complete=True, prompt_complete=True),
+                                  event=end_of_compute, stream=compute)
+    assert transfer.next_sequence == 7  # nothing of the KV was left for the end of the step: only the hidden row
+    pump(p, d, lambda: bool([m for m in p.messages if m["kind"] == "commit"]))
+    assert p.take("commit") == [dict(kind="commit", tid="req", count=7)]
+    d.connector.command(dict(kind="commit", tid="req", count=7))
+    pump(p, d, lambda: bool([m for m in d.messages if m["kind"] == "received"]))
+    torch.cuda.synchronize()
+    for got, want in zip(device_bytes(d.pool), (D.key.data.reshape(-1), D.value.data.reshape(-1))):
+        assert np.array_equal(got, want)
+    assert torch.equal(d.engine.imported["req"].cpu(), torch.full((16,), 2.0))
+    d.engine.admit("req")
+    p.connector.command(dict(kind="ack", tid="req"))
+    pump(p, d, lambda: not p.connector.transfers)
+    del d.engine.scheduler.requests["req"]
+    d.connector.output_finished("req")
+    per_token = 2 * 8 * 4 * 64 * 2 * 2
+    assert p.connector.close()["bytes_sent"] == tokens * per_token + 16 * 4
+    d.connector.close()
+
+
+@pytest.mark.parametrize("direction", DIRECTIONS)
+def test_a_prefix_resident_on_the_decode_side_is_reserved_skipped_and_left_untouched(direction):
+    """The decode-side reservation hook end to end on the device (mirrors tests/test_pd.py:626-687 and
+    tests/test_stage_engine.py:595-648 of the reference): D imports a prompt, which publishes its pages; a second
+    prompt sharing 4 pages is reserved with ``cached_tokens`` = 64 on the shared physical blocks, P starts at token 64,
+    ``bytes_sent`` is smaller by the prefix, the shared blocks keep their bytes and the whole pool equals the oracle's."""
+    import numpy as np
+
+    from oracle import handoff_oracle as ho
+    from vllm_rlt_b200.pd.config import PDConfig
+
+    config = PDConfig()
+    shape = dict(shape=(4, 4, 64), page=16, planes=2, blocks=64, stage=True)
+    p = Worker("prefill", config, 0, seed=1, device="cuda:0", direction=direction, **shape)
+    d = Worker("decode", config, 1, seed=2, device="cuda:0", direction=direction, prefix_caching=True, **shape)
+    p.connector.command(dict(kind="connect", peers=[d.transport.info]))
+    d.connector.command(dict(kind="connect", peers=[p.transport.info]))
+    P, D = oracle_of(p, 1 << 30), oracle_of(d, 1 << 40)
+    per_token = 2 * 4 * 4 * 64 * 2 * 2
+
+    def run(tid, prompt):
+        d.connector.command(dict(kind="reserve", tid=tid, tokens=prompt, params=Params(), peer="prefill-0"))
+        (reserved,) = d.take("reserved")
+        p.connector.command(dict(kind="prefill", tid=tid, tokens=prompt, params=Params(), peer="decode-0",
+                                 tables=reserved["tables"], slot=reserved["slot"], cached_tokens=reserved["cached_tokens"]))
+        request = p.engine.requests[tid]
+        p.engine.begin_prefill(request)
+        p.engine.end_prefill(request, torch.full((16,), 1.0, device="cuda:0"))
+        event = torch.cuda.Event()
+        event.record()
+        ho.handoff_rows(P, D, p.pool.plane_block_tables(tid), reserved["tables"], reserved["cached_tokens"], len(prompt))
+        p.connector.prefill_submitted(request, phase="PREFILLING_RECURRENT", start=0,
+                                      progress=SimpleNamespace(chunk_complete=True, prompt_complete=True), event=event, stream=None)
+        pump(p, d, lambda: bool([m for m in p.messages if m["kind"] == "commit"]))
+        (commit,) = p.take("commit")
+        d.connector.command(dict(kind="commit", tid=tid, count=commit["count"]))
+        pump(p, d, lambda: bool([m for m in d.messages if m["kind"] == "received"]))
+        d.take("received")
+        p.connector.command(dict(kind="ack", tid=tid))
+        pump(p, d, lambda: tid not in p.connector.transfers)
+        return reserved
+
+    first = run("one", list(range(1, 101)))          # 100 tokens: pages 0..5 become cached on D
+    assert first["cached_tokens"] == 0 and p.transport.bytes_sent == 100 * per_token + 64
+    second = run("two", list(range(1, 65)) + list(range(500, 540)))   # shares 4 whole pages = 64 tokens
+    assert second["cached_tokens"] == 64
+    assert [list(t[:4]) for t in second["tables"]] == [list(t[:4]) for t in first["tables"]]
+    assert p.transport.bytes_sent == (100 + 104 - 64) * per_token + 2 * 64
+    assert d.pool._allocations["two"].imported == 104 and d.engine.requests["two"].num_prefilled_tokens == 104
+    torch.cuda.synchronize()
+    for got, want in zip(device_bytes(d.pool), (D.key.data.reshape(-1), D.value.data.reshape(-1))):
+        assert np.array_equal(got, want)  # includes the shared blocks: written once, by the first import

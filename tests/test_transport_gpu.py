@@ -164,3 +164,57 @@ def test_notification_is_only_visible_after_the_bytes():
         p.poll()
     p.close()
     d.close()
+
+
+@pytest.mark.parametrize("fp8", [False, True])
+@pytest.mark.parametrize("two_gpus", [False, True])
+def test_offered_chunks_are_pulled_by_the_receiver_and_acknowledged(fp8, two_gpus):
+    """The pull direction of ``submit_tables``: the sender only offers (behind an event), the receiver's GPU reads the
+    sender's pool through peer pointers, reports the chunk when its own launch has finished and acknowledges it."""
+    from vllm_rlt_b200.kernels import kv_handoff as kh
+    from vllm_rlt_b200.pd.config import PDConfig
+    from vllm_rlt_b200.pd.transport import B200Transport
+
+    if two_gpus and torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    dev_p, dev_d = "cuda:0", "cuda:1" if two_gpus else "cuda:0"
+    config = PDConfig(transfer_chunk_bytes=1 << 20, max_inflight_bytes=8 << 20)
+    P = make_pool(dev_p, fp8=fp8, seed=1)
+    D = make_pool(dev_d, fp8=fp8, seed=2, fill=False)
+    requests = [("a", 0, 40), ("b", 5, 16), ("c", 16, 33)]
+    for rid, n in {"a": 40, "b": 16, "c": 33}.items():
+        assert P.allocate(rid, n) and D.reserve_transfer(rid, n) is not None
+    hidden_p = torch.arange(4 * 64, dtype=torch.bfloat16, device=dev_p).reshape(4, 64)
+    hidden_d = torch.zeros(4, 64, dtype=torch.bfloat16, device=dev_d)
+    p = B200Transport("p0", P, hidden_p, config, direction="pull")
+    d = B200Transport("d0", D, hidden_d, config, lane=9, direction="pull")
+    p.connect(d.info)
+    d.connect(p.info)
+    want = expected_destination(P, D, requests)
+    launches = kh.kernel_launches()
+    with torch.cuda.device(dev_p):
+        producer = torch.cuda.Stream()
+        with torch.cuda.stream(producer):
+            torch.cuda._sleep(int(0.05 * 1.9e9))  # the KV is "written" 50 ms from now
+            ready = torch.cuda.Event()
+            ready.record(producer)
+    sent = 0
+    hb = p.info["hidden_bytes"]
+    for seq, (rid, start, end) in enumerate(requests):
+        size = kh.PoolView.from_cache(P).payload_bytes(end - start, 2) + hb
+        extra = [(p.info["hidden_ptr"] + 1 * hb, d.info["hidden_ptr"] + 2 * hb, hb)]
+        assert p.submit_tables(rid, seq, "d0", [(P.plane_block_tables(rid), D.plane_block_tables(rid), start, end)], size,
+                               extra=extra, after=ready)
+        sent += size
+    assert d.poll() == ([], []) and not ready.query()  # nothing is offered before the producer's event has fired
+    assert all(p.busy(rid) for rid, _, _ in requests)
+    notes = drain(p, d, len(requests))
+    assert sorted((a, t, s) for a, t, s in notes) == [("p0", "a", 0), ("p0", "b", 1), ("p0", "c", 2)]
+    assert p.bytes_sent == sent == d.bytes_received and p.transfers == 3 and p.inflight_bytes == 0 and not d.reading
+    assert kh.kernel_launches() - launches == 3 * 3  # per chunk: the offer's post on P; the handoff and the hidden copy on D
+    torch.cuda.synchronize(dev_d)
+    for got, exp in zip(tensors(D), want):
+        assert torch.equal(got.view(torch.uint8), exp.view(torch.uint8))
+    assert torch.equal(hidden_d[2].cpu(), hidden_p[1].cpu()) and int(hidden_d[[0, 1, 3]].abs().sum()) == 0
+    d.close()  # the reader unmaps the source pool before its owner lets go of it
+    p.close()

@@ -60,8 +60,9 @@ def _decode_worker(conn, fp8):
         raise
 
 
+@pytest.mark.parametrize("direction", ["push", "pull"])
 @pytest.mark.parametrize("fp8", [False, True])
-def test_cross_process_write_and_notification(fp8):
+def test_cross_process_write_and_notification(fp8, direction):
     from oracle import handoff_oracle as ho
     from vllm_rlt_b200.pd.config import PDConfig
     from vllm_rlt_b200.pd.transport import B200Transport
@@ -80,7 +81,8 @@ def test_cross_process_write_and_notification(fp8):
         assert "error" not in hello, hello
         hidden = torch.arange(4 * 64, dtype=torch.bfloat16, device="cuda:0").reshape(4, 64)
         cfg = PDConfig(transfer_chunk_bytes=1 << 20, max_transfer_descriptors=5)
-        p = B200Transport("p0", pool, hidden, cfg)
+        # "b" goes by tables: pushed by this process's GPU, or offered and pulled by the decode worker's
+        p = B200Transport("p0", pool, hidden, cfg, direction=direction)
         p.connect(hello["info"])
         parent.send(p.info)
         seq = 0
