@@ -541,6 +541,7 @@ def run_single(args):
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": batch.metadata_bytes,
                 "d2h_bytes_per_step": 16, "ms_per_step": statistics.mean(e2e_times) * 1e3,
                 "note": "KV pools are device-resident by the API's nature; host inputs are tables, ranges and exit planes"},
+        "p50_latency_ms": statistics.median(lat),
         "latency_ms": {"p50": statistics.median(lat), "max": max(lat), "min": min(lat),
                        "what": "one launch per request, CUDA events, intra-device",
                        "last_layer_slice_p50": statistics.median(tail),

@@ -216,7 +216,12 @@ RLT_API int rlt_kv_pack(const RltPool* src, const RltBatch* batch, const RltOpti
  *
  * The first call on each device looks up the array's device address (one
  * runtime query, with that device current); make that first call before
- * starting any stream capture. All calls on a device share the one array and
+ * starting any stream capture. It is also the latest moment at which the
+ * array's 4.2 MB are placed on that device: CUDA loads a library's device
+ * image lazily, at the first use of one of its kernels or symbols there. A
+ * worker that hands all remaining HBM to its pool must therefore make this
+ * first call (or any launch of this library) BEFORE the pool takes the memory,
+ * or the placement itself can fail. All calls on a device share the one array and
  * it keeps the previous call's contents; every word a call reads is written
  * by that call first, so nothing has to be cleared, but two calls that overlap
  * on the GPU (different streams, no ordering between them) race on it: order

@@ -264,3 +264,5 @@ def test_a_prefix_resident_on_the_decode_side_is_reserved_skipped_and_left_untou
     torch.cuda.synchronize()
     for got, want in zip(device_bytes(d.pool), (D.key.data.reshape(-1), D.value.data.reshape(-1))):
         assert np.array_equal(got, want)  # includes the shared blocks: written once, by the first import
+    d.transport.close()  # the reader unmaps before the owner lets go (the imports stay reserved on D)
+    p.transport.close()

@@ -37,6 +37,7 @@ struct FinalizeParams {
   int table_width, num_requests;
   const int* rows;                // [n][3]: request index, exit plane, token position
   int n;
+  int group_rows;                 // rows of one page taken together: at most kGroupRows, fewer for very long rows
   int* status;
 };
 
@@ -71,18 +72,23 @@ __device__ __forceinline__ void copy_layers(const char* src, char* dst, const in
 constexpr int kFanPlanes = 64;
 
 // ---------------------------------------------------------------------------------------------
-// finalize_fan_kernel: one load, one store per deeper plane, work split by cost.
+// finalize_fan_kernel: one load, one store per deeper plane; work split by cost; rows of one page move together.
 //
-// A row that exits at plane e costs (1 + deeper planes) row copies: nothing for the deepest plane, four for plane 0
-// of a four-plane pool. Handing rows to CTAs round-robin leaves the CTAs with sums of a few dozen such costs, which
-// differ by +-10 %; the early finishers idle while HBM runs below its rate. So every CTA first derives the same
-// exclusive scan of the row costs (each thread sums a contiguous slice of rows; one block scan of the 256 sums),
-// cuts the total into gridDim.x equal shares and takes the contiguous run of rows - down to a fraction of the first
-// and last row, in whole (tensor, layer) pieces - that makes up its share. No atomics, no scratch memory, and two
-// neighbouring CTAs compute their common boundary from the same numbers.
+// Cost. A row that exits at plane e costs (1 + deeper planes) row copies: nothing for the deepest plane, four for
+// plane 0 of a four-plane pool. Every CTA derives the same exclusive scan of the row costs (each thread sums a
+// contiguous slice of rows; one block scan of the 256 sums), cuts the total into gridDim.x equal shares and takes
+// the contiguous run of rows - down to a fraction of the first and last row, in whole (tensor, layer) pieces - that
+// makes up its share. No atomics, no scratch memory, and two neighbouring CTAs compute their common cut from the
+// same numbers.
 //
-// Inside its run a CTA walks rows in order, so the next row's block-table entries are fetched before the current
-// row is streamed and the only barrier per row finds them already there.
+// Locality. A row is 24 pieces of 4 KiB that lie 64 KiB apart, so copying row after row sprays DRAM with 4 KiB
+// accesses. Consecutive rows of a batch are usually consecutive tokens of one request, hence rows of one page, and
+// on every deeper plane their copies are neighbours in one block. Rows of a CTA's run that share (request, page) are
+// therefore taken as a group and walked layer by layer, token by token: the stores of one layer to one plane then
+// cover up to block_size * token_bytes contiguous bytes (64 KiB for the Ouro shape). The block-table entries of a
+// group (one per plane, shared by its rows) are fetched while the previous group streams.
+
+constexpr int kGroupRows = 32;  // rows of one page taken together (one warp detects and compacts them)
 
 // (1 + deeper planes) if the row is valid and has deeper planes, else 0. `say`: report an invalid row (one CTA does).
 __device__ __forceinline__ int row_cost(const FinalizeParams& p, int row, bool say) {
@@ -95,41 +101,61 @@ __device__ __forceinline__ int row_cost(const FinalizeParams& p, int row, bool s
   return exit_plane + 1 < p.planes ? p.planes - exit_plane : 0;
 }
 
-// Pieces [a, b) of one region of one row: piece = (K|V, selected layer). Vector i of the flat array belongs to piece
-// a + i / row_vecs. The vector is loaded once and stored to the same in-block offset of every deeper plane whose
-// block is valid (plane_off >= 0).
+// What one group needs while it streams: per plane the byte offset of the page's block (either region), per carried
+// row its exit plane and the byte offset of its token inside a block layer (either region).
+struct GroupTables {
+  long long plane_off[2][kFanPlanes];  // -1: that plane's block id is outside the pool
+  int tok_off[2][kGroupRows];
+  int exit_plane[kGroupRows];
+  int carried;   // rows with something to copy (those are the ones listed above)
+  int rows;      // rows of the batch the group spans, carried or not
+  unsigned magic;  // div_magic(carried), 0 when carried <= 1
+};
+
+// Pieces [a, b) of every carried row of a group, for one region: piece = (K|V, selected layer). The flat vector array
+// is ordered piece, row, vector, so consecutive threads walk consecutive tokens of one layer. Each vector is loaded
+// once from the row's exit plane and stored to the same in-block offset of every deeper plane whose block is valid.
 template <typename T>
-__device__ __forceinline__ void fan_pieces(const FinalizeRegion& rg, const long long* plane_off, int exit_plane, int planes,
-                                           const int* layer_of, int layers, int a, int b) {
-  const int total = (b - a) * rg.row_vecs;
-  const long long src_off = plane_off[exit_plane];
+__device__ __forceinline__ void fan_group(const FinalizeRegion& rg, const GroupTables& gt, int g, int planes,
+                                          const int* layer_of, int layers, int a, int b) {
+  const int carried = gt.carried;
+  const int total = (b - a) * carried * rg.row_vecs;
+  // where vector i lives: (source/destination offset inside a plane's block, row of the group, K|V)
+  auto locate = [&](int i, int* row, int* kv) -> long long {
+    const int q = rg.row_magic ? static_cast<int>(__umulhi(static_cast<unsigned>(i), rg.row_magic)) : i;  // piece x row
+    const int piece_rel = gt.magic ? static_cast<int>(__umulhi(static_cast<unsigned>(q), gt.magic)) : q;
+    const int r = q - piece_rel * carried;
+    const int piece = a + piece_rel;
+    *kv = piece >= layers;
+    *row = r;
+    return layer_of[piece - *kv * layers] * rg.layer_bytes + gt.tok_off[g][r] +
+           static_cast<long long>(i - q * rg.row_vecs) * static_cast<long long>(sizeof(T));
+  };
   for (int base = threadIdx.x; base < total; base += kThreads * kUnroll) {
     T regs[kUnroll];
-    long long at[kUnroll];
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
       const int i = base + u * kThreads;
-      at[u] = -1;
       if (i < total) {
-        const int q = rg.row_magic ? static_cast<int>(__umulhi(static_cast<unsigned>(i), rg.row_magic)) : i;
-        const int piece = a + q;
-        const int kv = piece >= layers;
-        const int slot = piece - kv * layers;
-        // bit 62 carries K|V so that the store loop needs no second table
-        at[u] = layer_of[slot] * rg.layer_bytes + static_cast<long long>(i - q * rg.row_vecs) * static_cast<long long>(sizeof(T));
-        const char* pool = kv ? rg.value : rg.key;
-        regs[u] = ld_stream(reinterpret_cast<const T*>(pool + src_off + at[u]));
-        at[u] |= static_cast<long long>(kv) << 62;
+        int r, kv;
+        const long long at = locate(i, &r, &kv);
+        const long long src = gt.plane_off[g][gt.exit_plane[r]];
+        if (src >= 0) regs[u] = ld_stream(reinterpret_cast<const T*>((kv ? rg.value : rg.key) + src + at));
       }
     }
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
-      if (at[u] >= 0) {
-        char* pool = (at[u] >> 62) ? rg.value : rg.key;
-        const long long in_row = at[u] & ((1ll << 62) - 1);
-        for (int t = exit_plane + 1; t < planes; ++t) {
-          const long long pb = plane_off[t];
-          if (pb >= 0) st_stream(reinterpret_cast<T*>(pool + pb + in_row), regs[u]);
+      const int i = base + u * kThreads;
+      if (i < total) {
+        int r, kv;
+        const long long at = locate(i, &r, &kv);  // recomputed rather than kept live across the loads
+        const int e = gt.exit_plane[r];
+        if (gt.plane_off[g][e] >= 0) {
+          char* pool = kv ? rg.value : rg.key;
+          for (int t = e + 1; t < planes; ++t) {
+            const long long pb = gt.plane_off[g][t];
+            if (pb >= 0) st_stream(reinterpret_cast<T*>(pool + pb + at), regs[u]);
+          }
         }
       }
     }
@@ -142,10 +168,10 @@ __global__ void __launch_bounds__(kThreads, 3) finalize_fan_kernel(const Finaliz
   __shared__ long long slice_start[kThreads + 1];  // cost of all rows before each thread's slice; [kThreads] = total
   __shared__ long long warp_part[kThreads / 32];
   __shared__ int cut_row[2];        // first row of this CTA's share, and the row its share ends in
-  __shared__ long long cut_rem[2];  // cost of that row that lies before the cut
-  // per row, double buffered: byte offset of the token's row in each plane, for either region; -1 = invalid block
-  __shared__ long long plane_off[2][2][kFanPlanes];
+  __shared__ long long cut_rem[2];  // (cost x pieces) of that row that lies before the cut
+  __shared__ GroupTables tables[2];  // double buffered: the next group's are written while this one streams
   const int tid = static_cast<int>(threadIdx.x);
+  const int lane = tid & 31, warp = tid >> 5;
   if (tid == 0) {
     int n = 0;
     for (int layer = 0; layer < p.num_layers; ++layer) {
@@ -160,7 +186,6 @@ __global__ void __launch_bounds__(kThreads, 3) finalize_fan_kernel(const Finaliz
   long long mine = 0;
   for (int i = mine_lo; i < mine_hi; ++i) mine += row_cost(p, i, blockIdx.x == 0);
   {
-    const int lane = tid & 31, warp = tid >> 5;
     long long inc = mine;
 #pragma unroll
     for (int d = 1; d < 32; d <<= 1) {
@@ -207,66 +232,116 @@ __global__ void __launch_bounds__(kThreads, 3) finalize_fan_kernel(const Finaliz
     }
   }
   __syncthreads();
-  const int row_first = cut_row[0], row_last = min(cut_row[1], p.n - 1);
+  // The share: pieces [head_lo, pieces) of row `first` if head_lo > 0, whole rows [whole_lo, whole_hi), and pieces
+  // [0, tail_hi) of row whole_hi if tail_hi > 0. A share inside one row is the head alone, cut at both ends.
+  const int first = cut_row[0], last = cut_row[1];
+  const int head_lo = static_cast<int>(cut_rem[0] / row_cost(p, first, false));
+  const int tail_hi = last < p.n ? static_cast<int>(cut_rem[1] / max(row_cost(p, last, false), 1)) : 0;
+  const bool one_row = first == last;
+  const int whole_lo = first + (head_lo > 0 || one_row ? 1 : 0);
+  const int whole_hi = last;  // exclusive
 
-  // Block-table entry of this thread's plane for `row` (threads exit plane .. planes - 1 take part): the load is
-  // issued here and its value is first used after the current row has been streamed.
-  auto lookup = [&](int row, int* page_offset) -> int {
-    *page_offset = -1;
-    if (row > row_last || tid >= p.planes) return 0;
-    const int request = p.rows[3 * row], exit_plane = p.rows[3 * row + 1], position = p.rows[3 * row + 2];
-    if (request < 0 || request >= p.num_requests || exit_plane < 0 || exit_plane + 1 >= p.planes || position < 0 ||
-        position >= p.table_width * p.block_size || tid < exit_plane)
-      return 0;
-    const int page = position / p.block_size;
-    *page_offset = position - page * p.block_size;
-    return p.tables[(static_cast<long long>(request) * p.planes + tid) * p.table_width + page];
+  // A group starts at row `start`. Its extent: the head and the tail are groups of their own; otherwise up to
+  // kGroupRows consecutive whole rows of the same request and page. `limit` is where it may reach at most.
+  auto limit_of = [&](int start) -> int {
+    if (start < whole_lo || start >= whole_hi) return start + 1;
+    return min(whole_hi, start + p.group_rows);
   };
-  auto publish = [&](int row, int block, int page_offset, long long (*out)[kFanPlanes]) {
-    if (page_offset < 0) return;
-    if (block < 0 || block >= p.num_blocks) {
-      report(p.status, RLT_STATUS_BAD_BLOCK, p.rows[3 * row], p.rows[3 * row + 2] / p.block_size, block);
-      out[0][tid] = out[1][tid] = -1;
+  // Step 1 of fetching a group (before the current one streams): the loads are issued, nothing waits for them.
+  // Threads below `planes` look up the page's block on their plane; warp 0 reads the group's candidate rows.
+  auto fetch = [&](int start, int* block, int* request, int* exit_plane, int* position) {
+    *block = -2;
+    *request = -1;
+    if (start > last || start >= p.n) return;
+    const int r0 = p.rows[3 * start], pos0 = p.rows[3 * start + 2];
+    const bool head_ok = r0 >= 0 && r0 < p.num_requests && pos0 >= 0 && pos0 < p.table_width * p.block_size;
+    if (head_ok && tid < p.planes)
+      *block = p.tables[(static_cast<long long>(r0) * p.planes + tid) * p.table_width + pos0 / p.block_size];
+    if (warp == 0 && start + lane < limit_of(start)) {
+      *request = p.rows[3 * (start + lane)];
+      *exit_plane = p.rows[3 * (start + lane) + 1];
+      *position = p.rows[3 * (start + lane) + 2];
+    }
+  };
+  // Step 2 (after the current group has streamed): write the group's tables. Warp 0 finds how far the run of rows
+  // with the head row's (request, page) goes and compacts the rows that have something to copy.
+  auto publish = [&](int start, GroupTables& out, int block, int request, int exit_plane, int position) {
+    if (start > last || start >= p.n) {
+      if (tid == 0) out.rows = out.carried = 0;
       return;
     }
-    out[0][tid] = block * p.region[0].block_bytes + page_offset * p.region[0].token_bytes;
-    if (p.num_regions == 2) out[1][tid] = block * p.region[1].block_bytes + page_offset * p.region[1].token_bytes;
+    if (tid < p.planes) {
+      long long at0 = -1, at1 = -1;
+      if (block >= 0 && block < p.num_blocks) {
+        at0 = block * p.region[0].block_bytes;
+        if (p.num_regions == 2) at1 = block * p.region[1].block_bytes;
+      } else if (block != -2) {
+        report(p.status, RLT_STATUS_BAD_BLOCK, p.rows[3 * start], p.rows[3 * start + 2] / p.block_size, block);
+      }
+      out.plane_off[0][tid] = at0;
+      out.plane_off[1][tid] = at1;
+    }
+    if (warp == 0) {
+      const int r0 = __shfl_sync(0xffffffffu, request, 0), pos0 = __shfl_sync(0xffffffffu, position, 0);
+      const bool listed = request >= 0 && start + lane < limit_of(start);
+      const bool valid = listed && request < p.num_requests && exit_plane >= 0 && exit_plane < p.planes && position >= 0 &&
+                         position < p.table_width * p.block_size;
+      const bool head_valid = __shfl_sync(0xffffffffu, static_cast<int>(valid), 0) != 0;
+      const bool same = lane == 0 || (head_valid && valid && request == r0 && position / p.block_size == pos0 / p.block_size);
+      const unsigned run = __ballot_sync(0xffffffffu, same);
+      const int rows = run == 0xffffffffu ? 32 : __ffs(~run) - 1;  // leading ones: how far the run goes
+      const bool carry = lane < rows && valid && exit_plane + 1 < p.planes;
+      const unsigned keep = __ballot_sync(0xffffffffu, carry);
+      if (carry) {
+        const int slot = __popc(keep & ((1u << lane) - 1u));
+        const int offset = position % p.block_size;
+        out.exit_plane[slot] = exit_plane;
+        out.tok_off[0][slot] = offset * static_cast<int>(p.region[0].token_bytes);
+        out.tok_off[1][slot] = p.num_regions == 2 ? offset * static_cast<int>(p.region[1].token_bytes) : 0;
+      }
+      if (lane == 0) {
+        const int carried = __popc(keep);
+        out.rows = rows;
+        out.carried = carried;
+        out.magic = carried > 1 ? static_cast<unsigned>((1ull << 32) / carried) + 1u : 0u;
+      }
+    }
   };
 
   int parity = 0;
   {
-    int page_offset;
-    const int block = lookup(row_first, &page_offset);
-    publish(row_first, block, page_offset, plane_off[0]);
+    int block, request, exit_plane = 0, position = 0;
+    fetch(first, &block, &request, &exit_plane, &position);
+    publish(first, tables[0], block, request, exit_plane, position);
   }
   __syncthreads();
-  for (int row = row_first; row <= row_last; ++row, parity ^= 1) {
-    int next_offset;
-    const int next_block = lookup(row + 1, &next_offset);  // in flight while this row streams
-    const int cost = row_cost(p, row, false);
-    if (cost > 0) {
-      // whole (tensor, layer) pieces of this row that fall inside the share
-      const int lo = row == row_first ? static_cast<int>(cut_rem[0] / cost) : 0;
-      const int hi = row == cut_row[1] ? static_cast<int>(cut_rem[1] / cost) : pieces;
-      const int exit_plane = p.planes - cost;
-      if (plane_off[parity][0][exit_plane] >= 0) {  // the source block is valid
-        for (int g = 0; g < p.num_regions; ++g) {
-          const int a = max(lo - g * pieces_per_region, 0), b = min(hi - g * pieces_per_region, pieces_per_region);
-          if (a >= b) continue;
-          const FinalizeRegion& rg = p.region[g];
-          const long long* off = plane_off[parity][g];
-          if (rg.vec_bytes == 16) {
-            fan_pieces<uint4>(rg, off, exit_plane, p.planes, layer_of, layers, a, b);
-          } else if (rg.vec_bytes == 4) {
-            fan_pieces<uint32_t>(rg, off, exit_plane, p.planes, layer_of, layers, a, b);
-          } else {
-            fan_pieces<uint8_t>(rg, off, exit_plane, p.planes, layer_of, layers, a, b);
-          }
+  for (int start = first; start <= last && start < p.n;) {
+    const GroupTables& gt = tables[parity];
+    const int next = start + max(gt.rows, 1);
+    int block, request, exit_plane = 0, position = 0;
+    fetch(next, &block, &request, &exit_plane, &position);  // in flight while this group streams
+    if (gt.carried > 0) {
+      // pieces of each row that fall inside the share: everything, except for the head and the tail
+      int lo = 0, hi = pieces;
+      if (start == first && (head_lo > 0 || one_row)) lo = head_lo;
+      if (start == last) hi = tail_hi;
+      for (int g = 0; g < p.num_regions; ++g) {
+        const int a = max(lo - g * pieces_per_region, 0), b = min(hi - g * pieces_per_region, pieces_per_region);
+        if (a >= b) continue;
+        const FinalizeRegion& rg = p.region[g];
+        if (rg.vec_bytes == 16) {
+          fan_group<uint4>(rg, gt, g, p.planes, layer_of, layers, a, b);
+        } else if (rg.vec_bytes == 4) {
+          fan_group<uint32_t>(rg, gt, g, p.planes, layer_of, layers, a, b);
+        } else {
+          fan_group<uint8_t>(rg, gt, g, p.planes, layer_of, layers, a, b);
         }
       }
     }
-    publish(row + 1, next_block, next_offset, plane_off[parity ^ 1]);
-    __syncthreads();  // the next row's offsets are visible; this row's buffer is free for the row after
+    publish(next, tables[parity ^ 1], block, request, exit_plane, position);
+    __syncthreads();  // the next group's tables are visible; this group's buffer is free for the one after
+    parity ^= 1;
+    start = next;
   }
 }
 
@@ -336,6 +411,7 @@ int rlt_kv_finalize(const RltPool* pool, const int32_t* tables, int32_t num_requ
     return RLT_E_LIMIT;
   if (pool->num_planes == 1) return RLT_OK;  // a SHARED pool has nothing deeper to fill
   rlt::FinalizeParams p{};
+  int group_rows = 32;
   p.num_regions = pool->scales.key != nullptr ? 2 : 1;
   if (p.num_regions == 2 && pool->scales.value == nullptr) return RLT_E_INVALID;
   for (int g = 0; g < p.num_regions; ++g) {
@@ -354,9 +430,13 @@ int rlt_kv_finalize(const RltPool* pool, const int32_t* tables, int32_t num_requ
     out.vec_bytes = (bits & 15u) == 0 ? 16 : (bits & 3u) == 0 ? 4 : 1;
     out.row_vecs = static_cast<int>(r.token_bytes / out.vec_bytes);
     out.row_magic = out.row_vecs == 1 ? 0u : rlt::div_magic(static_cast<uint32_t>(out.row_vecs));
-    // the flat index (selected layers x row vectors) times row_vecs must stay below 2^32 for the multiplier split
-    if (64ll * out.row_vecs * out.row_vecs >= (1ll << 32)) return RLT_E_LIMIT;
+    // the flat index (pieces x rows of a group x row vectors) times row_vecs must stay below 2^32 for the
+    // multiplier split: long rows get smaller groups
+    if (128ll * out.row_vecs * out.row_vecs >= (1ll << 32)) return RLT_E_LIMIT;
+    const long long fit = ((1ll << 32) - 1) / (128ll * out.row_vecs * out.row_vecs);
+    if (fit < group_rows) group_rows = static_cast<int>(fit);
   }
+  p.group_rows = group_rows;
   p.planes = pool->num_planes;
   p.block_size = pool->block_size;
   p.num_blocks = pool->num_blocks;

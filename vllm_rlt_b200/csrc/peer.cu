@@ -79,7 +79,16 @@ int rlt_ipc_close(void* base) {
 
 int rlt_host_register(void* host, size_t bytes, void** device_ptr) {
   if (host == nullptr || bytes == 0 || device_ptr == nullptr) return RLT_E_INVALID;
-  RLT_CUDA_TRY(cudaHostRegister(host, bytes, cudaHostRegisterPortable | cudaHostRegisterMapped));
+  cudaError_t reg = cudaHostRegister(host, bytes, cudaHostRegisterPortable | cudaHostRegisterMapped);
+  if (reg == cudaErrorHostMemoryAlreadyRegistered) {
+    // A mapping that was unmapped without being unregistered leaves its registration behind, and a new mapping
+    // may land on the same addresses: drop the stale registration and register what is there now.
+    (void)cudaGetLastError();
+    (void)cudaHostUnregister(host);
+    (void)cudaGetLastError();
+    reg = cudaHostRegister(host, bytes, cudaHostRegisterPortable | cudaHostRegisterMapped);
+  }
+  RLT_CUDA_TRY(reg);
   const cudaError_t e = cudaHostGetDevicePointer(device_ptr, host, 0);
   if (e != cudaSuccess) {
     (void)cudaHostUnregister(host);

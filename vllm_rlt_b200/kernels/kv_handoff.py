@@ -294,6 +294,47 @@ class HandoffBatch:
         self.has_exit = exits is not None
         self.exit_count = exit_count
 
+    @classmethod
+    def from_device(cls, src_tables, dst_tables, tok_begin, tok_end, *, block_size: int, exit_planes=None,
+                    exit_offsets=None) -> "HandoffBatch":
+        """A batch whose arrays already sit in device memory, for instance block tables and exit planes that a peer
+        sent over NCCL: nothing is staged, copied or read back. ``src_tables`` / ``dst_tables`` are contiguous int32
+        ``[requests, planes, width]`` (either may be None), ``tok_begin`` / ``tok_end`` int32 ``[requests]``,
+        ``exit_planes`` int32 with one entry per token and ``exit_offsets`` int64 ``[requests]``. No host-side
+        validation is possible; the kernels check ranges, block ids and exit planes and report through the status words.
+        """
+        tables = src_tables if src_tables is not None else dst_tables
+        if tables is None or tables.dim() != 3:
+            raise ValueError("block tables must be [requests, planes, width]")
+        n, _, width = tables.shape
+        if not 1 <= n <= _lib.MAX_REQUESTS:
+            raise ValueError(f"a handoff batch holds 1 to {_lib.MAX_REQUESTS} requests")
+        checks = [(src_tables, torch.int32, "src_tables"), (dst_tables, torch.int32, "dst_tables"),
+                  (tok_begin, torch.int32, "tok_begin"), (tok_end, torch.int32, "tok_end"),
+                  (exit_planes, torch.int32, "exit_planes"), (exit_offsets, torch.int64, "exit_offsets")]
+        for t, dtype, name in checks:
+            if t is not None and (not t.is_cuda or t.dtype != dtype or not t.is_contiguous()):
+                raise ValueError(f"{name} must be a contiguous CUDA {dtype} tensor")
+        if src_tables is not None and dst_tables is not None and (src_tables.shape[0] != n or dst_tables.shape[0] != n or
+                                                                  src_tables.shape[2] != dst_tables.shape[2]):
+            raise ValueError("source and destination tables must agree in requests and width")
+        if tok_begin.numel() != n or tok_end.numel() != n:
+            raise ValueError("one token range per request is required")
+        if (exit_planes is None) != (exit_offsets is None) or (exit_offsets is not None and exit_offsets.numel() != n):
+            raise ValueError("exit_planes and exit_offsets come as a pair, one offset per request")
+        self = cls.__new__(cls)
+        self.num_requests, self.table_width, self.block_size = n, width, block_size
+        self.ranges, self.total_tokens = None, None
+        self.src_planes = src_tables.shape[1] if src_tables is not None else 0
+        self.dst_planes = dst_tables.shape[1] if dst_tables is not None else 0
+        self.metadata_bytes = 0
+        self._dev = (src_tables, dst_tables, tok_begin, tok_end, exit_planes, exit_offsets)  # keeps them alive
+        names = ("src_tables", "dst_tables", "tok_begin", "tok_end", "exit_planes", "exit_offsets")
+        self._ptr = {name: t.data_ptr() for name, t in zip(names, self._dev) if t is not None}
+        self.has_exit = exit_planes is not None
+        self.exit_count = exit_planes.numel() if exit_planes is not None else 0
+        return self
+
     def as_struct(self) -> _lib.RltBatch:
         g = self._ptr.get
         return _lib.RltBatch(

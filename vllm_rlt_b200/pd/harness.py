@@ -444,6 +444,7 @@ def run_multi(args, rank: int, world: int) -> None:
             "e2e": {"value": total_payload / float(e2e_s.item()) / 1e9, "unit": bench.UNIT,
                     "h2d_bytes_per_step": sum(e["batch"].metadata_bytes for e in edges), "d2h_bytes_per_step": 16,
                     "ms_per_step": float(e2e_s.item()) * 1e3},
+            "p50_latency_ms": statistics.median(lat),
             "latency_ms": {"p50": statistics.median(lat), "max": max(lat), "min": min(lat),
                            "what": "rank 0, one launch + completion flag per request, CUDA events on the prefill stream"},
             "gpu_launches": int(n_launch.item()), "clocks": clocks,

@@ -234,20 +234,83 @@ def run_pull(args, rank: int, world: int) -> None:
         checks = [(e["source"], per_source[e["source"]], e["mine"], e["sub"]["dst"]) for e in edges]
     verified, verified_bytes = verify.verify_over_group(pool, is_prefill, checks, mode=args.mode, deep=deep, device=device)
 
-    # ---- end to end: the decode side stages tables from the host every step, launches, reads the status back
-    e2e = []
+    # ---- end to end: every step the prefill worker stages its block tables and exit planes from pinned host memory
+    # and sends them to the decode worker over NCCL (the deployment's metadata exchange); the decode worker stages its
+    # own tables and ranges from the host, launches straight from the received device arrays, and the status is read back
+    def pinned(array):
+        return torch.from_numpy(np.ascontiguousarray(array)).pin_memory()
+
+    for e in edges:
+        mine = e["mine"]
+        wp = w if is_prefill else per_source[e["source"]]
+        lengths = [wp.lengths[i] for i in mine]
+        shape = (len(mine), s.planes, width)
+        e["wire"] = dict(src=torch.zeros(shape, dtype=torch.int32, device=device),
+                         exits=torch.zeros(max(1, sum(lengths)), dtype=torch.int32, device=device))
+        if is_prefill:
+            e["host"] = dict(src=pinned(exchange.encode_tables([wp.src_tables[i] for i in mine], s.planes, width).numpy()),
+                             exits=None if wp.exit_planes is None else
+                             pinned(np.concatenate([np.asarray(wp.exit_planes[i], np.int32) for i in mine])))
+        else:
+            ends = np.cumsum(lengths)
+            e["host"] = dict(dst=pinned(exchange.encode_tables(e["sub"]["dst"], dst_planes, width).numpy()),
+                             begin=pinned(np.asarray([r[0] for r in e["sub"]["ranges"]], np.int32)),
+                             end=pinned(np.asarray([r[1] for r in e["sub"]["ranges"]], np.int32)),
+                             offsets=pinned((ends - np.asarray(lengths)).astype(np.int64)))
+        e["has_exits"] = wp.exit_planes is not None
+
+    def e2e_step():
+        nonlocal counter
+        counter += 1
+        staged = 0
+        if is_prefill:
+            for e in edges:
+                e["wire"]["src"].copy_(e["host"]["src"], non_blocking=True)
+                staged += e["host"]["src"].numel() * 4
+                dist.send(e["wire"]["src"], e["decode"])
+                if e["has_exits"]:
+                    e["wire"]["exits"].copy_(e["host"]["exits"], non_blocking=True)
+                    staged += e["host"]["exits"].numel() * 4
+                    dist.send(e["wire"]["exits"], e["decode"])
+                kh.kv_signal(e["ready_ptr"], counter)
+            for e in edges:
+                kh.kv_wait(e["done"], counter, kh._lib.MAX_WAIT_NS, status)
+        else:
+            for e in edges:
+                dist.recv(e["wire"]["src"], e["source"])
+                if e["has_exits"]:
+                    dist.recv(e["wire"]["exits"], e["source"])
+                mine_dev = {k: v.to(device, non_blocking=True) for k, v in e["host"].items()}
+                staged += sum(v.numel() * v.element_size() for v in e["host"].values())
+                b = kh.HandoffBatch.from_device(e["wire"]["src"], mine_dev["dst"], mine_dev["begin"], mine_dev["end"],
+                                                block_size=s.block_size,
+                                                exit_planes=e["wire"]["exits"] if e["has_exits"] else None,
+                                                exit_offsets=mine_dev["offsets"] if e["has_exits"] else None)
+                kh.kv_wait(e["ready"], counter, kh._lib.MAX_WAIT_NS, status)
+                kh.kv_handoff(e["sv"], dv, b, mode=mode, status=status, variant=args.variant, deep_layers=deep)
+                kh.kv_signal(e["done_ptr"], counter)
+                e["last_batch"] = (b, mine_dev)
+        return staged
+
+    if is_prefill:
+        for e, planned in zip(edges, plan):
+            e["decode"] = planned["decode"]
+    e2e, staged_now = [], 0
     for i in range(args.warmup + args.steps):
         dist.barrier()
         torch.cuda.synchronize()
         t_start = time.perf_counter()
-        step(fresh_batches=True)
+        staged_now = e2e_step()
         kh.raise_for_status(status)
         if i >= args.warmup:
             e2e.append(time.perf_counter() - t_start)
     e2e_s = torch.tensor([statistics.mean(e2e)], device=device, dtype=torch.float64)
     dist.all_reduce(e2e_s, op=dist.ReduceOp.MAX)
-    staged_bytes = torch.tensor([0 if is_prefill else sum(e["batch"].metadata_bytes for e in edges)], device=device)
+    staged_bytes = torch.tensor([staged_now], device=device)
     dist.all_reduce(staged_bytes)
+    # the destination was written once more by the end-to-end steps, from tables that crossed NCCL: check it again
+    verified_e2e, verified_e2e_bytes = verify.verify_over_group(pool, is_prefill, checks, mode=args.mode, deep=deep, device=device)
+    verified = verified and verified_e2e and verified_e2e_bytes == verified_bytes
 
     # ---- per-request latency between rank 0 and its first partner: ready flag -> pull -> done flag, timed on the prefill
     # stream. The decode worker knows a request from its reservation on, so it queues wait -> pull -> done ahead of
@@ -324,8 +387,11 @@ def run_pull(args, rank: int, world: int) -> None:
                                  "token's exit plane cross the link and `value` counts every destination byte"},
             "per_pair_gbps": per_pair, "link_bytes": total_wire, "link_gbps_per_pair": per_link,
             "e2e": {"value": total_payload / float(e2e_s.item()) / 1e9, "unit": bench.UNIT,
-                    "h2d_bytes_per_step": int(staged_bytes.item()), "d2h_bytes_per_step": 16 * n_decode, "ms_per_step": float(e2e_s.item()) * 1e3,
-                    "note": "tables, ranges and exit planes are staged from the host on the decode ranks every step"},
+                    "h2d_bytes_per_step": int(staged_bytes.item()), "d2h_bytes_per_step": 16 * world, "ms_per_step": float(e2e_s.item()) * 1e3,
+                    "note": "every step: the prefill worker stages its block tables and exit planes from pinned host memory and "
+                            "sends them to the decode worker over NCCL; the decode worker stages its own tables and ranges, "
+                            "waits for the ready flag, pulls, raises the done flag; both read their status words back"},
+            "p50_latency_ms": statistics.median(lat),
             "latency_ms": {"p50": statistics.median(lat), "max": max(lat), "min": min(lat),
                            "what": "rank 0 -> its first decode partner: ready flag, pull, done flag; CUDA events on the prefill stream; "
                                    "the decode side has its wait and pull queued before the flag is raised"},

@@ -415,15 +415,21 @@ class CudaBackend:
     marker = event  # an event at the current end of the transfer stream, used to tell when queued work begins
 
     def close(self):
-        import ctypes as C  # noqa: F401
-
         from .. import _lib
 
-        for box, _, host in self._mailboxes.values():
+        boxes, self._mailboxes = self._mailboxes, {}
+        for box, _, host in boxes.values():
             _lib.check(_lib.load().rlt_host_unregister(host), "rlt_host_unregister")
             box.close()
-        self._mailboxes.clear()
         self.mapping.close()
+
+    def __del__(self):
+        # a backend that is dropped without close() must still unregister what it registered: the mailbox mappings
+        # go away with their objects, and a registration left behind would cover whatever is mapped there next
+        try:
+            self.close()
+        except Exception:
+            pass
 
 
 def _pid() -> int:
