@@ -684,6 +684,13 @@ def suite_kernels(args):
         n = min(1 << 30, src.key_cache.numel() * 2)
         ms = _timed(lambda: kh.kv_push(src.key_cache.data_ptr(), dst.key_cache.data_ptr(), n))
         report("segments", "push_kernel (one range)", 2 * n, ms)
+        # context for launches this short: a plain device-to-device copy of the same sizes (the HBM peak in
+        # MEASURED_PEAKS.json is the same operation on 2 GiB, where ramp-up and tail weigh less)
+        flat_a, flat_b = src.key_cache.view(torch.uint8).reshape(-1), dst.key_cache.view(torch.uint8).reshape(-1)
+        for size, label in ((n, "1 GiB"), (blocks * block, "the 256 blocks' bytes")):
+            size = min(size, flat_a.numel(), flat_b.numel())
+            ms = _timed(lambda: flat_b[:size].copy_(flat_a[:size]))
+            report("segments", f"context: Tensor.copy_ of {label}, contiguous", 2 * size, ms)
 
     if wanted("tensors"):
         ids = torch.randint(0, 2**40, (1 << 26,), dtype=torch.int64, device=dev)
