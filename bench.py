@@ -854,6 +854,8 @@ def suite_deployment(args):
         "bytes_sent": sent, "transfers": sum(m.get("transfers", 0) for m in worker_metrics.values()),
         "transfer_seconds_sum": seconds,
         "gbps_while_transferring": (sent / seconds / 1e9) if seconds else None, "startup_s": startup,
+        "marks_ms_from_prefill_started": [
+            {k: round((v - t["prefill_started"]) * 1e3, 3) for k, v in t.items() if isinstance(v, float)} for t in marks[:4]],
     }), flush=True)
 
 

@@ -115,6 +115,7 @@ struct GroupTables {
 // Pieces [a, b) of every carried row of a group, for one region: piece = (K|V, selected layer). The flat vector array
 // is ordered piece, row, vector, so consecutive threads walk consecutive tokens of one layer. Each vector is loaded
 // once from the row's exit plane and stored to the same in-block offset of every deeper plane whose block is valid.
+// This form serves rows shorter than a warp's reach (scale rows); fan_group_rows below serves the long ones.
 template <typename T>
 __device__ __forceinline__ void fan_group(const FinalizeRegion& rg, const GroupTables& gt, int g, int planes,
                                           const int* layer_of, int layers, int a, int b) {
@@ -156,6 +157,48 @@ __device__ __forceinline__ void fan_group(const FinalizeRegion& rg, const GroupT
             const long long pb = gt.plane_off[g][t];
             if (pb >= 0) st_stream(reinterpret_cast<T*>(pool + pb + at), regs[u]);
           }
+        }
+      }
+    }
+  }
+}
+
+// The same pieces with one warp per (piece, row): where the row lives is worked out once per warp and row instead of
+// once per vector, and each lane then keeps kRowUnroll 16-byte loads in flight (4 KiB per warp for the Ouro shape).
+// Consecutive warps take consecutive rows of one layer, so the CTA still covers neighbouring tokens together.
+constexpr int kRowUnroll = 8;
+
+__device__ __forceinline__ void fan_group_rows(const FinalizeRegion& rg, const GroupTables& gt, int g, int planes,
+                                               const int* layer_of, int layers, int a, int b) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int carried = gt.carried;
+  const int jobs = (b - a) * carried;
+  for (int job = warp; job < jobs; job += kThreads / 32) {
+    const int piece_rel = gt.magic ? static_cast<int>(__umulhi(static_cast<unsigned>(job), gt.magic)) : job;
+    const int r = job - piece_rel * carried;
+    const int piece = a + piece_rel;
+    const int kv = piece >= layers;
+    const int e = gt.exit_plane[r];
+    const long long src_block = gt.plane_off[g][e];
+    if (src_block < 0) continue;
+    char* pool = kv ? rg.value : rg.key;
+    const long long in_block = layer_of[piece - kv * layers] * rg.layer_bytes + gt.tok_off[g][r];
+    const uint4* from = reinterpret_cast<const uint4*>(pool + src_block + in_block);
+    for (int base = lane; base < rg.row_vecs; base += 32 * kRowUnroll) {
+      uint4 regs[kRowUnroll];
+#pragma unroll
+      for (int u = 0; u < kRowUnroll; ++u) {
+        const int v = base + u * 32;
+        if (v < rg.row_vecs) regs[u] = ld_stream(from + v);
+      }
+      for (int t = e + 1; t < planes; ++t) {
+        const long long pb = gt.plane_off[g][t];
+        if (pb < 0) continue;
+        uint4* to = reinterpret_cast<uint4*>(pool + pb + in_block);
+#pragma unroll
+        for (int u = 0; u < kRowUnroll; ++u) {
+          const int v = base + u * 32;
+          if (v < rg.row_vecs) st_stream(to + v, regs[u]);
         }
       }
     }
@@ -329,7 +372,9 @@ __global__ void __launch_bounds__(kThreads, 3) finalize_fan_kernel(const Finaliz
         const int a = max(lo - g * pieces_per_region, 0), b = min(hi - g * pieces_per_region, pieces_per_region);
         if (a >= b) continue;
         const FinalizeRegion& rg = p.region[g];
-        if (rg.vec_bytes == 16) {
+        if (rg.vec_bytes == 16 && rg.row_vecs >= 32) {
+          fan_group_rows(rg, gt, g, p.planes, layer_of, layers, a, b);
+        } else if (rg.vec_bytes == 16) {
           fan_group<uint4>(rg, gt, g, p.planes, layer_of, layers, a, b);
         } else if (rg.vec_bytes == 4) {
           fan_group<uint32_t>(rg, gt, g, p.planes, layer_of, layers, a, b);

@@ -6,23 +6,24 @@
 // partition_segments produces (:95-112): up to a few hundred ranges whose sizes
 // differ by orders of magnitude (a 1.5 MiB block next to a 4 KiB partial row).
 //
-// Work split: the ranges are laid end to end, and CTA c of a persistent grid copies
-// bytes [c * T / G, (c + 1) * T / G) of that line (cuts rounded to 256 bytes inside a
-// range). Every CTA computes the same exclusive scan of the range sizes with
-// warp-shuffle prefix sums in shared memory and finds its first range by binary
-// search, so every CTA moves the same number of bytes to within 256 whatever the mix
-// of range sizes; a split into fixed tiles left up to one tile of difference per CTA,
-// which is 7 % of a launch that moves 0.8 GB.
+// Work split: the ranges are cut into tiles of 32 KiB (two passes of the copy loop) and the tiles of all
+// ranges form one flat index space that the persistent grid strides over: at any moment the CTAs work on
+// neighbouring tiles, so the DRAM channels see one dense window of addresses. Every CTA computes the
+// exclusive scan of the per-range tile counts with warp-shuffle prefix sums in shared memory and finds a tile's
+// range by binary search. (Tiles of 64 KiB left up to 7 % of imbalance on a launch that moves 0.8 GB; giving each
+// CTA one contiguous share instead put hundreds of far-apart streams on the memory system and measured slower.)
 //
 // Roofline: one read and one write per byte. Local copies are HBM bound; a
 // destination on a peer GPU is bound by NVLink (one direction).
+
+#include <cstdlib>
 
 #include "common.cuh"
 
 namespace rlt {
 namespace {
 
-constexpr long long kCutBytes = 256;  // shares are cut at multiples of this inside a range: vector alignment survives
+constexpr long long kTileBytesDefault = 32 * 1024;
 constexpr int kUnroll = 4;  // four 16-byte loads in flight per thread and three CTAs per SM measured best on HBM
 constexpr int kCtasPerSm = 3;
 
@@ -45,7 +46,7 @@ __device__ __forceinline__ void stream_range(const char* __restrict__ src, char*
   }
 }
 
-// One piece of one range. Pointers that are both 16-byte aligned take the vector path with a byte tail;
+// One tile of one range. Pointers that are both 16-byte aligned take the vector path with a byte tail;
 // otherwise the widest element both pointers and the length allow.
 __device__ __forceinline__ void copy_piece(const char* src, char* dst, long long n) {
   const unsigned long long both = reinterpret_cast<unsigned long long>(src) | reinterpret_cast<unsigned long long>(dst);
@@ -60,76 +61,63 @@ __device__ __forceinline__ void copy_piece(const char* src, char* dst, long long
   }
 }
 
-// Byte position `at` of a line of `total` bytes, moved down to a multiple of kCutBytes (the end of the line stays).
-__device__ __forceinline__ long long cut_of(long long total, long long part, long long parts) {
-  // total / parts * part + remainder term: no overflow for any int64 total
-  const long long at = total / parts * part + total % parts * part / parts;
-  return part >= parts ? total : at & ~(kCutBytes - 1);
+__global__ void __launch_bounds__(kThreads, 3) push_kernel(const char* src, char* dst, long long nbytes, long long kTileBytes) {
+  const long long tiles = (nbytes + kTileBytes - 1) / kTileBytes;
+  for (long long t = blockIdx.x; t < tiles; t += gridDim.x) {
+    const long long at = t * kTileBytes;
+    copy_piece(src + at, dst + at, min(kTileBytes, nbytes - at));
+  }
 }
 
-__global__ void __launch_bounds__(kThreads, 3) push_kernel(const char* src, char* dst, long long nbytes) {
-  const long long lo = cut_of(nbytes, blockIdx.x, gridDim.x), hi = cut_of(nbytes, blockIdx.x + 1, gridDim.x);
-  if (hi > lo) copy_piece(src + lo, dst + lo, hi - lo);
-}
-
-__global__ void __launch_bounds__(kThreads, 3) segment_copy_kernel(const long long* __restrict__ segments, int count) {
-  extern __shared__ long long seg_start[];  // [count + 1] exclusive scan of the range sizes
-  __shared__ long long warp_sum[kThreads / 32];
-  __shared__ long long carry;
+__global__ void __launch_bounds__(kThreads, 3) segment_copy_kernel(const long long* __restrict__ segments, int count, long long kTileBytes) {
+  extern __shared__ int tile_off[];  // [count + 1] exclusive scan of tiles per range
+  __shared__ int warp_sum[kThreads / 32];
+  __shared__ int carry;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   if (threadIdx.x == 0) {
     carry = 0;
-    seg_start[0] = 0;
+    tile_off[0] = 0;
   }
   __syncthreads();
   for (int base = 0; base < count; base += kThreads) {
     const int s = base + threadIdx.x;
-    long long n = 0;
+    int tiles = 0;
     if (s < count) {
-      n = segments[3ll * s + 2];
-      if (n < 0) n = 0;
+      const long long n = segments[3ll * s + 2];
+      tiles = n > 0 ? static_cast<int>((n + kTileBytes - 1) / kTileBytes) : 0;
     }
-    long long inc = n;
-#pragma unroll
-    for (int d = 1; d < 32; d <<= 1) {
-      const long long up = __shfl_up_sync(0xffffffffu, inc, d);
-      if (lane >= d) inc += up;
-    }
+    const int inc = warp_inclusive_scan(tiles);
     if (lane == 31) warp_sum[warp] = inc;
     __syncthreads();
-    long long before = carry;
+    int before = carry;
     for (int w = 0; w < warp; ++w) before += warp_sum[w];
-    if (s < count) seg_start[s + 1] = before + inc;
+    if (s < count) tile_off[s + 1] = before + inc;
     __syncthreads();
     if (threadIdx.x == kThreads - 1) carry = before + inc;
     __syncthreads();
   }
-  const long long total = seg_start[count];
-  // This CTA's share of the line. A cut is rounded down to a multiple of kCutBytes *inside its range*, so the
-  // CTA on either side of it derives the same cut from the same numbers.
-  long long share[2];
-  int first = 0;
-#pragma unroll
-  for (int k = 0; k < 2; ++k) {
-    const long long part = static_cast<long long>(blockIdx.x) + k;
-    long long at = part >= gridDim.x ? total : total / gridDim.x * part + total % gridDim.x * part / gridDim.x;
-    int lo = 0, hi = count;  // last range that starts at or before `at`
+  const int total = tile_off[count];
+  for (int t = blockIdx.x; t < total; t += gridDim.x) {
+    int lo = 0, hi = count;  // last range whose first tile is at or before t
     while (hi - lo > 1) {
       const int mid = (lo + hi) >> 1;
-      if (seg_start[mid] <= at) lo = mid; else hi = mid;
+      if (tile_off[mid] <= t) lo = mid; else hi = mid;
     }
-    if (at < total) at = seg_start[lo] + ((at - seg_start[lo]) & ~(kCutBytes - 1));
-    share[k] = at;
-    if (k == 0) first = lo;
+    const long long at = static_cast<long long>(t - tile_off[lo]) * kTileBytes;
+    const long long n = segments[3ll * lo + 2];
+    copy_piece(reinterpret_cast<const char*>(segments[3ll * lo]) + at, reinterpret_cast<char*>(segments[3ll * lo + 1]) + at,
+               min(kTileBytes, n - at));
   }
-  for (int s = first; s < count && seg_start[s] < share[1]; ++s) {
-    const long long lo = max(share[0], seg_start[s]) - seg_start[s];
-    const long long hi = min(share[1], seg_start[s + 1]) - seg_start[s];
-    if (hi > lo) {
-      copy_piece(reinterpret_cast<const char*>(segments[3ll * s]) + lo, reinterpret_cast<char*>(segments[3ll * s + 1]) + lo,
-                 hi - lo);
-    }
-  }
+}
+
+// EXPERIMENT knobs (to be removed): tile size and CTAs per SM from the environment
+long long tile_bytes() {
+  static const long long v = [] { const char* e = getenv("RLT_COPY_TILE_KIB"); return e ? atoll(e) * 1024 : kTileBytesDefault; }();
+  return v;
+}
+int ctas_per_sm() {
+  static const int v = [] { const char* e = getenv("RLT_COPY_CTAS"); return e ? atoi(e) : kCtasPerSm; }();
+  return v;
 }
 
 }  // namespace
@@ -146,9 +134,9 @@ int rlt_kv_push(const void* src, void* dst, int64_t nbytes, rlt_stream_t stream)
   if (rc != RLT_OK) return rc;
   // one persistent wave; a small range gets one CTA per 16 KiB (one pass of the copy loop)
   const long long passes = (nbytes + 16383) / 16384;
-  const int grid = static_cast<int>(passes < sms * static_cast<long long>(rlt::kCtasPerSm) ? passes : sms * static_cast<long long>(rlt::kCtasPerSm));
+  const int grid = static_cast<int>(passes < sms * static_cast<long long>(rlt::ctas_per_sm()) ? passes : sms * static_cast<long long>(rlt::ctas_per_sm()));
   rlt::push_kernel<<<grid, rlt::kThreads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-      static_cast<const char*>(src), static_cast<char*>(dst), nbytes);
+      static_cast<const char*>(src), static_cast<char*>(dst), nbytes, rlt::tile_bytes());
   RLT_CUDA_TRY(cudaGetLastError());
   rlt::g_launches.fetch_add(1, std::memory_order_relaxed);
   return RLT_OK;
@@ -162,9 +150,9 @@ int rlt_kv_copy_segments(const int64_t* segments, int32_t count, rlt_stream_t st
   int sms = 0;
   const int rc = rlt::sm_count(&sms);
   if (rc != RLT_OK) return rc;
-  const size_t smem = (static_cast<size_t>(count) + 1) * sizeof(long long);
-  rlt::segment_copy_kernel<<<sms * rlt::kCtasPerSm, rlt::kThreads, smem, reinterpret_cast<cudaStream_t>(stream)>>>(
-      reinterpret_cast<const long long*>(segments), count);
+  const size_t smem = (static_cast<size_t>(count) + 1) * sizeof(int);
+  rlt::segment_copy_kernel<<<sms * rlt::ctas_per_sm(), rlt::kThreads, smem, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const long long*>(segments), count, rlt::tile_bytes());
   RLT_CUDA_TRY(cudaGetLastError());
   rlt::g_launches.fetch_add(1, std::memory_order_relaxed);
   return RLT_OK;

@@ -333,6 +333,11 @@ class PDStageConnector:
             return
         self._forget(t)
 
+    def _trace(self, what, tid):
+        note = getattr(self.transport, "_note", None)  # the transport's optional chunk trace (RLT_KV_TRACE)
+        if callable(note) and getattr(self.transport, "_trace_dir", None):
+            note(what, tid, -1)
+
     def _announce_active(self, t):
         if t.active:
             return
@@ -377,6 +382,7 @@ class PDStageConnector:
         if type(count) is not int or count <= 0:
             raise RuntimeError("invalid transfer commit count")
         t.expected = count
+        self._trace("commit arrived", transfer_id)
 
     def acknowledge(self, transfer_id):
         t = self.transfers.get(transfer_id)
@@ -622,6 +628,7 @@ class Exporter:
                 and c.engine.release_transfer_compute(t.request, ready_event=t.last_event)):
             c.notify("prefill_complete", tid=t.tid, overlaps=t.transfer_overlaps,
                      boundaries=(t.transfer_boundary_first, t.transfer_boundary_last, t.transfer_boundary_count))
+            c._trace("prefill_complete sent", t.tid)
         self.send_next(t)
 
     def unwind(self, t):
@@ -648,6 +655,7 @@ class Exporter:
             if not t.committed and t.compute_done and not t.chunks:
                 t.committed = True
                 c.notify("commit", tid=t.tid, count=t.next_sequence)
+                c._trace("commit sent", t.tid)
             if t.committed and t.acknowledged and t.request.compute_released and not c.transport.busy(t.tid):
                 c._remove(t)
 
@@ -696,6 +704,7 @@ class Importer:
             raise RuntimeError("stale import activation")
         t.ready = True
         c.notify("received", tid=t.tid)
+        c._trace("received sent", t.tid)
 
     def watch(self, t):
         c = self.c

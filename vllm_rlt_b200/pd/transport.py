@@ -512,6 +512,14 @@ class B200Transport:
         self.bytes_received = 0
         self.transfers = 0
         self.transfer_seconds = 0.0
+        # RLT_KV_TRACE=<directory>: every step of every chunk with the host's monotonic clock (which all processes of
+        # a host share), written to <directory>/<worker name>.jsonl at close(); off by default
+        self._trace_dir = os.environ.get("RLT_KV_TRACE")
+        self._trace: list[tuple] = []
+
+    def _note(self, what: str, transfer_id: str, sequence: int) -> None:
+        if self._trace_dir:
+            self._trace.append((time.monotonic(), what, transfer_id, sequence))
 
     # -- handshake ---------------------------------------------------------------------------
 
@@ -640,6 +648,7 @@ class B200Transport:
         box.write_descriptor(link["lane"], at, raw)
         started = self._order_after(after)  # the offer leaves when the producer's event has fired
         self._post(link, body)
+        self._note("offer queued", transfer_id, sequence)
         handle = self._offered[(self._agent_of(link), transfer_id, sequence)] = _RemoteCompletion()
         return self._ticket(handle, transfer_id, sequence, size, (), started)
 
@@ -664,6 +673,7 @@ class B200Transport:
             planes = (where["plane_end"] or len(target)) - where["plane_begin"]
             size += (end - start) * planes * 2 * layers * row
         self._pulls.append(_Pull(self.backend.event(), agent, message.transfer_id, message.sequence, size, keep))
+        self._note("pull launched", message.transfer_id, message.sequence)
 
     def poll(self):
         remaining = deque()
@@ -674,9 +684,11 @@ class B200Transport:
                 if message.kind == LANDED:
                     notifications.append((agent, message.transfer_id, message.sequence))
                 elif message.kind == OFFER:
+                    self._note("offer seen", message.transfer_id, message.sequence)
                     self._begin_pull(agent, message)
                 elif message.kind == PULLED:
                     handle = self._offered.pop((agent, message.transfer_id, message.sequence), None)
+                    self._note("pulled seen", message.transfer_id, message.sequence)
                     if handle is not None:
                         handle.done = True
         # chunks this worker is reading: report each once its launch has finished, then tell its owner
@@ -685,6 +697,7 @@ class B200Transport:
             if not pull.reported and pull.event.query():
                 pull.reported = True
                 pull.keepalive = ()
+                self._note("pull finished", pull.transfer_id, pull.sequence)
                 self.bytes_received += pull.size
                 notifications.append((pull.peer, pull.transfer_id, pull.sequence))
             if pull.reported:
@@ -697,7 +710,8 @@ class B200Transport:
         now = time.monotonic()
         for ticket in self.pending:
             if ticket.started_at is None and (ticket.started is None or ticket.started.query()):
-                ticket.started_at = now  # time-outs and transfer time count from when the copy could begin,
+                ticket.started_at = now
+                self._note("copy or offer begun", ticket.transfer_id, ticket.sequence)  # time-outs and transfer time count from when the copy could begin,
                 #                          not from when it was queued behind the prefill that produces the KV
             if ticket.started_at is not None and now - ticket.started_at > self.config.request_timeout:
                 raise TimeoutError("KV write timed out; registered memory must be quarantined")
@@ -710,6 +724,7 @@ class B200Transport:
             self.bytes_sent += ticket.size
             self.transfers += 1
             self.transfer_seconds += time.monotonic() - ticket.started_at
+            self._note("ticket done", ticket.transfer_id, ticket.sequence)
             finished.append(ticket)
         self.pending = remaining
         return finished, notifications
@@ -725,6 +740,14 @@ class B200Transport:
     def close(self):
         if self.pending or self._pulls:
             raise RuntimeError("cannot deregister memory with in-flight transfers")
+        if self._trace_dir and self._trace:
+            import json
+
+            os.makedirs(self._trace_dir, exist_ok=True)
+            with open(os.path.join(self._trace_dir, f"{self.name}.jsonl"), "a") as out:
+                for row in self._trace:
+                    out.write(json.dumps(row) + "\n")
+            self._trace = []
         self._link.clear()
         self.backend.close()
         self.mailbox.close()
