@@ -180,7 +180,7 @@ def test_chunks_respect_the_byte_limit_and_sequence_numbers_are_dense(direction)
     assert d.take("received")
     mover = (d if direction == "pull" else p).transport.backend  # whose device ran the table-driven launches
     kinds = [c[0] if isinstance(c, tuple) else "segments" for c in mover.copies]
-    assert kinds.count("tables") == 4
+    assert kinds.count("tables") == 1  # five tickets and five notifications, but chunks ready together are one launch
     assert torch.equal(pool_rows(p.pool, p.pool.plane_block_tables("r"), 0, 12),
                        pool_rows(d.pool, d.pool.plane_block_tables("r"), 0, 12))
     run_handoff(p, d, "s", 11)  # last piece has room for the hidden row: it rides along

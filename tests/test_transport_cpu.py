@@ -289,3 +289,39 @@ def test_time_outs_and_transfer_time_count_from_when_the_copy_could_begin():
     time.sleep(0.12)
     with pytest.raises(TimeoutError, match="quarantined"):
         p.poll()
+
+
+@pytest.mark.parametrize("direction", ["push", "pull"])
+def test_chunks_submitted_together_share_one_launch_but_keep_their_tickets_and_notifications(direction):
+    config = PDConfig(transfer_chunk_bytes=3000, max_inflight_bytes=7000)
+    pc, dc = cpu_cache(), cpu_cache()
+    pc.key_cache.view(torch.uint8).random_(0, 256)
+    p = tr.B200Transport("p0", pc, torch.zeros(2, 16), config, backend=FakeBackend(), direction=direction)
+    d = tr.B200Transport("d0", dc, torch.zeros(2, 16), config, backend=FakeBackend(), lane=1, direction=direction)
+    p.connect(d.info)
+    d.connect(p.info)
+    tables = ((0, 1), (2, 3), (4, 5), (6, 7))
+    per_token = 4 * 2 * 3 * 32
+    request = [(tables, tables, 0, 8)]
+    with pytest.raises(ValueError, match="consecutive sequence numbers"):
+        p.submit_tables("t", 4, "d0", request, 8 * per_token, parts=[(4, 3 * per_token), (6, 5 * per_token)])
+    with pytest.raises(ValueError, match="add up"):
+        p.submit_tables("t", 4, "d0", request, 8 * per_token, parts=[(4, 3 * per_token), (5, 3 * per_token)])
+    with pytest.raises(ValueError, match="exceeds configured chunk size"):
+        p.submit_tables("t", 4, "d0", request, 8 * per_token, parts=[(4, 4 * per_token), (5, 4 * per_token)])
+    parts = [(4, 3 * per_token), (5, 3 * per_token), (6, 2 * per_token)]
+    assert p.submit_tables("t", 4, "d0", request, 8 * per_token, parts=parts)
+    assert len(p.pending) == 3 and p.inflight_bytes == 8 * per_token
+    assert p.submit_tables("t", 7, "d0", request, 8 * per_token, parts=[(7, 3 * per_token), (8, 3 * per_token), (9, 2 * per_token)]) is False
+    notes = []
+    for _ in range(3):
+        notes += d.poll()[1]
+        p.poll()
+    assert notes == [("p0", "t", 4), ("p0", "t", 5), ("p0", "t", 6)]
+    mover = d if direction == "pull" else p
+    assert [c[0] for c in mover.backend.copies if isinstance(c, tuple)] == ["tables"]  # one launch for the three
+    assert p.transfers == 3 and p.bytes_sent == 8 * per_token and not p.pending and p.inflight_bytes == 0
+    assert torch.equal(dc.key_cache[:8].view(torch.uint8), pc.key_cache[:8].view(torch.uint8))
+    assert int(dc.key_cache[8:].view(torch.uint8).sum()) == 0
+    for t in (p, d):
+        t.close()

@@ -585,40 +585,78 @@ class Exporter:
                 pass
 
     def send_next(self, t):
+        """Put the head of the transfer's queue on the wire: a caller-built descriptor chunk alone, table chunks
+        together with every chunk behind them that is ready at the same moment (one launch, see ``_group``)."""
         if not t.chunks:
             return False
-        chunk = t.chunks[0]
-        sent = self._send_table_chunk(t, chunk) if isinstance(chunk, TableChunk) else self._send_descriptors(t, chunk)
-        if sent:
+        head = t.chunks[0]
+        if not isinstance(head, TableChunk):
+            if not self._send_descriptors(t, head):
+                return False
+            taken = 1
+        else:
+            taken = self._send_table_chunks(t)
+        for _ in range(taken):
             t.chunks.popleft()
-            t.submitted_since_compute = True
-        return bool(sent)
+        t.submitted_since_compute = t.submitted_since_compute or taken > 0
+        return taken > 0
+
+    def _group(self, t):
+        """The table chunks at the head of the queue that can leave as one launch: same producer event, same plane and
+        layer slice, token ranges that continue one another (a trailing hidden-row-only chunk joins too), and as
+        many of them as the in-flight budget has room for (always at least the first)."""
+        head = t.chunks[0]
+        room = self.c.config.max_inflight_bytes - self.c.transport.inflight_bytes
+        group, total, end = [], 0, head.start
+        for chunk in t.chunks:
+            if not isinstance(chunk, TableChunk):
+                break
+            same_launch = (chunk.event is head.event and chunk.planes == head.planes and chunk.layers == head.layers
+                           and chunk.source_tables == head.source_tables and chunk.target_tables == head.target_tables)
+            if not same_launch or chunk.start != end:  # a hidden-row-only chunk sits at the end of its range
+                break
+            if group and (total + chunk.size > room or len(group) == 255):
+                break
+            group.append(chunk)
+            total += chunk.size
+            end = max(end, chunk.end)
+            if chunk.hidden is not None:
+                break  # the hidden row closes a prompt: nothing follows it
+        return group
 
     def _send_descriptors(self, t, chunk):
         """A caller-built descriptor chunk, the reference's form: (event, sequence, local, remote, size)."""
         event, sequence, local, remote, size = chunk
         return event.query() and self.c.transport.submit(t.tid, sequence, t.peer, local, remote, size)
 
-    def _send_table_chunk(self, t, chunk):
+    def _send_table_chunks(self, t):
+        """Submit the head group; returns how many chunks went out (0: not now)."""
         transport = self.c.transport
+        head = t.chunks[0]
         behind = {}
         if self.c._device_ordered():
-            behind["after"] = chunk.event
-        elif not chunk.event.query():
-            return False
-        riders = [chunk.hidden] if chunk.hidden is not None else []
-        if chunk.start >= chunk.end:  # nothing but the hidden row
+            behind["after"] = head.event
+        elif not head.event.query():
+            return 0
+        group = self._group(t)
+        riders = [c.hidden for c in group if c.hidden is not None]
+        start, end = group[0].start, max(c.end for c in group)
+        total = sum(c.size for c in group)
+        if start >= end:  # nothing but the hidden row
             here, there = transport.info["device"], transport.peers[t.peer]["device"]
-            return transport.submit(t.tid, chunk.sequence, t.peer, [(s, n, here) for s, _, n in riders],
-                                    [(d, n, there) for _, d, n in riders], chunk.size, **behind)
+            sent = transport.submit(t.tid, head.sequence, t.peer, [(s, n, here) for s, _, n in riders],
+                                    [(d, n, there) for _, d, n in riders], head.size, **behind)
+            return 1 if sent else 0
         where = {}
-        if chunk.planes is not None:
-            where.update(plane_begin=chunk.planes[0], plane_end=chunk.planes[1])
-        if chunk.layers is not None:
-            where.update(layer_begin=chunk.layers[0], layer_end=chunk.layers[1])
-        return transport.submit_tables(t.tid, chunk.sequence, t.peer,
-                                       [(chunk.source_tables, chunk.target_tables, chunk.start, chunk.end)], chunk.size,
-                                       extra=riders, **where, **behind)
+        if head.planes is not None:
+            where.update(plane_begin=head.planes[0], plane_end=head.planes[1])
+        if head.layers is not None:
+            where.update(layer_begin=head.layers[0], layer_end=head.layers[1])
+        if len(group) > 1:
+            where["parts"] = [(c.sequence, c.size) for c in group]
+        sent = transport.submit_tables(t.tid, head.sequence, t.peer, [(head.source_tables, head.target_tables, start, end)],
+                                       total, extra=riders, **where, **behind)
+        return len(group) if sent else 0
 
     # -- table steps
 

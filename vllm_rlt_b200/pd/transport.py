@@ -76,6 +76,7 @@ class Message:
     transfer_id: str
     sequence: int
     descriptor: bytes = b""
+    count: int = 1  # consecutive sequence numbers, starting at ``sequence``, that this one message stands for
 
 
 class _RemoteCompletion:
@@ -193,7 +194,8 @@ class Mailbox:
     Lane layout: slot 0 is a header whose first 8 bytes hold the count of messages the receiver
     has consumed; slots 1..SLOTS are the message ring; ``RING_BYTES`` of descriptor ring follow. Message ``n``
     (1-based) of a lane lives in ring slot ``(n - 1) % SLOTS`` and carries stamp ``n`` in its first 8 bytes; the
-    body is ``[sequence u32][tid length u8][kind u8][pad u16][descriptor offset u32][descriptor bytes u32][tid]``.
+    body is ``[sequence u32][tid length u8][kind u8][count u16][descriptor offset u32][descriptor bytes u32][tid]``;
+    ``count`` consecutive sequence numbers starting at ``sequence`` share the message (chunks that left as one launch).
     The sender writes body then stamp - its GPU with ``rlt_kv_post`` when the message must follow device work,
     its CPU otherwise; the receiver's host reads stamp then body. A descriptor is written by the sender's CPU
     before the message that names it is posted, and read by the receiver before it counts the message consumed.
@@ -220,11 +222,14 @@ class Mailbox:
         return lane * LANE_BYTES + SLOT_BYTES * (1 + (n - 1) % SLOTS)
 
     @staticmethod
-    def encode(transfer_id: str, sequence: int, kind: int = LANDED, descriptor: tuple[int, int] = (0, 0)) -> bytes:
+    def encode(transfer_id: str, sequence: int, kind: int = LANDED, descriptor: tuple[int, int] = (0, 0),
+               count: int = 1) -> bytes:
         raw = transfer_id.encode()
         if len(raw) > TID_MAX:
             raise ValueError(f"transfer id longer than {TID_MAX} bytes")
-        return struct.pack("<IBBHII", sequence, len(raw), kind, 0, *descriptor) + raw.ljust(TID_MAX, b"\0")
+        if not 1 <= count < 1 << 16:
+            raise ValueError("a message stands for 1 to 65535 sequence numbers")
+        return struct.pack("<IBBHII", sequence, len(raw), kind, count, *descriptor) + raw.ljust(TID_MAX, b"\0")
 
     def consumed(self, lane: int) -> int:
         return int(self.words[lane * LANE_BYTES // 8])
@@ -246,7 +251,7 @@ class Mailbox:
             at = self.slot_offset(lane, n)
             if int(self.words[at // 8]) != n:
                 return
-            sequence, length, kind, _, d_off, d_len = struct.unpack_from("<IBBHII", self.bytes, at + 8)
+            sequence, length, kind, count, d_off, d_len = struct.unpack_from("<IBBHII", self.bytes, at + 8)
             tid = bytes(self.bytes[at + 24 : at + 24 + min(length, TID_MAX)]).decode()
             descriptor = b""
             if d_len:
@@ -254,7 +259,7 @@ class Mailbox:
                 descriptor = bytes(self.bytes[base : base + d_len])
             self.next[lane] = n + 1
             self.words[lane * LANE_BYTES // 8] = n  # lets the sender reuse the slot and the descriptor's bytes
-            yield Message(kind, tid, sequence, descriptor)
+            yield Message(kind, tid, sequence, descriptor, max(1, count))
 
     def close(self):
         if self.shm is None:
@@ -300,6 +305,7 @@ class CudaBackend:
         self.mapping = peerlib.PeerMapping()
         self.peerlib = peerlib
         self._mailboxes: dict[str, tuple[Mailbox, int]] = {}
+        self._views: dict[tuple, tuple] = {}
         self.stream = torch.cuda.Stream(self.device)
 
     def _on_stream(self):
@@ -371,23 +377,29 @@ class CudaBackend:
         ``pull=True``: the peer's pool is the source and the local pool the destination (plain peer loads)."""
         from ..kernels import kv_handoff as kh
 
-        mine = kh.PoolView.from_cache(cache)
-        codes = mine.codes.rebased(translate(peer_info["key_ptr"], 1), translate(peer_info["value_ptr"], 1))
-        scales = None
-        if mine.scales is not None:
-            sr = peer_info["scale_region"]
-            scales = mine.scales.rebased(translate(sr["key_ptr"], 1), translate(sr["value_ptr"], 1))
-        if pull:
-            theirs = kh.PoolView(codes, scales, peer_info["num_blocks"], peer_info["block_size"], peer_info["num_layers"],
-                                 peer_info["depths"], peer_info["device"])
-            if mode == kh.MODE_EXIT_ONLY and mine.num_planes != 1:
-                raise ValueError("an exit-only pull needs a single-plane destination pool")
-            src, dst = theirs, mine
-        else:
-            planes = 1 if mode == kh.MODE_EXIT_ONLY else peer_info["depths"]
-            theirs = kh.PoolView(codes, scales, peer_info["num_blocks"], peer_info["block_size"], peer_info["num_layers"],
-                                 planes, peer_info["device"])
-            src, dst = mine, theirs
+        # the two pool views of a (peer, direction, plane count) never change: build them once
+        key = (peer_info["agent"], pull, mode == kh.MODE_EXIT_ONLY)
+        views = self._views.get(key)
+        if views is None:
+            mine = kh.PoolView.from_cache(cache)
+            codes = mine.codes.rebased(translate(peer_info["key_ptr"], 1), translate(peer_info["value_ptr"], 1))
+            scales = None
+            if mine.scales is not None:
+                sr = peer_info["scale_region"]
+                scales = mine.scales.rebased(translate(sr["key_ptr"], 1), translate(sr["value_ptr"], 1))
+            if pull:
+                theirs = kh.PoolView(codes, scales, peer_info["num_blocks"], peer_info["block_size"], peer_info["num_layers"],
+                                     peer_info["depths"], peer_info["device"])
+                if mode == kh.MODE_EXIT_ONLY and mine.num_planes != 1:
+                    raise ValueError("an exit-only pull needs a single-plane destination pool")
+                views = (theirs, mine)
+            else:
+                planes = 1 if mode == kh.MODE_EXIT_ONLY else peer_info["depths"]
+                theirs = kh.PoolView(codes, scales, peer_info["num_blocks"], peer_info["block_size"], peer_info["num_layers"],
+                                     planes, peer_info["device"])
+                views = (mine, theirs)
+            self._views[key] = views
+        src, dst = views
         with self.torch.cuda.device(self.device), self._on_stream():
             batch = kh.HandoffBatch(
                 [r[0] for r in requests], [r[1] for r in requests], [(r[2], r[3]) for r in requests],
@@ -418,6 +430,7 @@ class CudaBackend:
         from .. import _lib
 
         boxes, self._mailboxes = self._mailboxes, {}
+        self._views = {}
         for box, _, host in boxes.values():
             _lib.check(_lib.load().rlt_host_unregister(host), "rlt_host_unregister")
             box.close()
@@ -452,6 +465,7 @@ class _Pull:
     size: int
     keepalive: tuple = ()
     reported: bool = False  # (peer, tid, seq) has been handed to the connector; "pulled" may still be unsent
+    count: int = 1          # consecutive sequence numbers the launch covers
 
 
 def default_direction() -> str:
@@ -612,22 +626,33 @@ class B200Transport:
         return self._ticket(self.backend.event(), transfer_id, sequence, size, keep, started)
 
     def submit_tables(self, transfer_id, sequence, peer, requests, size, *, mode=0, layer_begin=0, layer_end=0,
-                      plane_begin=0, plane_end=0, exit_planes=None, extra=(), status=None, after=None):
+                      plane_begin=0, plane_end=0, exit_planes=None, extra=(), status=None, after=None, parts=None):
         """Table-driven form of ``submit``: ``requests`` is a list of ``(source tables, target tables,
         start, end)`` and the GPU walks the tables itself; ``extra`` holds plain ``(source address,
         peer address, bytes)`` ranges that ride along (the final hidden-state row).
 
+        ``parts`` lets several chunks that are ready together leave as ONE launch: a list of ``(sequence, size)``
+        with consecutive sequence numbers starting at ``sequence`` and sizes adding up to ``size``. Each part keeps
+        its own ticket, its own share of the in-flight budget and its own notification at the receiver; only the
+        launch, the staging of the tables and the mailbox message are shared.
+
         In the pull direction nothing is copied here: the chunk is offered and the peer reads it (see the module
-        docstring); the ticket completes when the peer says so. Launches that carry per-token exit planes or a
+        docstring); the tickets complete when the peer says so. Launches that carry per-token exit planes or a
         status array are always pushed (a descriptor does not carry them).
         """
         link = self._peer_link(peer)
-        if not self._admit(size, link):
+        parts = [(sequence, size)] if parts is None else list(parts)
+        if [s for s, _ in parts] != list(range(sequence, sequence + len(parts))) or sum(n for _, n in parts) != size:
+            raise ValueError("parts must be consecutive sequence numbers whose sizes add up to the submission")
+        for _, n in parts:
+            if n > self.config.transfer_chunk_bytes:
+                raise ValueError("transfer exceeds configured chunk size")
+        if self.inflight_bytes + size > self.config.max_inflight_bytes or not self._slot_free(link):
             return False
         where = dict(mode=mode, layer_begin=layer_begin, layer_end=layer_end, plane_begin=plane_begin, plane_end=plane_end)
         if self.direction == "pull" and exit_planes is None and status is None:
-            return self._offer(link, transfer_id, sequence, requests, size, extra, where, after)
-        body = Mailbox.encode(transfer_id, sequence, LANDED)
+            return self._offer(link, transfer_id, parts, requests, extra, where, after)
+        body = Mailbox.encode(transfer_id, sequence, LANDED, count=len(parts))
         translate = link["translate"]
         started = self._order_after(after)
         keep = tuple(self.backend.handoff(self.cache, self.peers[peer], translate, requests, exit_planes=exit_planes,
@@ -635,22 +660,28 @@ class B200Transport:
         if extra:
             keep += tuple(self.backend.copy_segments([(s, translate(d, n), n) for s, d, n in extra]))
         self._post(link, body)
-        return self._ticket(self.backend.event(), transfer_id, sequence, size, keep, started)
+        done = self.backend.event()
+        for seq, n in parts:
+            self._ticket(done, transfer_id, seq, n, keep, started)
+        return True
 
-    def _offer(self, link, transfer_id, sequence, requests, size, extra, where, after) -> bool:
+    def _offer(self, link, transfer_id, parts, requests, extra, where, after) -> bool:
         page = self.info["block_size"]
         raw = encode_chunk([trim_request(*r, page) for r in requests], extra, **where)
         box = link["box"]
         at = link["ring"].reserve(len(raw), link["stamp"] + 1, box.consumed(link["lane"]))
         if at is None:
             return False  # the peer has not yet read the descriptors ahead of this one: retry later
-        body = Mailbox.encode(transfer_id, sequence, OFFER, (at, len(raw)))
+        first = parts[0][0]
+        body = Mailbox.encode(transfer_id, first, OFFER, (at, len(raw)), count=len(parts))
         box.write_descriptor(link["lane"], at, raw)
         started = self._order_after(after)  # the offer leaves when the producer's event has fired
         self._post(link, body)
-        self._note("offer queued", transfer_id, sequence)
-        handle = self._offered[(self._agent_of(link), transfer_id, sequence)] = _RemoteCompletion()
-        return self._ticket(handle, transfer_id, sequence, size, (), started)
+        self._note("offer queued", transfer_id, first)
+        handle = self._offered[(self._agent_of(link), transfer_id, first)] = _RemoteCompletion()
+        for seq, n in parts:
+            self._ticket(handle, transfer_id, seq, n, (), started)
+        return True
 
     def _agent_of(self, link) -> str:
         return next(name for name, other in self._link.items() if other is link)
@@ -672,7 +703,8 @@ class B200Transport:
         for _, target, start, end in requests:
             planes = (where["plane_end"] or len(target)) - where["plane_begin"]
             size += (end - start) * planes * 2 * layers * row
-        self._pulls.append(_Pull(self.backend.event(), agent, message.transfer_id, message.sequence, size, keep))
+        self._pulls.append(_Pull(self.backend.event(), agent, message.transfer_id, message.sequence, size, keep,
+                                 count=message.count))
         self._note("pull launched", message.transfer_id, message.sequence)
 
     def poll(self):
@@ -682,7 +714,7 @@ class B200Transport:
         for lane, agent in self._lane_agent.items():
             for message in self.mailbox.drain(lane):
                 if message.kind == LANDED:
-                    notifications.append((agent, message.transfer_id, message.sequence))
+                    notifications += [(agent, message.transfer_id, message.sequence + k) for k in range(message.count)]
                 elif message.kind == OFFER:
                     self._note("offer seen", message.transfer_id, message.sequence)
                     self._begin_pull(agent, message)
@@ -699,11 +731,11 @@ class B200Transport:
                 pull.keepalive = ()
                 self._note("pull finished", pull.transfer_id, pull.sequence)
                 self.bytes_received += pull.size
-                notifications.append((pull.peer, pull.transfer_id, pull.sequence))
+                notifications += [(pull.peer, pull.transfer_id, pull.sequence + k) for k in range(pull.count)]
             if pull.reported:
                 link = self._peer_link(pull.peer)
                 if self._slot_free(link):
-                    self._post(link, Mailbox.encode(pull.transfer_id, pull.sequence, PULLED), from_host=True)
+                    self._post(link, Mailbox.encode(pull.transfer_id, pull.sequence, PULLED, count=pull.count), from_host=True)
                     continue
             still.append(pull)
         self._pulls = still
@@ -718,7 +750,6 @@ class B200Transport:
             if ticket.started_at is None or not ticket.handle.query():
                 remaining.append(ticket)
                 continue
-            ticket.handle = None
             ticket.keepalive = ()
             self.inflight_bytes -= ticket.size
             self.bytes_sent += ticket.size
