@@ -881,6 +881,11 @@ def main():
                     help="N >= 2, direct path: the prefill GPU writes into the decode pool, or the decode GPU reads the prefill pool")
     ap.add_argument("--path", default="direct", choices=["direct", "staged"],
                     help="N >= 2: one kernel that writes destination blocks over NVLink, or pack into peer staging + scatter")
+    ap.add_argument("--latency-requests", type=int, default=16,
+                    help="N >= 2: how many requests (per wave) get their own timed handoff for the latency percentiles")
+    ap.add_argument("--waves", type=int, default=1,
+                    help="N >= 2, pull: run this many independent draws of the workload one after another and report them as "
+                         "one line (for request counts whose pools do not fit the GPUs at once)")
     ap.add_argument("--suite", default=None, choices=["kernels", "peer", "deployment"],
                     help="another measurement instead of the benchmark line (see the module docstring)")
     ap.add_argument("--only", default="", help="--suite kernels: comma-separated groups (finalize,pack,segments,tensors)")

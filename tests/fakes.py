@@ -56,6 +56,8 @@ class FakeBackend:
         self.copies.append(list(triples))
         return ()
 
+    copy_ranges = copy_segments
+
     def handoff(self, cache, peer_info, translate, requests, *, mode=0, layer_begin=0, layer_end=0,
                 plane_begin=0, plane_end=0, exit_planes=None, status=None, pull=False):
         """Row-by-row statement of the table-driven launch over host tensors (all-planes mode only).

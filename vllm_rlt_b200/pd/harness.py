@@ -31,14 +31,15 @@ MODES = {"exit_only": 2, "dedup": 1, "all": 0}
 POOL_LIMIT_BYTES = 165 << 30  # what one pool may take of a 180 GB GPU
 
 
-def make_workload(args, prefill_index: int, lengths=None):
+def make_workload(args, prefill_index: int, lengths=None, wave: int = 0):
     """The workload of one prefill worker; every rank can rebuild any worker's from its index.
 
     All workers get the same prompt lengths (those of worker 0), so that per-GPU work is identical at
-    every N (weak scaling); block tables and exit planes are seeded per worker. A workload whose source or
+    every N (weak scaling); block tables and exit planes are seeded per worker. ``wave`` selects one of several
+    independent draws, for workloads whose full request count does not fit the pools at once. A workload whose source or
     destination pool cannot fit one GPU is refused here, before anything is allocated.
     """
-    w = _make_workload(args, prefill_index, lengths)
+    w = _make_workload(args, prefill_index, lengths, wave)
     for side, blocks in (("source", w.src_blocks), ("destination", w.dst_blocks)):
         need = blocks * w.shape.block_bytes
         if need > POOL_LIMIT_BYTES:
@@ -47,12 +48,12 @@ def make_workload(args, prefill_index: int, lengths=None):
     return w
 
 
-def _make_workload(args, prefill_index: int, lengths=None):
+def _make_workload(args, prefill_index: int, lengths=None, wave: int = 0):
     from vllm_rlt_b200 import workloads as wl
 
     if lengths is None and prefill_index != 0:
-        lengths = _make_workload(args, 0).lengths
-    seed = wl.SEED_BASE + 1 + 17 * prefill_index
+        lengths = _make_workload(args, 0, None, wave).lengths
+    seed = wl.SEED_BASE + 1 + 17 * prefill_index + 1009 * wave  # a wave is another draw of the same distribution
     name = getattr(args, "workload", "ouro1p4b")
     if name == "ouro1p4b":
         return wl.last_exited_exit_only(wl.OURO_1P4B, requests=args.requests, mode=args.mode, seed=seed, lengths=lengths)

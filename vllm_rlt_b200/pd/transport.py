@@ -368,6 +368,16 @@ class CudaBackend:
                 keep.append(dev)
         return (host, *keep)
 
+    def copy_ranges(self, triples):
+        """A few plain (source, destination, bytes) ranges, one ``rlt_kv_push`` launch each: no descriptor table to
+        build, pin and upload, which matters for the single hidden-state row that rides on a chunk."""
+        from ..kernels import kv_handoff as kh
+
+        with self.torch.cuda.device(self.device), self._on_stream():
+            for src, dst, n in triples:
+                kh.kv_push(src, dst, n)
+        return ()
+
     def handoff(self, cache, peer_info, translate, requests, *, mode=0, layer_begin=0, layer_end=0,
                 plane_begin=0, plane_end=0, exit_planes=None, status=None, pull=False):
         """One table-driven launch for ``requests`` = [(source tables, target tables, start, end), ...], optionally
@@ -658,7 +668,7 @@ class B200Transport:
         keep = tuple(self.backend.handoff(self.cache, self.peers[peer], translate, requests, exit_planes=exit_planes,
                                           status=status, **where))
         if extra:
-            keep += tuple(self.backend.copy_segments([(s, translate(d, n), n) for s, d, n in extra]))
+            keep += tuple(self.backend.copy_ranges([(s, translate(d, n), n) for s, d, n in extra]))
         self._post(link, body)
         done = self.backend.event()
         for seq, n in parts:
@@ -696,7 +706,7 @@ class B200Transport:
         keep = tuple(self.backend.handoff(self.cache, self.peers[agent], translate, requests, pull=True, **where)) if requests else ()
         size = 0
         if extra:
-            keep += tuple(self.backend.copy_segments([(translate(s, n), d, n) for s, d, n in extra]))
+            keep += tuple(self.backend.copy_ranges([(translate(s, n), d, n) for s, d, n in extra]))
             size += sum(n for _, _, n in extra)
         layers = (where["layer_end"] or self.info["num_layers"]) - where["layer_begin"]
         row = self.info["token_bytes"] + (self.info["scale_region"]["token_bytes"] if self.info["scale_region"] else 0)
