@@ -636,6 +636,14 @@ def suite_kernels(args):
         ms = _timed(lambda: kh.kv_finalize(sv, tables, rows, status=status))
         report("finalize", "finalize_fan_kernel", (sources + copies) * ptb, ms, rows=len(rows), source_rows=sources,
                copied_rows=copies, note="each exit row with deeper planes is read once and written once per deeper plane")
+        # the same launch with every token leaving at plane 0: whole pages read from one block and written to three,
+        # no holes on any plane - separates the kernel's own overhead from the cost of the scattered pattern above
+        dense = rows.clone()
+        dense[:, 1] = 0
+        ms = _timed(lambda: kh.kv_finalize(sv, tables, dense, status=status))
+        report("finalize", "finalize_fan_kernel, every token exits at plane 0 (dense pages)", len(rows) * s.planes * ptb, ms,
+               rows=len(rows))
+        kh.kv_finalize(sv, tables, rows, status=status)  # restore the copies the dedup measurements below rely on
         few = rows[:256].contiguous()  # what one decode step finalizes
         ms = _timed(lambda: kh.kv_finalize(sv, tables, few, status=status))
         fe = exits[:256]
@@ -854,6 +862,10 @@ def suite_deployment(args):
         "bytes_sent": sent, "transfers": sum(m.get("transfers", 0) for m in worker_metrics.values()),
         "transfer_seconds_sum": seconds,
         "gbps_while_transferring": (sent / seconds / 1e9) if seconds else None, "startup_s": startup,
+        "pulled_bytes": sum(m.get("bytes_received", 0) for m in worker_metrics.values()),
+        "pull_device_seconds": sum(m.get("pull_seconds", 0.0) for m in worker_metrics.values()),
+        "pull_gbps_device_timed": (sum(m.get("bytes_received", 0) for m in worker_metrics.values())
+                                   / max(sum(m.get("pull_seconds", 0.0) for m in worker_metrics.values()), 1e-12) / 1e9),
         "marks_ms_from_prefill_started": [
             {k: round((v - t["prefill_started"]) * 1e3, 3) for k, v in t.items() if isinstance(v, float)} for t in marks[:4]],
     }), flush=True)

@@ -129,3 +129,50 @@ def test_pull_edges_agree_on_both_ends_for_every_split():
                     assert len({e["ready_slot"] for e in plans[d]}) == len(plans[d])
                     for e in plans[d]:
                         assert e["decode"] == d and e in plans[e["prefill"]]
+
+
+def _verify_worker(rank, world, port, out, damage):
+    """Rank 0 owns a source pool, rank 1 the destination after a handoff written with loops; they run the same
+    whole-transfer check the multi-GPU benchmark runs, over gloo instead of NCCL."""
+    import torch.distributed as dist
+
+    from tests.test_verify_cpu import SMALL, make_pool, plain_handoff
+    from vllm_rlt_b200 import workloads
+    from vllm_rlt_b200.pd import verify
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        w = workloads.last_exited_exit_only(SMALL, requests=3, min_len=5, max_len=19, partial_fraction=0.7, mode="dedup", seed=5)
+        src = make_pool(SMALL, w.src_blocks, SMALL.planes, seed=1)  # both ranks can build it: seeded
+        everything = list(range(len(w.lengths)))
+        if rank == 0:
+            ok, nbytes = verify.verify_over_group(src, True, [(1, w, everything, None)], mode="dedup", device="cpu")
+        else:
+            dst = make_pool(SMALL, w.dst_blocks, w.dst_planes, fill=verify.FILL_BYTE)
+            plain_handoff(src, dst, w, "dedup")
+            if damage:
+                dst.key_cache.view(torch.uint8)[int(w.dst_tables[0][0][0]), 0, 0, 0, 0] ^= 1
+            ok, nbytes = verify.verify_over_group(dst, False, [(0, w, everything, [w.dst_tables[i] for i in everything])],
+                                                  mode="dedup", device="cpu")
+        out.put((rank, ok, nbytes, w.payload_bytes))
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("damage", [False, True])
+def test_whole_transfer_verification_over_two_ranks(damage):
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_verify_worker, args=(r, 2, port, out, damage)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = sorted(out.get(timeout=180) for _ in range(2))
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for rank, ok, nbytes, payload in results:  # both ranks learn the same verdict and the same byte count
+        assert ok == (not damage)
+        assert nbytes == (0 if damage else payload)

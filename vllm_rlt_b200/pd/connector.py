@@ -241,8 +241,12 @@ class PDStageConnector:
             raise RuntimeError("cannot close a connector with pending transfers")
         self.transport.close()
         t = self.transport
-        return {"prefill_tokens": self.prefill_tokens, "bytes_sent": t.bytes_sent, "transfers": t.transfers,
-                "transfer_seconds": t.transfer_seconds}
+        metrics = {"prefill_tokens": self.prefill_tokens, "bytes_sent": t.bytes_sent, "transfers": t.transfers,
+                   "transfer_seconds": t.transfer_seconds}
+        received = getattr(t, "bytes_received", 0)
+        if isinstance(received, int) and received:  # the pull direction: what this worker's GPU read, and for how long
+            metrics.update(bytes_received=received, pull_seconds=t.pull_seconds)
+        return metrics
 
     # ------------------------------------------------------------------ StageConnector part
 

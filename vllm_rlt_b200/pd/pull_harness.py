@@ -14,6 +14,7 @@ that the copy runs on the decode GPU's SMs instead of the prefill GPU's.
 
 from __future__ import annotations
 
+import gc
 import json
 import os
 import random
@@ -449,6 +450,7 @@ def run_pull(args, rank: int, world: int) -> None:
     for wave in range(waves):
         line, lat = one_wave(wave)
         torch.cuda.synchronize()
+        gc.collect()  # the wave's closures form reference cycles that would keep its pools alive into the next wave
         torch.cuda.empty_cache()
         dist.barrier()
         if rank == 0:

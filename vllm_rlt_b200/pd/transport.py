@@ -436,6 +436,13 @@ class CudaBackend:
 
     marker = event  # an event at the current end of the transfer stream, used to tell when queued work begins
 
+    def timed_event(self):
+        """Like ``event`` but usable with ``elapsed_time`` (device time between two of them)."""
+        ev = self.torch.cuda.Event(enable_timing=True)
+        with self.torch.cuda.device(self.device):
+            ev.record(self.stream)
+        return ev
+
     def close(self):
         from .. import _lib
 
@@ -476,6 +483,7 @@ class _Pull:
     keepalive: tuple = ()
     reported: bool = False  # (peer, tid, seq) has been handed to the connector; "pulled" may still be unsent
     count: int = 1          # consecutive sequence numbers the launch covers
+    begun: object = None    # timing event recorded before the launch (backends that can time on the device)
 
 
 def default_direction() -> str:
@@ -534,6 +542,7 @@ class B200Transport:
         self.inflight_bytes = 0
         self.bytes_sent = 0
         self.bytes_received = 0
+        self.pull_seconds = 0.0  # device time this worker's GPU spent reading peers' pools
         self.transfers = 0
         self.transfer_seconds = 0.0
         # RLT_KV_TRACE=<directory>: every step of every chunk with the host's monotonic clock (which all processes of
@@ -703,6 +712,8 @@ class B200Transport:
         requests, extra, where = decode_chunk(message.descriptor)
         link = self._peer_link(agent)
         translate = link["translate"]
+        timed = getattr(self.backend, "timed_event", None)
+        begun = timed() if timed is not None else None
         keep = tuple(self.backend.handoff(self.cache, self.peers[agent], translate, requests, pull=True, **where)) if requests else ()
         size = 0
         if extra:
@@ -713,8 +724,9 @@ class B200Transport:
         for _, target, start, end in requests:
             planes = (where["plane_end"] or len(target)) - where["plane_begin"]
             size += (end - start) * planes * 2 * layers * row
-        self._pulls.append(_Pull(self.backend.event(), agent, message.transfer_id, message.sequence, size, keep,
-                                 count=message.count))
+        done = timed() if timed is not None else self.backend.event()
+        self._pulls.append(_Pull(done, agent, message.transfer_id, message.sequence, size, keep, count=message.count,
+                                 begun=begun))
         self._note("pull launched", message.transfer_id, message.sequence)
 
     def poll(self):
@@ -741,6 +753,8 @@ class B200Transport:
                 pull.keepalive = ()
                 self._note("pull finished", pull.transfer_id, pull.sequence)
                 self.bytes_received += pull.size
+                if pull.begun is not None:
+                    self.pull_seconds += pull.begun.elapsed_time(pull.event) * 1e-3  # device time of the launch(es)
                 notifications += [(pull.peer, pull.transfer_id, pull.sequence + k) for k in range(pull.count)]
             if pull.reported:
                 link = self._peer_link(pull.peer)
