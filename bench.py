@@ -633,22 +633,45 @@ def suite_kernels(args):
     copies = int((s.planes - 1 - exits).sum())
     sources = int((exits < s.planes - 1).sum())
     if wanted("finalize"):
+        # Finalize writes two to three rows for each one it reads, and HBM takes writes more slowly than the mix of
+        # the copy the peak was measured with. The same volume as pure writes (the library memset) is timed first;
+        # each finalize line carries its own write rate next to it.
+        scratch = dst.key_cache.view(torch.uint8).reshape(-1)
+        size = min(scratch.numel(), 3 << 30)
+        ms = _timed(lambda: scratch[:size].zero_())
+        write_rate = size / ms / 1e6
+        report("finalize", "context: Tensor.zero_ of 3 GiB (writes only)", size, ms)
+        # one read, three writes of contiguous data by a library kernel: each 64 KiB run of the source is broadcast into
+        # three adjacent runs of the output (the second and third read of a run come from cache)
+        run = 1 << 16
+        runs = min(size // (3 * run), src.key_cache.numel() * 2 // run)
+        fan_src = src.key_cache.view(torch.uint8).reshape(-1)[: runs * run].view(runs, 1, run)
+        fan_dst = scratch[: runs * 3 * run].view(runs, 3, run)
+        ms = _timed(lambda: fan_dst.copy_(fan_src.expand(runs, 3, run)))
+        report("finalize", "context: Tensor.copy_ of 64 KiB runs broadcast to three (1 read : 3 writes, contiguous)",
+               4 * runs * run, ms, written_gbps=round(3 * runs * run / ms / 1e6, 1))
+
+        def finalize_line(name, read_rows, written_rows, ms, **extra):
+            written = written_rows * ptb / ms / 1e6
+            report("finalize", name, (read_rows + written_rows) * ptb, ms, written_gbps=round(written, 1),
+                   memset_write_gbps=round(write_rate, 1), written_over_memset=round(written / write_rate, 3), **extra)
+
         ms = _timed(lambda: kh.kv_finalize(sv, tables, rows, status=status))
-        report("finalize", "finalize_fan_kernel", (sources + copies) * ptb, ms, rows=len(rows), source_rows=sources,
-               copied_rows=copies, note="each exit row with deeper planes is read once and written once per deeper plane")
+        finalize_line("finalize_fan_kernel", sources, copies, ms, rows=len(rows), source_rows=sources, copied_rows=copies,
+                      note="each exit row with deeper planes is read once and written once per deeper plane")
         # the same launch with every token leaving at plane 0: whole pages read from one block and written to three,
-        # no holes on any plane - separates the kernel's own overhead from the cost of the scattered pattern above
+        # no holes on any plane - separates the cost of the scattered pattern above from the kernel's own
         dense = rows.clone()
         dense[:, 1] = 0
         ms = _timed(lambda: kh.kv_finalize(sv, tables, dense, status=status))
-        report("finalize", "finalize_fan_kernel, every token exits at plane 0 (dense pages)", len(rows) * s.planes * ptb, ms,
-               rows=len(rows))
+        finalize_line("finalize_fan_kernel, every token exits at plane 0 (dense pages)", len(rows),
+                      len(rows) * (s.planes - 1), ms, rows=len(rows))
         kh.kv_finalize(sv, tables, rows, status=status)  # restore the copies the dedup measurements below rely on
         few = rows[:256].contiguous()  # what one decode step finalizes
         ms = _timed(lambda: kh.kv_finalize(sv, tables, few, status=status))
         fe = exits[:256]
-        report("finalize", "finalize_fan_kernel (256 rows, one decode step)",
-               (int((fe < s.planes - 1).sum()) + int((s.planes - 1 - fe).sum())) * ptb, ms, rows=256)
+        finalize_line("finalize_fan_kernel (256 rows, one decode step)", int((fe < s.planes - 1).sum()),
+                      int((s.planes - 1 - fe).sum()), ms, rows=256)
     else:
         kh.kv_finalize(sv, tables, rows, status=status)
 
@@ -864,8 +887,8 @@ def suite_deployment(args):
         "gbps_while_transferring": (sent / seconds / 1e9) if seconds else None, "startup_s": startup,
         "pulled_bytes": sum(m.get("bytes_received", 0) for m in worker_metrics.values()),
         "pull_device_seconds": sum(m.get("pull_seconds", 0.0) for m in worker_metrics.values()),
-        "pull_gbps_device_timed": (sum(m.get("bytes_received", 0) for m in worker_metrics.values())
-                                   / max(sum(m.get("pull_seconds", 0.0) for m in worker_metrics.values()), 1e-12) / 1e9),
+        # median over the pull launches of the run (the first one of a process carries the module load)
+        "pull_gbps_p50_device_timed": max((m.get("pull_gbps_p50", 0.0) for m in worker_metrics.values()), default=0.0),
         "marks_ms_from_prefill_started": [
             {k: round((v - t["prefill_started"]) * 1e3, 3) for k, v in t.items() if isinstance(v, float)} for t in marks[:4]],
     }), flush=True)

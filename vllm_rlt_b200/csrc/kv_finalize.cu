@@ -14,7 +14,6 @@
 // plane. Pools with more than kFanPlanes planes use the older kernel, whose unit is
 // (row, target plane, tensor) and which reads the row once per target.
 
-#include <cstdlib>
 
 #include "common.cuh"
 
@@ -40,7 +39,6 @@ struct FinalizeParams {
   const int* rows;                // [n][3]: request index, exit plane, token position
   int n;
   int group_rows;                 // rows of one page taken together: at most kGroupRows, fewer for very long rows
-  int bulk;                       // move long rows with the bulk-copy engine (shared-memory rings) instead of registers
   int* status;
 };
 
@@ -209,126 +207,7 @@ __device__ __forceinline__ void fan_group_rows(const FinalizeRegion& rg, const G
 }
 
 // ---------------------------------------------------------------------------------------------
-// The same (piece, row) jobs moved by the bulk-copy engine instead of through registers: a 4 KiB row is loaded into
-// shared memory once with cp.async.bulk and stored from there to every deeper plane with one bulk store per plane,
-// so the fan-out costs no register traffic and almost no instructions. Every warp owns a ring of kFanStages stages
-// tracked by mbarriers; lane 0 drives it (loads run kFanLag jobs ahead of the stores), and every wait is bounded:
-// a load that never lands is reported as RLT_STATUS_STALL and the warp stops.
-constexpr int kFanStages = 6;
-constexpr int kFanLag = 4;
-constexpr int kFanStageBytes = 4096;
-
-struct FanRing {
-  unsigned long long full[kFanStages];    // mbarriers: "the load into this stage has landed"
-  long long in_block[kFanStages];         // byte offset of the staged piece inside a plane's block
-  int bytes[kFanStages];
-  short exit_plane[kFanStages];
-  short kv[kFanStages];
-};
-
-__device__ __forceinline__ unsigned fan_smem(const void* p) { return static_cast<unsigned>(__cvta_generic_to_shared(p)); }
-
-__device__ __forceinline__ bool fan_wait(unsigned long long* bar, int parity) {
-  const unsigned addr = fan_smem(bar);
-  for (int spin = 0; spin < (1 << 22); ++spin) {
-    unsigned done;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(done)
-        : "r"(addr), "r"(parity)
-        : "memory");
-    if (done) return true;
-  }
-  return false;
-}
-
-struct FanWorker {
-  FanRing* ring;
-  unsigned char* stages;
-  long long issued;    // jobs whose load was issued
-  long long finished;  // jobs whose stores were issued (job k's stores form bulk group k)
-  bool dead;
-
-  // job k's load has landed: store its stage to every deeper plane, one commit group for the stage
-  __device__ __forceinline__ void finish(long long k, const FinalizeRegion& rg, const long long* plane_off, int planes) {
-    const int s = static_cast<int>(k % kFanStages);
-    if (!fan_wait(&ring->full[s], static_cast<int>((k / kFanStages) & 1))) {
-      dead = true;
-      return;
-    }
-    char* pool = ring->kv[s] ? rg.value : rg.key;
-    const unsigned src = fan_smem(stages + static_cast<size_t>(s) * kFanStageBytes);
-    for (int t = ring->exit_plane[s] + 1; t < planes; ++t) {
-      const long long pb = plane_off[t];
-      if (pb < 0) continue;
-      asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(pool + pb + ring->in_block[s]),
-                   "r"(src), "r"(ring->bytes[s])
-                   : "memory");
-    }
-    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-  }
-
-  __device__ __forceinline__ void emit(const char* src, long long in_block, int bytes, int exit_plane, int kv,
-                                       const FinalizeRegion& rg, const long long* plane_off, int planes) {
-    if (dead) return;
-    const int s = static_cast<int>(issued % kFanStages);
-    if (issued >= kFanStages) {
-      // the stores of job issued - kFanStages (bulk group of that number) must have read the stage. At least
-      // issued - kFanLag groups exist, so letting kFanStages - kFanLag - 1 younger ones stay pending is enough.
-      asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(kFanStages - kFanLag - 1) : "memory");
-    }
-    ring->in_block[s] = in_block;
-    ring->bytes[s] = bytes;
-    ring->exit_plane[s] = static_cast<short>(exit_plane);
-    ring->kv[s] = static_cast<short>(kv);
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(fan_smem(&ring->full[s])), "r"(bytes) : "memory");
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-                     fan_smem(stages + static_cast<size_t>(s) * kFanStageBytes)),
-                 "l"(src), "r"(bytes), "r"(fan_smem(&ring->full[s]))
-                 : "memory");
-    ++issued;
-    if (issued - finished > kFanLag) finish(finished++, rg, plane_off, planes);
-  }
-
-  // everything issued so far has been stored and the stores have read their stages: the group's tables may change
-  __device__ __forceinline__ void drain(const FinalizeRegion& rg, const long long* plane_off, int planes) {
-    while (finished < issued && !dead) finish(finished++, rg, plane_off, planes);
-    asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-  }
-};
-
-// Pieces [a, b) of every carried row of a group for a region with 16-byte aligned rows, by bulk copies. Jobs are dealt to
-// the warps round-robin in (piece, row) order; rows longer than a stage go in several parts.
-__device__ __forceinline__ void fan_group_bulk(FanWorker& w, const FinalizeRegion& rg, const GroupTables& gt, int g, int planes,
-                                               const int* layer_of, int layers, int a, int b) {
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  if (lane != 0) return;
-  const int carried = gt.carried;
-  const int jobs = (b - a) * carried;
-  const int row_bytes = static_cast<int>(rg.token_bytes);
-  for (int job = warp; job < jobs; job += kThreads / 32) {
-    const int piece_rel = gt.magic ? static_cast<int>(__umulhi(static_cast<unsigned>(job), gt.magic)) : job;
-    const int r = job - piece_rel * carried;
-    const int piece = a + piece_rel;
-    const int kv = piece >= layers;
-    const int e = gt.exit_plane[r];
-    const long long src_block = gt.plane_off[g][e];
-    if (src_block < 0) continue;
-    const char* pool = kv ? rg.value : rg.key;
-    const long long in_block = layer_of[piece - kv * layers] * rg.layer_bytes + gt.tok_off[g][r];
-    for (int off = 0; off < row_bytes; off += kFanStageBytes) {
-      const int n = min(kFanStageBytes, row_bytes - off);
-      w.emit(pool + src_block + in_block + off, in_block + off, n, e, kv, rg, gt.plane_off[g], planes);
-    }
-  }
-  // the stages refer to this group's tables: finish them before the caller moves on
-  w.drain(rg, gt.plane_off[g], planes);
-}
-
-template <bool kBulk>
-__global__ void __launch_bounds__(kThreads, kBulk ? 1 : 3) finalize_fan_kernel(const FinalizeParams p) {
+__global__ void __launch_bounds__(kThreads, 3) finalize_fan_kernel(const FinalizeParams p) {
   __shared__ int layer_of[64];  // the selected layers, in order
   __shared__ int n_selected;
   __shared__ long long slice_start[kThreads + 1];  // cost of all rows before each thread's slice; [kThreads] = total
@@ -336,22 +215,8 @@ __global__ void __launch_bounds__(kThreads, kBulk ? 1 : 3) finalize_fan_kernel(c
   __shared__ int cut_row[2];        // first row of this CTA's share, and the row its share ends in
   __shared__ long long cut_rem[2];  // (cost x pieces) of that row that lies before the cut
   __shared__ GroupTables tables[2];  // double buffered: the next group's are written while this one streams
-  extern __shared__ __align__(128) unsigned char fan_stages[];  // bulk path: kFanStages x kFanStageBytes per warp
-  __shared__ FanRing rings[kThreads / 32];
   const int tid = static_cast<int>(threadIdx.x);
   const int lane = tid & 31, warp = tid >> 5;
-  FanWorker worker;
-  worker.ring = &rings[warp];
-  worker.stages = fan_stages + static_cast<size_t>(warp) * kFanStages * kFanStageBytes;
-  worker.issued = 0;
-  worker.finished = 0;
-  worker.dead = false;
-  if (kBulk && lane == 0) {
-    for (int s = 0; s < kFanStages; ++s)
-      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(fan_smem(&worker.ring->full[s])), "r"(1) : "memory");
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-  }
   if (tid == 0) {
     int n = 0;
     for (int layer = 0; layer < p.num_layers; ++layer) {
@@ -509,9 +374,7 @@ __global__ void __launch_bounds__(kThreads, kBulk ? 1 : 3) finalize_fan_kernel(c
         const int a = max(lo - g * pieces_per_region, 0), b = min(hi - g * pieces_per_region, pieces_per_region);
         if (a >= b) continue;
         const FinalizeRegion& rg = p.region[g];
-        if (kBulk && rg.vec_bytes == 16 && rg.token_bytes >= 512) {
-          fan_group_bulk(worker, rg, gt, g, p.planes, layer_of, layers, a, b);
-        } else if (rg.vec_bytes == 16 && rg.row_vecs >= 32) {
+        if (rg.vec_bytes == 16 && rg.row_vecs >= 32) {
           fan_group_rows(rg, gt, g, p.planes, layer_of, layers, a, b);
         } else if (rg.vec_bytes == 16) {
           fan_group<uint4>(rg, gt, g, p.planes, layer_of, layers, a, b);
@@ -526,10 +389,6 @@ __global__ void __launch_bounds__(kThreads, kBulk ? 1 : 3) finalize_fan_kernel(c
     __syncthreads();  // the next group's tables are visible; this group's buffer is free for the one after
     parity ^= 1;
     start = next;
-  }
-  if (kBulk && lane == 0) {
-    asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
-    if (worker.dead) report(p.status, RLT_STATUS_STALL, static_cast<int>(blockIdx.x), warp, 0);
   }
 }
 
@@ -646,16 +505,7 @@ int rlt_kv_finalize(const RltPool* pool, const int32_t* tables, int32_t num_requ
   if (fan) {
     // one persistent wave of three CTAs per SM; a CTA's share may be a fraction of a row, so small batches
     // still use every SM (a share of less than one (tensor, layer) piece is simply empty)
-    static const int use_bulk = [] { const char* e = getenv("RLT_FINALIZE_BULK"); return e ? atoi(e) : 0; }();  // EXPERIMENT
-    p.bulk = use_bulk;
-    const size_t ring_bytes = p.bulk ? static_cast<size_t>(rlt::kThreads / 32) * rlt::kFanStages * rlt::kFanStageBytes : 0;
-    if (p.bulk) {  // 192 KiB of stages per CTA: one CTA per SM
-      RLT_CUDA_TRY(cudaFuncSetAttribute(rlt::finalize_fan_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        static_cast<int>(ring_bytes)));
-      rlt::finalize_fan_kernel<true><<<sms, rlt::kThreads, ring_bytes, reinterpret_cast<cudaStream_t>(stream)>>>(p);
-    } else {
-      rlt::finalize_fan_kernel<false><<<sms * 3, rlt::kThreads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(p);
-    }
+    rlt::finalize_fan_kernel<<<sms * 3, rlt::kThreads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(p);
   } else {
     rlt::finalize_kernel<<<grid, rlt::kThreads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(p);
   }

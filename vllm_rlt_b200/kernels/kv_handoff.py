@@ -199,8 +199,8 @@ class HandoffBatch:
             raise ValueError("invalid KV range")
         self.ranges = [(int(s), int(e)) for s, e in bounds]
         self.total_tokens = int((end - begin).sum())
-        # Per side: every table row of every request, its length, and one flat int32 array of all entries in
-        # (request, plane, page) order. The checks are those of the reference's planner, done on whole arrays.
+        # Per side: one int32 array [requests, planes, pages], zero-padded to the longest table. The checks are those of
+        # the reference's planner, done on whole arrays.
         sides, width = [], 1
         for tables, limit in ((src_tables, src_blocks), (dst_tables, dst_blocks)):
             if tables is None:
@@ -211,42 +211,54 @@ class HandoffBatch:
             planes = len(tables[0])
             if any(len(req) != planes for req in tables):
                 raise ValueError("requests of one batch must have the same number of planes")
-            rows = [table for req in tables for table in req]
-            lens = np.fromiter(map(len, rows), np.int64, count=n * planes).reshape(n, planes)
-            pages = lens[:, 0]
-            if (end > lens.min(axis=1) * block_size).any():
-                raise ValueError("KV range exceeds allocation")
-            if (lens != pages[:, None]).any():
-                raise ValueError("the planes of one request must have tables of equal length")
-            total = int(lens.sum())
-            if isinstance(rows[0], np.ndarray):
-                flat = np.concatenate(rows).astype(np.int32, copy=False)
+            pages0 = len(tables[0][0])
+            if all(len(table) == pages0 for req in tables for table in req):
+                # tables of one length (a single request, or a chunk's trimmed tables): one conversion, no padding
+                padded = np.asarray(tables, dtype=np.int32).reshape(n, planes, pages0)
+                if (end > pages0 * block_size).any():
+                    raise ValueError("KV range exceeds allocation")
+                pages_max = pages0
             else:
-                flat = np.fromiter((b for table in rows for b in table), np.int32, count=total)
-            width = max(width, int(pages.max()))
-            sides.append((flat, planes, lens.reshape(-1), limit))
+                rows = [table for req in tables for table in req]
+                lens = np.fromiter(map(len, rows), np.int64, count=n * planes).reshape(n, planes)
+                pages = lens[:, 0]
+                if (end > lens.min(axis=1) * block_size).any():
+                    raise ValueError("KV range exceeds allocation")
+                if (lens != pages[:, None]).any():
+                    raise ValueError("the planes of one request must have tables of equal length")
+                total = int(lens.sum())
+                if isinstance(rows[0], np.ndarray):
+                    flat = np.concatenate(rows).astype(np.int32, copy=False)
+                else:
+                    flat = np.fromiter((b for table in rows for b in table), np.int32, count=total)
+                pages_max = int(pages.max())
+                padded = np.zeros((n, planes, pages_max), np.int32)
+                # a boolean mask is filled in row-major order, which is the order of the flat array
+                padded.reshape(n * planes, pages_max)[np.arange(pages_max) < lens.reshape(-1)[:, None]] = flat
+            width = max(width, pages_max)
+            sides.append((padded, limit))
         self.table_width = width
         arrays = []
-        first, last = begin // block_size, (end - 1) // block_size
         used = None
         for side in sides:
             if side is None:
                 arrays.append(None)
                 continue
-            flat, planes, row_len, limit = side
-            a = np.zeros((n, planes, width), np.int32)
-            # a boolean mask is filled in row-major order, which is the order of the flat array
-            a.reshape(n * planes, width)[np.arange(width) < row_len[:, None]] = flat
+            a, limit = side
+            if a.shape[2] < width:  # the two sides share one width
+                wider = np.zeros((n, a.shape[1], width), np.int32)
+                wider[:, :, : a.shape[2]] = a
+                a = wider
             # negative ids compare as huge unsigned numbers; the padding (0) is a valid id, so the mask of
             # pages that the ranges touch is only needed when something looks wrong
             bad = a < 0 if limit is None else a.view(np.uint32) >= limit
             if bad.any():
                 if used is None:
                     cols = np.arange(width)
-                    used = (cols >= first[:, None]) & (cols <= last[:, None])
+                    used = (cols >= (begin // block_size)[:, None]) & (cols <= ((end - 1) // block_size)[:, None])
                 if (bad & used[:, None, :]).any():
                     raise ValueError("physical block outside registered pool")
-            arrays.append(a)
+            arrays.append(np.ascontiguousarray(a))
         self.src_planes = arrays[0].shape[1] if arrays[0] is not None else 0
         self.dst_planes = arrays[1].shape[1] if arrays[1] is not None else 0
         exit_parts = offsets = None

@@ -245,7 +245,9 @@ class PDStageConnector:
                    "transfer_seconds": t.transfer_seconds}
         received = getattr(t, "bytes_received", 0)
         if isinstance(received, int) and received:  # the pull direction: what this worker's GPU read, and for how long
-            metrics.update(bytes_received=received, pull_seconds=t.pull_seconds)
+            rates = sorted(getattr(t, "pull_rates", ()))
+            metrics.update(bytes_received=received, pull_seconds=t.pull_seconds,
+                           pull_gbps_p50=rates[len(rates) // 2] if rates else 0.0)
         return metrics
 
     # ------------------------------------------------------------------ StageConnector part
@@ -742,6 +744,7 @@ class Importer:
             raise RuntimeError("unexpected transfer sequence")
         if len(t.received) < t.expected:
             return
+        c._trace("all chunks landed", t.tid)
         if not c.engine.accept_import(t.request, c.hidden[t.slot], cached_tokens=t.cached_tokens):
             raise RuntimeError("stale import activation")
         t.ready = True

@@ -40,6 +40,8 @@ def make_workload(args, prefill_index: int, lengths=None, wave: int = 0):
     destination pool cannot fit one GPU is refused here, before anything is allocated.
     """
     w = _make_workload(args, prefill_index, lengths, wave)
+    if w.exit_planes is None and getattr(args, "mode", "all") != "all":
+        raise SystemExit(f"workload {getattr(args, 'workload', 'ouro1p4b')!r} has no per-token exit planes: run it with --mode all")
     for side, blocks in (("source", w.src_blocks), ("destination", w.dst_blocks)):
         need = blocks * w.shape.block_bytes
         if need > POOL_LIMIT_BYTES:

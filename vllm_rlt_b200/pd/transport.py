@@ -543,6 +543,7 @@ class B200Transport:
         self.bytes_sent = 0
         self.bytes_received = 0
         self.pull_seconds = 0.0  # device time this worker's GPU spent reading peers' pools
+        self.pull_rates: deque[float] = deque(maxlen=4096)  # GB/s of each pull launch, device-timed
         self.transfers = 0
         self.transfer_seconds = 0.0
         # RLT_KV_TRACE=<directory>: every step of every chunk with the host's monotonic clock (which all processes of
@@ -714,7 +715,9 @@ class B200Transport:
         translate = link["translate"]
         timed = getattr(self.backend, "timed_event", None)
         begun = timed() if timed is not None else None
+        self._note("pull decoded", message.transfer_id, message.sequence)
         keep = tuple(self.backend.handoff(self.cache, self.peers[agent], translate, requests, pull=True, **where)) if requests else ()
+        self._note("pull tables launched", message.transfer_id, message.sequence)
         size = 0
         if extra:
             keep += tuple(self.backend.copy_ranges([(translate(s, n), d, n) for s, d, n in extra]))
@@ -736,6 +739,7 @@ class B200Transport:
         for lane, agent in self._lane_agent.items():
             for message in self.mailbox.drain(lane):
                 if message.kind == LANDED:
+                    self._note("landed seen", message.transfer_id, message.sequence)
                     notifications += [(agent, message.transfer_id, message.sequence + k) for k in range(message.count)]
                 elif message.kind == OFFER:
                     self._note("offer seen", message.transfer_id, message.sequence)
@@ -754,7 +758,10 @@ class B200Transport:
                 self._note("pull finished", pull.transfer_id, pull.sequence)
                 self.bytes_received += pull.size
                 if pull.begun is not None:
-                    self.pull_seconds += pull.begun.elapsed_time(pull.event) * 1e-3  # device time of the launch(es)
+                    seconds = pull.begun.elapsed_time(pull.event) * 1e-3  # device time of the launch(es)
+                    self.pull_seconds += seconds
+                    if seconds > 0:
+                        self.pull_rates.append(pull.size / seconds / 1e9)
                 notifications += [(pull.peer, pull.transfer_id, pull.sequence + k) for k in range(pull.count)]
             if pull.reported:
                 link = self._peer_link(pull.peer)
