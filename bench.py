@@ -641,15 +641,6 @@ def suite_kernels(args):
         ms = _timed(lambda: scratch[:size].zero_())
         write_rate = size / ms / 1e6
         report("finalize", "context: Tensor.zero_ of 3 GiB (writes only)", size, ms)
-        # one read, three writes of contiguous data by a library kernel: each 64 KiB run of the source is broadcast into
-        # three adjacent runs of the output (the second and third read of a run come from cache)
-        run = 1 << 16
-        runs = min(size // (3 * run), src.key_cache.numel() * 2 // run)
-        fan_src = src.key_cache.view(torch.uint8).reshape(-1)[: runs * run].view(runs, 1, run)
-        fan_dst = scratch[: runs * 3 * run].view(runs, 3, run)
-        ms = _timed(lambda: fan_dst.copy_(fan_src.expand(runs, 3, run)))
-        report("finalize", "context: Tensor.copy_ of 64 KiB runs broadcast to three (1 read : 3 writes, contiguous)",
-               4 * runs * run, ms, written_gbps=round(3 * runs * run / ms / 1e6, 1))
 
         def finalize_line(name, read_rows, written_rows, ms, **extra):
             written = written_rows * ptb / ms / 1e6
@@ -666,6 +657,11 @@ def suite_kernels(args):
         ms = _timed(lambda: kh.kv_finalize(sv, tables, dense, status=status))
         finalize_line("finalize_fan_kernel, every token exits at plane 0 (dense pages)", len(rows),
                       len(rows) * (s.planes - 1), ms, rows=len(rows))
+        # and with every token leaving at plane 1: the same 1 : 2 mix of reads and writes as the U{0..3} launch, on whole pages
+        dense[:, 1] = 1
+        ms = _timed(lambda: kh.kv_finalize(sv, tables, dense, status=status))
+        finalize_line("finalize_fan_kernel, every token exits at plane 1 (dense pages, 1 read : 2 writes)", len(rows),
+                      len(rows) * (s.planes - 2), ms, rows=len(rows))
         kh.kv_finalize(sv, tables, rows, status=status)  # restore the copies the dedup measurements below rely on
         few = rows[:256].contiguous()  # what one decode step finalizes
         ms = _timed(lambda: kh.kv_finalize(sv, tables, few, status=status))

@@ -59,10 +59,12 @@ class FakeBackend:
     copy_ranges = copy_segments
 
     def handoff(self, cache, peer_info, translate, requests, *, mode=0, layer_begin=0, layer_end=0,
-                plane_begin=0, plane_end=0, exit_planes=None, status=None, pull=False):
+                plane_begin=0, plane_end=0, exit_planes=None, status=None, pull=False, before_launch=None):
         """Row-by-row statement of the table-driven launch over host tensors (all-planes mode only).
         ``pull``: the peer's memory is the source and the local tensors the destination."""
         assert mode == 0 and exit_planes is None
+        if before_launch is not None:
+            before_launch()
         page, layers = cache.block_size, cache.num_layers
         layer_end = layer_end or layers
         pairs = [(cache.key_cache, "key_ptr", peer_info), (cache.value_cache, "value_ptr", peer_info)]

@@ -73,6 +73,36 @@ def test_handoff_equals_reference_destination(case, batched, variant):
 
 
 @pytest.mark.parametrize("case", golden_json("handoff.json"), ids=lambda c: c["name"])
+@pytest.mark.parametrize("longer", ["source", "destination"])
+def test_tables_of_one_length_per_side_with_sides_of_different_length(case, longer):
+    """Requests sent one at a time have tables of one length per side, which the batch converts in one step; a side
+    whose tables run past the range (pages a later chunk will use) must not change what is copied."""
+    k = kh()
+    arrays = golden_npz(case["name"])
+    P = oracle_pool(case["kind"], case["shape"])
+    D = oracle_pool(case["kind"], case["shape"], device=1, base=1 << 40)
+    load_pool(P, arrays, "src_")
+    load_pool(D, arrays, "dst_before_")
+    gp, gd = GpuPool(P), GpuPool(D)
+    status = k.new_status()
+    for r in case["requests"]:
+        src = [np.asarray(t, np.int32) for t in r["src_tables"]]
+        dst = [np.asarray(t, np.int32) for t in r["dst_tables"]]
+        pad = np.zeros(3, np.int32)  # block 0 is a valid id; the range never reaches these pages
+        if longer == "source":
+            src = [np.concatenate([t, pad]) for t in src]
+        else:
+            dst = [np.concatenate([t, pad]) for t in dst]
+        batch = k.HandoffBatch([src], [dst], [(r["start"], r["end"])], block_size=P.block_size,
+                               src_blocks=P.num_blocks, dst_blocks=D.num_blocks)
+        assert batch.table_width == max(len(src[0]), len(dst[0]))
+        k.kv_handoff(gp.view(), gd.view(), batch, status=status)
+    k.raise_for_status(status)
+    load_pool(D, arrays, "dst_after_")
+    assert_pools_equal(gd, D)
+
+
+@pytest.mark.parametrize("case", golden_json("handoff.json"), ids=lambda c: c["name"])
 @pytest.mark.parametrize("variant", VARIANTS)
 def test_pack_equals_reference_wire_and_scatter_inverts_it(case, variant):
     k = kh()

@@ -379,7 +379,7 @@ class CudaBackend:
         return ()
 
     def handoff(self, cache, peer_info, translate, requests, *, mode=0, layer_begin=0, layer_end=0,
-                plane_begin=0, plane_end=0, exit_planes=None, status=None, pull=False):
+                plane_begin=0, plane_end=0, exit_planes=None, status=None, pull=False, before_launch=None):
         """One table-driven launch for ``requests`` = [(source tables, target tables, start, end), ...], optionally
         of one slice of layers and destination planes (0, 0 = all).
 
@@ -415,6 +415,8 @@ class CudaBackend:
                 [r[0] for r in requests], [r[1] for r in requests], [(r[2], r[3]) for r in requests],
                 block_size=src.block_size, exit_planes=exit_planes, src_blocks=src.num_blocks,
                 dst_blocks=dst.num_blocks, device=self.device)
+            if before_launch is not None:
+                before_launch()  # the tables are staged: what follows is the launch itself
             kh.kv_handoff(src, dst, batch, mode=mode, layer_begin=layer_begin, layer_end=layer_end,
                           plane_begin=plane_begin, plane_end=plane_end, status=status)
         return (batch,)
@@ -714,9 +716,20 @@ class B200Transport:
         link = self._peer_link(agent)
         translate = link["translate"]
         timed = getattr(self.backend, "timed_event", None)
-        begun = timed() if timed is not None else None
+        begun = None
+
+        def staged():  # called between staging the tables and the launch: device time counts from here
+            nonlocal begun
+            begun = timed() if timed is not None else None
+            self._note("pull tables staged", message.transfer_id, message.sequence)
+
         self._note("pull decoded", message.transfer_id, message.sequence)
-        keep = tuple(self.backend.handoff(self.cache, self.peers[agent], translate, requests, pull=True, **where)) if requests else ()
+        keep = ()
+        if requests:
+            keep = tuple(self.backend.handoff(self.cache, self.peers[agent], translate, requests, pull=True,
+                                              before_launch=staged, **where))
+        elif timed is not None:
+            begun = timed()
         self._note("pull tables launched", message.transfer_id, message.sequence)
         size = 0
         if extra:
