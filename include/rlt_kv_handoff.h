@@ -169,6 +169,36 @@ RLT_API int rlt_kv_handoff(const RltPool* src, const RltPool* dst, const RltBatc
                            const RltOptions* options, rlt_stream_t stream);
 
 /*
+ * rlt_kv_handoff in RLT_MODE_ALL_PLANES for a caller whose block tables are still in HOST memory: the call copies
+ * them into a staging slot of the library (pinned host memory and device memory, 16 slots of 64 KiB per GPU,
+ * allocated at the first call on that GPU), queues the host-to-device copy and the launch on `stream`, and returns.
+ * The arrays may be changed or freed as soon as it has returned. A batch whose tables and ranges exceed
+ * rlt_kv_host_batch_limit() bytes gets RLT_E_LIMIT and nothing is queued: stage such a batch yourself and call
+ * rlt_kv_handoff. When all 16 slots belong to launches that have not finished, the call waits for the oldest.
+ *
+ * This is what a transfer worker calls per chunk: one request, tables of a few hundred entries, where the time to
+ * stage them decides how soon after the producer's event the copy starts. It takes the place of the descriptor
+ * lists NixlConnector.submit builds per chunk on the host (vllm_rlt/pd/transport.py:182-201 over kv_segments,
+ * :29-63); block ids and ranges are checked on the device like in rlt_kv_handoff.
+ */
+typedef struct RltHostBatch {
+  int32_t num_requests;      /* 1..RLT_MAX_REQUESTS                                  */
+  int32_t table_width;       /* entries per table row, the same on both sides        */
+  int32_t src_planes;        /* rows per request in src_tables = src->num_planes     */
+  int32_t dst_planes;        /* rows per request in dst_tables = dst->num_planes     */
+  const int32_t* src_tables; /* HOST [num_requests, src_planes, table_width]         */
+  const int32_t* dst_tables; /* HOST [num_requests, dst_planes, table_width]         */
+  const int32_t* tok_begin;  /* HOST [num_requests]                                  */
+  const int32_t* tok_end;    /* HOST [num_requests]                                  */
+} RltHostBatch;
+
+RLT_API int rlt_kv_handoff_host(const RltPool* src, const RltPool* dst, const RltHostBatch* batch,
+                                const RltOptions* options, rlt_stream_t stream);
+
+/* Largest sum of table and range bytes rlt_kv_handoff_host accepts. */
+RLT_API int64_t rlt_kv_host_batch_limit(void);
+
+/*
  * Bytes of the packed wire image of a batch: total_tokens * planes * 2 *
  * layers * (codes row + scales row). Host-side arithmetic only.
  */

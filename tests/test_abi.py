@@ -32,7 +32,7 @@ def test_header_and_ctypes_agree_on_the_symbol_list(lib):
     from vllm_rlt_b200 import _lib
 
     names = declared_symbols()
-    assert len(names) >= 26
+    assert len(names) >= 28
     assert names == sorted(_lib.SIGNATURES)
     for name in names:
         assert getattr(lib, name) is not None
@@ -40,7 +40,7 @@ def test_header_and_ctypes_agree_on_the_symbol_list(lib):
 
 def test_header_compiles_as_plain_c(tmp_path):
     src = tmp_path / "t.c"
-    src.write_text('#include "rlt_kv_handoff.h"\nint main(void){RltPool p; RltBatch b; RltOptions o; (void)p;(void)b;(void)o; return RLT_OK;}\n')
+    src.write_text('#include "rlt_kv_handoff.h"\nint main(void){RltPool p; RltBatch b; RltOptions o; RltHostBatch h; (void)p;(void)b;(void)o;(void)h; return RLT_OK;}\n')
     subprocess.run(["gcc", "-std=c99", "-Wall", "-Werror", f"-I{HEADER.parent}", "-c", str(src), "-o", str(tmp_path / "t.o")], check=True)
 
 
@@ -50,14 +50,16 @@ def test_struct_layouts_match_the_compiler(tmp_path):
     src = tmp_path / "s.c"
     src.write_text(
         '#include <stdio.h>\n#include <stddef.h>\n#include "rlt_kv_handoff.h"\n'
-        "int main(void){printf(\"%zu %zu %zu %zu %zu %zu %zu\\n\", sizeof(RltRegion), sizeof(RltPool), sizeof(RltBatch),"
-        " sizeof(RltOptions), offsetof(RltPool, num_blocks), offsetof(RltBatch, exit_count), offsetof(RltOptions, status));return 0;}\n"
+        "int main(void){printf(\"%zu %zu %zu %zu %zu %zu %zu %zu %zu\\n\", sizeof(RltRegion), sizeof(RltPool), sizeof(RltBatch),"
+        " sizeof(RltOptions), offsetof(RltPool, num_blocks), offsetof(RltBatch, exit_count), offsetof(RltOptions, status),"
+        " sizeof(RltHostBatch), offsetof(RltHostBatch, tok_end));return 0;}\n"
     )
     exe = tmp_path / "s"
     subprocess.run(["gcc", f"-I{HEADER.parent}", str(src), "-o", str(exe)], check=True)
     got = list(map(int, subprocess.run([str(exe)], capture_output=True, text=True, check=True).stdout.split()))
     want = [C.sizeof(_lib.RltRegion), C.sizeof(_lib.RltPool), C.sizeof(_lib.RltBatch), C.sizeof(_lib.RltOptions),
-            _lib.RltPool.num_blocks.offset, _lib.RltBatch.exit_count.offset, _lib.RltOptions.status.offset]
+            _lib.RltPool.num_blocks.offset, _lib.RltBatch.exit_count.offset, _lib.RltOptions.status.offset,
+            C.sizeof(_lib.RltHostBatch), _lib.RltHostBatch.tok_end.offset]
     assert got == want
 
 
@@ -100,6 +102,21 @@ def test_argument_errors_are_found_on_the_host_before_any_launch(lib):
     assert lib.rlt_kv_pack(C.byref(pool), C.byref(batch), C.byref(opts), 0x7000, 64, None) == _lib.RLT_E_INVALID
     opts.deep_layer_mask = 0
     assert lib.rlt_kv_packed_bytes(C.byref(pool), 10, 3, 2) == 10 * 3 * 2 * 2 * 64
+    # the host-table form: same refusals, all before the staging ring or a device is touched
+    assert lib.rlt_kv_host_batch_limit() == 64 * 1024
+    assert lib.rlt_kv_handoff_host(None, None, None, None, None) == _lib.RLT_E_INVALID
+    tables = (C.c_int32 * 2)(0, 1)
+    one = (C.c_int32 * 1)(0)
+    host = _lib.RltHostBatch(1, 2, 1, 1, C.addressof(tables), C.addressof(tables), C.addressof(one), C.addressof(one))
+    opts.mode = _lib.MODE_DEDUP  # per-token exit planes do not come through this form
+    assert lib.rlt_kv_handoff_host(C.byref(pool), C.byref(pool), C.byref(host), C.byref(opts), None) == _lib.RLT_E_INVALID
+    opts.mode = _lib.MODE_ALL_PLANES
+    host.src_planes = 2  # the pool has one plane
+    assert lib.rlt_kv_handoff_host(C.byref(pool), C.byref(pool), C.byref(host), C.byref(opts), None) == _lib.RLT_E_GEOMETRY
+    host.src_planes, host.table_width = 1, 64 * 1024  # 2 x 256 KiB of tables: more than a staging slot
+    assert lib.rlt_kv_handoff_host(C.byref(pool), C.byref(pool), C.byref(host), C.byref(opts), None) == _lib.RLT_E_LIMIT
+    host.table_width, host.tok_end = 2, None
+    assert lib.rlt_kv_handoff_host(C.byref(pool), C.byref(pool), C.byref(host), C.byref(opts), None) == _lib.RLT_E_INVALID
     assert lib.rlt_kv_copy_segments(None, 1, None) == _lib.RLT_E_INVALID
     assert lib.rlt_kv_copy_segments(0x1000, _lib.MAX_SEGMENTS + 1, None) == _lib.RLT_E_LIMIT
     assert lib.rlt_kv_copy_segments(None, 0, None) == _lib.RLT_OK

@@ -103,6 +103,43 @@ def test_tables_of_one_length_per_side_with_sides_of_different_length(case, long
 
 
 @pytest.mark.parametrize("case", golden_json("handoff.json"), ids=lambda c: c["name"])
+def test_handoff_from_host_tables_equals_reference_destination(case):
+    """``rlt_kv_handoff_host``: the library stages the tables itself. One request per call, the calls repeated so
+    that the staging ring (16 slots) wraps; the arrays are overwritten right after each call returns."""
+    k = kh()
+    arrays = golden_npz(case["name"])
+    P = oracle_pool(case["kind"], case["shape"])
+    D = oracle_pool(case["kind"], case["shape"], device=1, base=1 << 40)
+    load_pool(P, arrays, "src_")
+    load_pool(D, arrays, "dst_before_")
+    gp, gd = GpuPool(P), GpuPool(D)
+    status = k.new_status()
+    for _ in range(7):  # every launch writes the same bytes; with 3 - 4 requests per case the ring wraps
+        for r in case["requests"]:
+            src = np.ascontiguousarray(np.asarray(r["src_tables"], np.int32)[None])
+            dst = np.ascontiguousarray(np.asarray(r["dst_tables"], np.int32)[None])
+            begin, end = np.asarray([r["start"]], np.int32), np.asarray([r["end"]], np.int32)
+            k.kv_handoff_host(gp.view(), gd.view(), src, dst, begin, end, status=status)
+            for a in (src, dst, begin, end):
+                a[...] = -7  # the call has copied them: nothing may read these arrays any more
+    k.raise_for_status(status)
+    load_pool(D, arrays, "dst_after_")
+    assert_pools_equal(gd, D)
+
+
+def test_host_tables_larger_than_a_staging_slot_are_refused():
+    k = kh()
+    case = golden_json("handoff.json")[0]
+    P = oracle_pool(case["kind"], case["shape"])
+    gp = GpuPool(P)
+    width = k.host_batch_limit() // (4 * 2 * P.planes) + 1
+    tables = np.zeros((1, P.planes, width), np.int32)
+    one = np.zeros(1, np.int32)
+    with pytest.raises(ValueError, match="limit"):
+        k.kv_handoff_host(gp.view(), gp.view(), tables, tables, one, one + 1)
+
+
+@pytest.mark.parametrize("case", golden_json("handoff.json"), ids=lambda c: c["name"])
 @pytest.mark.parametrize("variant", VARIANTS)
 def test_pack_equals_reference_wire_and_scatter_inverts_it(case, variant):
     k = kh()

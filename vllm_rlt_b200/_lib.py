@@ -59,6 +59,19 @@ class RltBatch(C.Structure):
     ]
 
 
+class RltHostBatch(C.Structure):
+    _fields_ = [
+        ("num_requests", C.c_int32),
+        ("table_width", C.c_int32),
+        ("src_planes", C.c_int32),
+        ("dst_planes", C.c_int32),
+        ("src_tables", C.c_void_p),
+        ("dst_tables", C.c_void_p),
+        ("tok_begin", C.c_void_p),
+        ("tok_end", C.c_void_p),
+    ]
+
+
 class RltOptions(C.Structure):
     _fields_ = [
         ("mode", C.c_int32),
@@ -83,6 +96,8 @@ SIGNATURES = {
     "rlt_last_cuda_error": (C.c_int, []),
     "rlt_kernel_launches": (C.c_int64, []),
     "rlt_kv_handoff": (C.c_int, [C.POINTER(RltPool), C.POINTER(RltPool), C.POINTER(RltBatch), C.POINTER(RltOptions), C.c_void_p]),
+    "rlt_kv_handoff_host": (C.c_int, [C.POINTER(RltPool), C.POINTER(RltPool), C.POINTER(RltHostBatch), C.POINTER(RltOptions), C.c_void_p]),
+    "rlt_kv_host_batch_limit": (C.c_int64, []),
     "rlt_kv_dedup_workspace_bytes": (C.c_int64, [C.c_int32, C.c_int32, C.c_int32]),
     "rlt_kv_packed_bytes": (C.c_int64, [C.POINTER(RltPool), C.c_int64, C.c_int32, C.c_int32]),
     "rlt_kv_pack": (C.c_int, [C.POINTER(RltPool), C.POINTER(RltBatch), C.POINTER(RltOptions), C.c_void_p, C.c_int64, C.c_void_p]),

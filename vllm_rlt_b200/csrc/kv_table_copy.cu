@@ -38,6 +38,9 @@
 // its exit plane. Where each (request, plane, block) starts in that image is computed on the device by
 // three small kernels (count, tile scan, finish) into a caller-provided workspace; see plan_dedup.
 
+#include <cstring>
+#include <mutex>
+
 #include "common.cuh"
 
 namespace rlt {
@@ -1192,6 +1195,58 @@ int static_plan_address(void** out) {
 }  // namespace
 }  // namespace rlt
 
+namespace rlt {
+namespace {
+
+// Staging of rlt_kv_handoff_host: per device a ring of slots, each a piece of pinned host memory and a piece of
+// device memory of the same size, allocated at the first call on that device. A slot is written by the host,
+// copied to the device on the caller's stream and read by the launch that follows; its event says when that
+// launch has finished, and the slot is reused only then.
+constexpr int kHostSlots = 16;
+constexpr size_t kHostSlotBytes = 64 * 1024;
+
+struct HostRing {
+  unsigned char* pinned = nullptr;
+  unsigned char* device = nullptr;
+  cudaEvent_t done[kHostSlots] = {};
+  int next = 0;
+};
+
+std::mutex g_host_ring_mutex;
+
+int host_ring(HostRing** out) {
+  constexpr int kMaxDevices = 64;
+  static HostRing rings[kMaxDevices];
+  int device = 0;
+  RLT_CUDA_TRY(cudaGetDevice(&device));
+  if (device < 0 || device >= kMaxDevices) return RLT_E_LIMIT;
+  HostRing& ring = rings[device];
+  if (ring.pinned == nullptr) {
+    void* host = nullptr;
+    void* dev = nullptr;
+    RLT_CUDA_TRY(cudaHostAlloc(&host, kHostSlots * kHostSlotBytes, cudaHostAllocDefault));
+    if (cudaError_t e = cudaMalloc(&dev, kHostSlots * kHostSlotBytes); e != cudaSuccess) {
+      cudaFreeHost(host);
+      return cuda_fail(e);
+    }
+    for (int i = 0; i < kHostSlots; ++i) {
+      if (cudaError_t e = cudaEventCreateWithFlags(&ring.done[i], cudaEventDisableTiming); e != cudaSuccess) {
+        for (int j = 0; j < i; ++j) cudaEventDestroy(ring.done[j]);
+        cudaFree(dev);
+        cudaFreeHost(host);
+        return cuda_fail(e);
+      }
+    }
+    ring.device = static_cast<unsigned char*>(dev);
+    ring.pinned = static_cast<unsigned char*>(host);
+  }
+  *out = &ring;
+  return RLT_OK;
+}
+
+}  // namespace
+}  // namespace rlt
+
 extern "C" {
 
 int rlt_kv_pack_dedup_static(const RltPool* src, const RltBatch* batch, const RltOptions* options, void* packed,
@@ -1209,6 +1264,52 @@ int rlt_kv_pack_dedup_static(const RltPool* src, const RltBatch* batch, const Rl
 }
 
 int64_t rlt_kv_static_plan_entries(void) { return rlt::kStaticPlanEntries; }
+
+int64_t rlt_kv_host_batch_limit(void) { return static_cast<int64_t>(rlt::kHostSlotBytes); }
+
+int rlt_kv_handoff_host(const RltPool* src, const RltPool* dst, const RltHostBatch* hb, const RltOptions* options,
+                        rlt_stream_t stream) {
+  if (src == nullptr || dst == nullptr || hb == nullptr || options == nullptr) return RLT_E_INVALID;
+  if (hb->num_requests < 1 || hb->num_requests > RLT_MAX_REQUESTS || hb->table_width < 1) return RLT_E_INVALID;
+  if (hb->src_tables == nullptr || hb->dst_tables == nullptr || hb->tok_begin == nullptr || hb->tok_end == nullptr)
+    return RLT_E_INVALID;
+  if (hb->src_planes != src->num_planes || hb->dst_planes != dst->num_planes) return RLT_E_GEOMETRY;
+  if (options->mode != RLT_MODE_ALL_PLANES) return RLT_E_INVALID;  // the other modes need per-token exit planes
+  const size_t n = static_cast<size_t>(hb->num_requests);
+  const size_t src_bytes = n * hb->src_planes * hb->table_width * sizeof(int32_t);
+  const size_t dst_bytes = n * hb->dst_planes * hb->table_width * sizeof(int32_t);
+  const size_t range_bytes = n * sizeof(int32_t);
+  const size_t total = src_bytes + dst_bytes + 2 * range_bytes;
+  if (total > rlt::kHostSlotBytes) return RLT_E_LIMIT;
+
+  const std::lock_guard<std::mutex> lock(rlt::g_host_ring_mutex);
+  rlt::HostRing* ring = nullptr;
+  const int rc = rlt::host_ring(&ring);
+  if (rc != RLT_OK) return rc;
+  const int slot = ring->next;
+  ring->next = (slot + 1) % rlt::kHostSlots;
+  // the launch that last read this slot (kHostSlots calls ago) must be over before the host overwrites it
+  RLT_CUDA_TRY(cudaEventSynchronize(ring->done[slot]));
+  unsigned char* host = ring->pinned + slot * rlt::kHostSlotBytes;
+  unsigned char* dev = ring->device + slot * rlt::kHostSlotBytes;
+  memcpy(host, hb->src_tables, src_bytes);
+  memcpy(host + src_bytes, hb->dst_tables, dst_bytes);
+  memcpy(host + src_bytes + dst_bytes, hb->tok_begin, range_bytes);
+  memcpy(host + src_bytes + dst_bytes + range_bytes, hb->tok_end, range_bytes);
+  const cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  RLT_CUDA_TRY(cudaMemcpyAsync(dev, host, total, cudaMemcpyHostToDevice, s));
+  RltBatch batch = {};
+  batch.num_requests = hb->num_requests;
+  batch.table_width = hb->table_width;
+  batch.src_tables = reinterpret_cast<const int32_t*>(dev);
+  batch.dst_tables = reinterpret_cast<const int32_t*>(dev + src_bytes);
+  batch.tok_begin = reinterpret_cast<const int32_t*>(dev + src_bytes + dst_bytes);
+  batch.tok_end = reinterpret_cast<const int32_t*>(dev + src_bytes + dst_bytes + range_bytes);
+  const int launched = rlt::launch_table_copy(rlt::kDirect, src, dst, &batch, options, nullptr, 0, s);
+  // recorded even when the launch was refused: the copy above still reads the slot
+  RLT_CUDA_TRY(cudaEventRecord(ring->done[slot], s));
+  return launched;
+}
 
 int rlt_kv_handoff(const RltPool* src, const RltPool* dst, const RltBatch* batch,
                    const RltOptions* options, rlt_stream_t stream) {

@@ -433,6 +433,35 @@ def kv_handoff(src: PoolView, dst: PoolView, batch: HandoffBatch, *, mode=MODE_A
     _lib.check(lib.rlt_kv_handoff(C.byref(s), C.byref(d), C.byref(b), C.byref(o), _stream_ptr(stream)), "rlt_kv_handoff")
 
 
+def host_batch_limit() -> int:
+    """Largest sum of table and range bytes ``kv_handoff_host`` accepts."""
+    return int(_lib.load().rlt_kv_host_batch_limit())
+
+
+def kv_handoff_host(src: PoolView, dst: PoolView, src_tables: np.ndarray, dst_tables: np.ndarray, tok_begin: np.ndarray,
+                    tok_end: np.ndarray, *, layer_begin=0, layer_end=0, plane_begin=0, plane_end=0, status=None,
+                    stream=None) -> None:
+    """All-planes handoff of a small batch whose tables are host arrays: the library stages them in a slot of its own
+    and queues copy and launch on ``stream`` (``rlt_kv_handoff_host``); the arrays are free again on return.
+
+    ``src_tables`` / ``dst_tables`` are C-contiguous int32 ``[requests, planes, width]`` of one width, ``tok_begin`` /
+    ``tok_end`` int32 ``[requests]``. Nothing is validated on the host beyond shapes; the kernel checks block ids and
+    ranges and reports through ``status``. Raises ``ValueError`` with the library's limit message when the batch does
+    not fit a staging slot."""
+    arrays = (src_tables, dst_tables, tok_begin, tok_end)
+    if any(a.dtype != np.int32 or not a.flags.c_contiguous for a in arrays):
+        raise ValueError("host tables and ranges must be C-contiguous int32 arrays")
+    n, src_planes, width = src_tables.shape
+    if dst_tables.shape[0] != n or dst_tables.shape[2] != width or tok_begin.shape != (n,) or tok_end.shape != (n,):
+        raise ValueError("source and destination tables must agree in requests and width, one range per request")
+    hb = _lib.RltHostBatch(n, width, src_planes, dst_tables.shape[1], src_tables.ctypes.data, dst_tables.ctypes.data,
+                           tok_begin.ctypes.data, tok_end.ctypes.data)
+    s, d = src.as_struct(), dst.as_struct()
+    o = _options(MODE_ALL_PLANES, layer_begin, layer_end, 0, status, 0, 0, None, plane_begin, plane_end, 0)
+    _lib.check(_lib.load().rlt_kv_handoff_host(C.byref(s), C.byref(d), C.byref(hb), C.byref(o), _stream_ptr(stream)),
+               "rlt_kv_handoff_host")
+
+
 def packed_bytes(pool: PoolView, total_tokens: int, wire_planes: int, layers: int | None = None) -> int:
     lib = _lib.load()
     s = pool.as_struct()

@@ -306,6 +306,7 @@ class CudaBackend:
         self.peerlib = peerlib
         self._mailboxes: dict[str, tuple[Mailbox, int]] = {}
         self._views: dict[tuple, tuple] = {}
+        self._host_limit = None  # bytes of tables one call of the library's own staging takes
         self.stream = torch.cuda.Stream(self.device)
 
     def _on_stream(self):
@@ -410,6 +411,15 @@ class CudaBackend:
                 views = (mine, theirs)
             self._views[key] = views
         src, dst = views
+        if exit_planes is None and status is None and mode == kh.MODE_ALL_PLANES:
+            host = self._host_tables(requests, src, dst)
+            if host is not None:  # a chunk's worth of tables: staged and launched by one call into the library
+                with self.torch.cuda.device(self.device):
+                    if before_launch is not None:
+                        before_launch()
+                    kh.kv_handoff_host(src, dst, *host, layer_begin=layer_begin, layer_end=layer_end,
+                                       plane_begin=plane_begin, plane_end=plane_end, stream=self.stream)
+                return ()
         with self.torch.cuda.device(self.device), self._on_stream():
             batch = kh.HandoffBatch(
                 [r[0] for r in requests], [r[1] for r in requests], [(r[2], r[3]) for r in requests],
@@ -420,6 +430,35 @@ class CudaBackend:
             kh.kv_handoff(src, dst, batch, mode=mode, layer_begin=layer_begin, layer_end=layer_end,
                           plane_begin=plane_begin, plane_end=plane_end, status=status)
         return (batch,)
+
+    def _host_tables(self, requests, src, dst):
+        """``(source tables, destination tables, begin, end)`` as int32 arrays for ``kv_handoff_host``, or None when
+        the batch is not of that kind (tables of different lengths, too large for a staging slot) or when anything
+        about it looks wrong: the general path then finds the error and words it as the reference does."""
+        import numpy as np
+
+        try:
+            source = np.asarray([r[0] for r in requests], dtype=np.int32)
+            target = np.asarray([r[1] for r in requests], dtype=np.int32)
+        except (ValueError, OverflowError):
+            return None
+        if source.ndim != 3 or target.ndim != 3 or source.shape[2] != target.shape[2] or source.shape[2] < 1:
+            return None
+        if source.shape[1] != src.num_planes or target.shape[1] != dst.num_planes:
+            return None
+        begin = np.asarray([r[2] for r in requests], dtype=np.int64)
+        end = np.asarray([r[3] for r in requests], dtype=np.int64)
+        if self._host_limit is None:
+            from ..kernels import kv_handoff as kh
+
+            self._host_limit = kh.host_batch_limit()
+        if source.nbytes + target.nbytes + 8 * len(requests) > self._host_limit:
+            return None
+        suspicious = ((begin < 0) | (begin >= end) | (end > source.shape[2] * src.block_size)).any() \
+            or (source.view(np.uint32) >= src.num_blocks).any() or (target.view(np.uint32) >= dst.num_blocks).any()
+        if suspicious:
+            return None
+        return source, target, begin.astype(np.int32), end.astype(np.int32)
 
     def post(self, slot_ptr: int, body: bytes, stamp: int):
         import ctypes as C
