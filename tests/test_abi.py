@@ -153,7 +153,7 @@ def test_torch_ops_are_registered_in_the_reference_namespace():
 
     _build.build_all()
     torch.ops.load_library(str(_build.PACKAGE / _build.OPS_NAME))
-    for name in ("kv_handoff", "kv_handoff_peer", "kv_pack", "kv_scatter", "kv_push", "kv_copy_segments", "kv_signal", "kv_wait"):
+    for name in ("kv_handoff", "kv_handoff_host", "kv_handoff_peer", "kv_pack", "kv_scatter", "kv_push", "kv_copy_segments", "kv_signal", "kv_wait"):
         assert hasattr(torch.ops.vllm_rlt, name)
     schema = str(torch.ops.vllm_rlt.kv_scatter.default._schema)
     assert "Tensor(a!) key" in schema

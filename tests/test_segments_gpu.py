@@ -158,6 +158,17 @@ def test_torch_ops_match_the_c_abi_path():
                         gd3.value_cache.data_ptr(), gd3.key_scale.data_ptr(), gd3.value_scale.data_ptr(),
                         D.num_blocks, D.planes, st, dt, begin, end, None, None, 0, 0, 0, status)
     assert_pools_equal(gd3, D)
+    # host-table form: the same tables as CPU tensors, staged by the library
+    gd4 = GpuPool(oracle_pool(case["kind"], case["shape"], device=1, base=1 << 40))
+    for t, name in zip(gd4.tensors(), ["key", "value", "key_scale", "value_scale"]):
+        t.view(torch.uint8).copy_(torch.from_numpy(arrays["dst_before_" + name].reshape(-1)).cuda().view(t.view(torch.uint8).shape))
+    ops.kv_handoff_host(gp.key_cache, gp.value_cache, gp.key_scale, gp.value_scale, gd4.key_cache, gd4.value_cache,
+                        gd4.key_scale, gd4.value_scale, st.cpu(), dt.cpu(), begin.cpu(), end.cpu(), 0, 0, status)
+    assert status.tolist() == [0, 0, 0, 0]
+    assert_pools_equal(gd4, D)
+    with pytest.raises(RuntimeError, match="CPU int32"):
+        ops.kv_handoff_host(gp.key_cache, gp.value_cache, gp.key_scale, gp.value_scale, gd4.key_cache, gd4.value_cache,
+                            gd4.key_scale, gd4.value_scale, st, dt, begin, end, 0, 0, status)
     with pytest.raises(RuntimeError, match="contiguous"):
         ops.kv_handoff(gp.key_cache.transpose(0, 1), gp.value_cache, None, None, gd.key_cache, gd.value_cache,
                        None, None, st, dt, begin, end, None, None, 0, 0, 0, None)

@@ -142,6 +142,39 @@ void kv_handoff_cuda(const at::Tensor& src_key, const at::Tensor& src_value, con
   check_rc(rlt_kv_handoff(&src, &dst, &b.batch, &o, current_stream(device)), "kv_handoff");
 }
 
+// The all-planes handoff with the block tables still in host memory (CPU int32 tensors): the library stages them
+// in a slot of its own and queues copy and launch on the current stream. For chunk-sized batches.
+void kv_handoff_host_cuda(const at::Tensor& src_key, const at::Tensor& src_value, const OptTensor& src_key_scale,
+                          const OptTensor& src_value_scale, at::Tensor& dst_key, at::Tensor& dst_value,
+                          const OptTensor& dst_key_scale, const OptTensor& dst_value_scale, const at::Tensor& src_tables,
+                          const at::Tensor& dst_tables, const at::Tensor& tok_begin, const at::Tensor& tok_end,
+                          int64_t layer_begin, int64_t layer_end, const OptTensor& status) {
+  const at::Device device = src_key.device();
+  const c10::cuda::CUDAGuard guard(device);
+  for (const at::Tensor* t : {&src_tables, &dst_tables, &tok_begin, &tok_end}) {
+    TORCH_CHECK(t->device().is_cpu() && t->scalar_type() == at::kInt && t->is_contiguous(),
+                "kv_handoff_host takes its tables and ranges as contiguous CPU int32 tensors");
+  }
+  TORCH_CHECK(src_tables.dim() == 3 && dst_tables.dim() == 3 && src_tables.size(0) == dst_tables.size(0) &&
+                  src_tables.size(2) == dst_tables.size(2),
+              "block tables must be [requests, planes, pages] and agree in requests and pages");
+  TORCH_CHECK(tok_begin.numel() == src_tables.size(0) && tok_end.numel() == src_tables.size(0),
+              "one token range per request");
+  RltHostBatch hb{};
+  hb.num_requests = static_cast<int32_t>(src_tables.size(0));
+  hb.table_width = static_cast<int32_t>(src_tables.size(2));
+  hb.src_planes = static_cast<int32_t>(src_tables.size(1));
+  hb.dst_planes = static_cast<int32_t>(dst_tables.size(1));
+  hb.src_tables = src_tables.data_ptr<int32_t>();
+  hb.dst_tables = dst_tables.data_ptr<int32_t>();
+  hb.tok_begin = tok_begin.data_ptr<int32_t>();
+  hb.tok_end = tok_end.data_ptr<int32_t>();
+  const RltPool src = pool_of(src_key, src_value, src_key_scale, src_value_scale, hb.src_planes);
+  const RltPool dst = pool_of(dst_key, dst_value, dst_key_scale, dst_value_scale, hb.dst_planes);
+  const RltOptions o = options_of(RLT_MODE_ALL_PLANES, layer_begin, layer_end, status_ptr(status, device));
+  check_rc(rlt_kv_handoff_host(&src, &dst, &hb, &o, current_stream(device)), "kv_handoff_host");
+}
+
 void kv_handoff_peer_cuda(const at::Tensor& src_key, const at::Tensor& src_value, const OptTensor& src_key_scale,
                           const OptTensor& src_value_scale, int64_t dst_key_ptr, int64_t dst_value_ptr,
                           int64_t dst_key_scale_ptr, int64_t dst_value_scale_ptr, int64_t dst_num_blocks,
@@ -313,6 +346,11 @@ TORCH_LIBRARY_FRAGMENT(vllm_rlt, ops) {
       "Tensor src_tables, Tensor dst_tables, Tensor tok_begin, Tensor tok_end, Tensor? exit_planes, "
       "Tensor? exit_offsets, int mode, int layer_begin, int layer_end, Tensor(e!)? status) -> ()");
   ops.def(
+      "kv_handoff_host(Tensor src_key, Tensor src_value, Tensor? src_key_scale, Tensor? src_value_scale, "
+      "Tensor(a!) dst_key, Tensor(b!) dst_value, Tensor(c!)? dst_key_scale, Tensor(d!)? dst_value_scale, "
+      "Tensor src_tables, Tensor dst_tables, Tensor tok_begin, Tensor tok_end, int layer_begin, int layer_end, "
+      "Tensor(e!)? status) -> ()");
+  ops.def(
       "kv_handoff_peer(Tensor src_key, Tensor src_value, Tensor? src_key_scale, Tensor? src_value_scale, "
       "int dst_key_ptr, int dst_value_ptr, int dst_key_scale_ptr, int dst_value_scale_ptr, int dst_num_blocks, "
       "int dst_num_planes, Tensor src_tables, Tensor dst_tables, Tensor tok_begin, Tensor tok_end, "
@@ -350,6 +388,7 @@ TORCH_LIBRARY_FRAGMENT(vllm_rlt, ops) {
 
 TORCH_LIBRARY_IMPL(vllm_rlt, CUDA, ops) {
   ops.impl("kv_handoff", &vllm_rlt_b200::kv_handoff_cuda);
+  ops.impl("kv_handoff_host", &vllm_rlt_b200::kv_handoff_host_cuda);
   ops.impl("kv_handoff_peer", &vllm_rlt_b200::kv_handoff_peer_cuda);
   ops.impl("kv_pack", &vllm_rlt_b200::kv_pack_cuda);
   ops.impl("kv_scatter", &vllm_rlt_b200::kv_scatter_cuda);
