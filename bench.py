@@ -12,7 +12,7 @@ Other measurements share the workloads and helpers of this file and print their 
 not the benchmark line:
 
     python bench.py --suite kernels [--requests 8]      every other kernel of the library on one GPU
-    python bench.py --suite peer [--pull] [--mode ...]  one process, two GPUs: the handoff kernel over NVLink
+    python bench.py --suite peer [--pull] [--mode ...] [--workload huginn]   one process, two GPUs: the kernel over NVLink
     python bench.py --suite deployment [...]            a vllm-rlt 1P:1D deployment with this connector swapped in
 """
 
@@ -759,7 +759,12 @@ def suite_peer(args):
     peer.enable_peer_access(1, 0)
     run_on = 1 if args.pull else 0
     torch.cuda.set_device(0)
-    w = workloads.last_exited_exit_only(requests=args.requests if args.requests != 64 else 2, mode=args.mode)
+    requests = args.requests if args.requests != 64 else 2
+    if args.workload == "huginn":  # 32 planes, 10,560-byte rows; short prompts keep the pools at a few GB
+        w = workloads.recurrent_depth_dedup(lengths=[min(args.tokens, 1024)] * requests)
+        args.mode = "dedup"
+    else:
+        w = workloads.last_exited_exit_only(requests=requests, mode=args.mode)
     s = w.shape
     src = KVPool(s.num_layers, s.num_kv_heads, s.head_dim, w.src_blocks, s.block_size, s.planes, device="cuda:0")
     dst = KVPool(s.num_layers, s.num_kv_heads, s.head_dim, w.dst_blocks, s.block_size, w.dst_planes, device="cuda:1")
@@ -794,7 +799,7 @@ def suite_peer(args):
     link = w.payload_bytes
     if args.mode == "dedup" and args.pull:
         link = sum(int(np.minimum(np.asarray(x[lo:hi]) + 1, w.dst_planes).sum()) for x, (lo, hi) in zip(w.exit_planes, w.ranges)) * s.token_plane_bytes
-    print(json.dumps({"suite": "peer", "link_bytes": link,
+    print(json.dumps({"suite": "peer", "workload": w.description, "link_bytes": link,
                       "direction": "pull (kernel on the destination GPU)" if args.pull else "push (kernel on the source GPU)",
                       "payload_bytes": w.payload_bytes, "ms": ms, "gbps": w.payload_bytes / ms / 1e6,
                       "link_gbps": link / ms / 1e6, "frac_of_nominal_900": link / ms / 1e6 / NVLINK_NOMINAL_GBS,

@@ -178,7 +178,8 @@ class StagedInputTensor:
         on_device = isinstance(values, torch.Tensor) and values.device.type != "cpu"
         if on_device:
             raise ValueError("staged input values must be CPU-owned")
-        piece = self.cpu[self._reserve(len(values))]  # looked up after growth
+        where = self._reserve(len(values))
+        piece = self.cpu[where]  # taken after a possible growth
         piece.copy_(torch.as_tensor(values, dtype=self.dtype))
         return piece
 
