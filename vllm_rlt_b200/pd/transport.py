@@ -168,15 +168,15 @@ class _RingWriter:
         if not self.live:
             start = self.head if self.head + nbytes <= self.size else 0
         else:
-            tail = self.live[0][1]
-            if tail < self.head or (tail == self.head and False):
+            tail = self.live[0][1]  # where the oldest live region starts
+            if tail < self.head:  # live bytes are [tail, head): free are [head, size) and [0, tail)
                 if self.head + nbytes <= self.size:
                     start = self.head
                 elif nbytes <= tail:
                     start = 0
                 else:
                     return None
-            elif self.head + nbytes <= tail:
+            elif self.head + nbytes <= tail:  # live bytes wrap around the end: free are [head, tail)
                 start = self.head
             else:
                 return None
