@@ -1052,7 +1052,11 @@ int launch_table_copy(Direction dir, const RltPool* src, const RltPool* dst, con
   }
 
   const int unit_kib = (opt->variant >> 4) & 0xff;
-  const long long unit_target = unit_kib ? unit_kib * 16384ll : 131072ll;
+  // 128 KiB of rows per unit; a dedup pack carries only the tokens that reach a unit's plane (5/8 of a block on
+  // average with uniform exits), so its units are sized at twice that (measured: 0.94 -> 0.97 of the HBM copy peak;
+  // the same change costs the other launches 2 - 4 %).
+  const long long unit_default = dedup_wire && dir == kPack ? 262144ll : 131072ll;
+  const long long unit_target = unit_kib ? unit_kib * 16384ll : unit_default;
   for (int g = 0; g < p.num_regions; ++g) {
     const RltRegion& s = g == 0 ? any->codes : any->scales;
     RegionParams& rg = p.region[g];
