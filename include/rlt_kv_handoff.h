@@ -174,7 +174,8 @@ RLT_API int rlt_kv_handoff(const RltPool* src, const RltPool* dst, const RltBatc
  * allocated at the first call on that GPU), queues the host-to-device copy and the launch on `stream`, and returns.
  * The arrays may be changed or freed as soon as it has returned. A batch whose tables and ranges exceed
  * rlt_kv_host_batch_limit() bytes gets RLT_E_LIMIT and nothing is queued: stage such a batch yourself and call
- * rlt_kv_handoff. When all 16 slots belong to launches that have not finished, the call waits for the oldest.
+ * rlt_kv_handoff. When all 16 slots belong to launches that have not finished, the call waits for the oldest
+ * on the host; for that reason, and because it allocates at its first use, it is not for CUDA-graph capture.
  *
  * This is what a transfer worker calls per chunk: one request, tables of a few hundred entries, where the time to
  * stage them decides how soon after the producer's event the copy starts. It takes the place of the descriptor

@@ -265,18 +265,6 @@ int rlt_tensor_copy(const void* src, void* dst, void* secondary, int64_t count, 
                     int32_t secondary_dtype, rlt_stream_t stream) {
   if (count == 0) return RLT_OK;
   if (src == nullptr || dst == nullptr || count < 0) return RLT_E_INVALID;
-  const bool aligned = ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 15u) == 0;
-  if (src_dtype == dst_dtype && secondary == nullptr && aligned) {
-    // no conversion and one output: a byte copy, which the tiled copy kernel does a few percent faster
-    int64_t element = 0;
-    switch (src_dtype) {
-      case RLT_DTYPE_I32: case RLT_DTYPE_F32: element = 4; break;
-      case RLT_DTYPE_I64: element = 8; break;
-      case RLT_DTYPE_F16: case RLT_DTYPE_BF16: element = 2; break;
-      default: return RLT_E_INVALID;
-    }
-    return rlt_kv_push(src, dst, count * element, stream);
-  }
   int sms = 0;
   const int rc0 = rlt::sm_count(&sms);
   if (rc0 != RLT_OK) return rc0;
