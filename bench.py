@@ -824,6 +824,8 @@ def suite_deployment(args):
     sys.path.insert(0, str(checkout))
     os.environ["PYTHONPATH"] = os.pathsep.join([str(checkout), str(ROOT), os.environ.get("PYTHONPATH", "")])
     os.environ.setdefault("RLT_KV_DIRECTION", args.direction)
+    if args.stream:  # the prefill worker reports its KV writes layer by layer (vllm_rlt_b200/pd/layer_watch.py)
+        os.environ["RLT_KV_STREAM"] = "1"
     from vllm_rlt import CacheConfig, SamplingParams, SchedulerConfig
     from vllm_rlt.models.ouro import OuroConfig
     from vllm_rlt.pd.config import PDConfig
@@ -886,6 +888,7 @@ def suite_deployment(args):
         "bytes_sent": sent, "transfers": sum(m.get("transfers", 0) for m in worker_metrics.values()),
         "transfer_seconds_sum": seconds,
         "gbps_while_transferring": (sent / seconds / 1e9) if seconds else None, "startup_s": startup,
+        "layer_streaming": bool(args.stream), "streamed_slices": sum(m.get("streamed_slices", 0) for m in worker_metrics.values()),
         "pulled_bytes": sum(m.get("bytes_received", 0) for m in worker_metrics.values()),
         "pull_device_seconds": sum(m.get("pull_seconds", 0.0) for m in worker_metrics.values()),
         # median over the pull launches of the run (the first one of a process carries the module load)
@@ -931,6 +934,8 @@ def main():
     ap.add_argument("--concurrency", type=int, default=1, help="--suite deployment: requests submitted at once")
     ap.add_argument("--chunk", type=int, default=2048, help="--suite deployment: prefill chunk size")
     ap.add_argument("--kv-dtype", default="auto", choices=["auto", "fp8_e4m3"], help="--suite deployment")
+    ap.add_argument("--stream", action="store_true",
+                    help="--suite deployment: stream finished layers behind the prefill (RLT_KV_STREAM=1 in the workers)")
     args = ap.parse_args()
     if args.suite is not None:
         {"kernels": suite_kernels, "peer": suite_peer, "deployment": suite_deployment}[args.suite](args)

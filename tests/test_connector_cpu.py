@@ -316,6 +316,95 @@ def test_layers_reported_one_by_one_leave_early_and_the_tail_is_one_slice(direct
         p.connector.layer_written(request, plane=0, layer=0, event=FakeEvent(), start=0, end=10)
 
 
+def cache_that_writes(pool, depths=2):
+    """Gives a pool the three things the layer watch looks at on a cache manager: how many depths there are, which
+    plane a depth is stored in, and the prepared write every traversal goes through (here it only counts calls)."""
+    pool.max_loops, pool._plane, pool.writes = depths, (lambda depth: depth), []
+    pool._write_prepared = lambda layer, batch, k, v: pool.writes.append(layer)
+    return pool
+
+
+def traversal(pool, request_id, depth, start, end, layers=3):
+    """One depth of a prefill step as the model drives it: one prepared batch, every layer written through it."""
+    allocation = object()
+    batch = SimpleNamespace(rows=tuple((allocation, depth, t) for t in range(start, end)), allocations=((request_id, allocation),))
+    for layer in range(layers):
+        pool._write_prepared(layer, batch, None, None)
+
+
+@pytest.mark.parametrize("direction", DIRECTIONS)
+def test_a_watched_cache_reports_its_own_writes_and_the_step_end_sends_only_the_rest(direction):
+    from vllm_rlt_b200.pd import layer_watch
+
+    p, d = make_pair(direction=direction)
+    cache_that_writes(p.pool)
+    assert layer_watch.eligible(p.connector)
+    watch = layer_watch.LayerWatch(p.connector).install()
+    watch.event_factory = FakeEvent
+    p.connector.stream_layers = 2
+    request, reserved = handoff_ready(p, d, "s", 10)
+    traversal(p.pool, "s", 0, 0, 10)
+    traversal(p.pool, "s", 1, 0, 10)
+    traversal(p.pool, "stranger", 0, 0, 4)  # not an export: written, not reported
+    assert p.pool.writes == [0, 1, 2] * 3 and watch.reported == 4
+    assert p.connector.transfers["s"].streamed_layers == {0: 3, 1: 3}
+    request.num_prefilled_tokens, request.hidden_state = 10, torch.full((16,), 3.0)
+    p.connector.prefill_submitted(request, phase="PREFILL", start=0,
+                                  progress=SimpleNamespace(chunk_complete=True, prompt_complete=True), event=None, stream=None)
+    settle(p, d)
+    (commit,) = p.take("commit")
+    assert commit["count"] == 5  # four slices while the step ran, the hidden row at its end
+    d.connector.command(dict(kind="commit", tid="s", count=5))
+    settle(p, d)
+    assert d.take("received")
+    assert torch.equal(pool_rows(p.pool, p.pool.plane_block_tables("s"), 0, 10), pool_rows(d.pool, reserved["tables"], 0, 10))
+    watch.remove()
+    assert "_write_prepared" in p.pool.__dict__ and p.pool._write_prepared is not watch  # the stand-in of this test is back
+
+
+def test_a_plane_written_twice_in_one_window_withdraws_the_window_and_the_step_end_sends_all_of_it():
+    from vllm_rlt_b200.pd import layer_watch
+
+    p, d = make_pair()
+    cache_that_writes(p.pool)
+    watch = layer_watch.LayerWatch(p.connector).install()
+    watch.event_factory = FakeEvent
+    p.connector.stream_layers = 2
+    request, reserved = handoff_ready(p, d, "s", 6)
+    traversal(p.pool, "s", 0, 0, 6)
+    assert watch.reported == 2
+    traversal(p.pool, "s", 0, 0, 6)  # the same plane again: what left may be stale
+    t = p.connector.transfers["s"]
+    assert watch.reported == 2 and t.streamed_window is None and t.stream_refused == (0, 6)
+    request.num_prefilled_tokens, request.hidden_state = 6, torch.ones(16)
+    p.connector.prefill_submitted(request, phase="PREFILL", start=0,
+                                  progress=SimpleNamespace(chunk_complete=True, prompt_complete=True), event=None, stream=None)
+    settle(p, d)
+    (commit,) = p.take("commit")
+    assert commit["count"] == 3  # the two early slices and the whole window again, which carries the hidden row
+    d.connector.command(dict(kind="commit", tid="s", count=3))
+    settle(p, d)
+    assert d.take("received")
+    assert torch.equal(pool_rows(p.pool, p.pool.plane_block_tables("s"), 0, 6), pool_rows(d.pool, reserved["tables"], 0, 6))
+
+
+def test_the_watch_is_refused_where_depths_share_a_plane_or_prefill_is_wavefront_chunked(monkeypatch):
+    from vllm_rlt_b200.pd import layer_watch
+
+    p, _ = make_pair()
+    cache_that_writes(p.pool)
+    assert layer_watch.eligible(p.connector)
+    p.pool._plane = lambda depth: 0  # every depth stored in one plane: rows are rewritten within a step
+    assert not layer_watch.eligible(p.connector)
+    p.pool._plane = lambda depth: depth
+    p.engine.scheduler.config.wavefront_chunked_prefill = True
+    assert not layer_watch.eligible(p.connector)
+    monkeypatch.setenv("RLT_KV_STREAM", "1")
+    assert layer_watch.wanted()
+    monkeypatch.setenv("RLT_KV_STREAM", "0")
+    assert not layer_watch.wanted()
+
+
 def test_nobody_calling_the_layer_hook_changes_nothing_and_a_non_exporting_request_is_ignored():
     p, d = make_pair()
     request, reserved = handoff_ready(p, d, "q", 6)

@@ -98,6 +98,7 @@ class RequestTransfer:
     # layer streaming: per destination plane, how many layers of the current prefill window have left already
     streamed_layers: dict = field(default_factory=dict)
     streamed_window: tuple | None = None
+    stream_refused: tuple | None = None  # a window whose early slices were withdrawn: it leaves whole at the chunk's end
 
     def note_range(self, start: int, end: int) -> None:
         """Remember the first and last token range put on the wire, and how many there were."""
@@ -157,6 +158,7 @@ class PDStageConnector:
         self.transfer_cursor = 0
         self.prefill_tokens = 0
         self.stream_layers = 4  # layers per slice that ``layer_written`` lets go at once
+        self.layer_watch = None  # set by ``create`` when this worker reports its KV writes itself (pd/layer_watch.py)
         self.exporter = Exporter(self)
         self.importer = Importer(self)
         self._control = {
@@ -189,7 +191,12 @@ class PDStageConnector:
         anchor = next(engine.model.parameters())
         hidden = torch.empty((rows, engine.model.config.hidden_size), device=anchor.device, dtype=anchor.dtype)
         make = transport_factory or B200Transport
-        return cls(engine, hidden, make(stage.stage_id, engine.cache_manager, hidden, config), config, notify=notify)
+        connector = cls(engine, hidden, make(stage.stage_id, engine.cache_manager, hidden, config), config, notify=notify)
+        from . import layer_watch
+
+        if layer_watch.wanted() and stage.accepts_prompt and layer_watch.eligible(connector):
+            connector.layer_watch = layer_watch.LayerWatch(connector).install()
+        return connector
 
     def startup_info(self):
         """Transport info plus a fingerprint of model config, weights, dtype, layout and attention
@@ -243,6 +250,9 @@ class PDStageConnector:
         t = self.transport
         metrics = {"prefill_tokens": self.prefill_tokens, "bytes_sent": t.bytes_sent, "transfers": t.transfers,
                    "transfer_seconds": t.transfer_seconds}
+        if self.layer_watch is not None:
+            self.layer_watch.remove()
+            metrics["streamed_slices"] = self.layer_watch.reported
         received = getattr(t, "bytes_received", 0)
         if isinstance(received, int) and received:  # the pull direction: what this worker's GPU read, and for how long
             rates = sorted(getattr(t, "pull_rates", ()))
@@ -287,6 +297,24 @@ class PDStageConnector:
         """
         t = self._export_of(request)
         if t is None or t.cancelled:
+            return False
+        return self.exporter.layer_written(t, plane, layer, event, start, end)
+
+    def report_layer(self, request_id, plane, layer, start, end, *, event=None) -> bool:
+        """``layer_written`` for a reporter that sits inside the model's forward (pd/layer_watch.py): it knows the
+        request by id, passes the window it saw, and must never get an exception back. A plane that is written a
+        second time inside one window withdraws the window from streaming: what left early may be stale, so the whole
+        window leaves at the chunk's end, as without streaming."""
+        t = self.transfers.get(request_id)
+        if t is None or not t.outgoing or t.cancelled or t.compute_done:
+            return False
+        window = (max(start, t.target_cached_tokens), end)
+        if window[0] >= window[1] or t.stream_refused == window:
+            return False
+        if t.streamed_window == window and layer + 1 <= t.streamed_layers.get(plane, 0):
+            t.streamed_window, t.streamed_layers, t.stream_refused = None, {}, window
+            return False
+        if not 0 <= plane < len(t.target_tables) or not 0 <= layer < self.transport.info["num_layers"]:
             return False
         return self.exporter.layer_written(t, plane, layer, event, start, end)
 

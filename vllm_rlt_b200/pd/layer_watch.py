@@ -1,0 +1,97 @@
+"""Layer streaming without a source edit: reports a prefill worker's KV writes to its connector as they are queued.
+
+``PDStageConnector.layer_written`` is the hook a model runner calls after the KV write of a layer
+(vllm_rlt/models/ouro.py:185 is the call site a maintainer would use). Where the runner is not edited, this module gets
+the same information from the cache manager itself: every eager prefill traversal writes its K/V rows through
+``KVCacheManager._write_prepared(layer, batch, k, v)`` (vllm_rlt/core/kv_cache_manager.py:848-886) with a ``KVMetadata``
+batch whose host rows say which request, depth and positions the rows belong to (vllm_rlt/worker/metadata.py:21-41).
+``LayerWatch`` wraps that one bound method ON THE WORKER'S OWN CACHE MANAGER INSTANCE, lets the write go ahead
+unchanged and then tells the connector "layer L of plane P of request R, tokens [a, b), is queued".
+
+It is switched on per worker with ``RLT_KV_STREAM=1`` and only where reporting early is safe:
+
+* a depth owns its plane (``last_exited`` storage: plane = depth). In a layout where several depths write one plane a
+  row is rewritten later in the same step, so nothing may leave early;
+* prefill is not wavefront-chunked (there one step advances several windows of a request at different depths, which the
+  connector's one-window bookkeeping would answer by sending everything twice).
+
+Everything else (graph-captured steps, which go through the runner's own device cache object; batches without host
+rows; requests that are not being exported; rows that are not one contiguous range) is simply not reported, and the
+next ``prefill_submitted`` sends whatever was not streamed, as it always does.
+"""
+
+from __future__ import annotations
+
+import os
+
+
+def wanted() -> bool:
+    return os.environ.get("RLT_KV_STREAM", "").strip().lower() in ("1", "true", "yes", "on")
+
+
+def eligible(connector) -> bool:
+    """Whether this worker's storage and scheduler allow layers to leave early (see the module docstring)."""
+    cache = connector.cache
+    depths = getattr(cache, "max_loops", None)
+    plane_of = getattr(cache, "_plane", None)
+    if not isinstance(depths, int) or not callable(plane_of) or not callable(getattr(cache, "_write_prepared", None)):
+        return False
+    if len({plane_of(d) for d in range(depths)}) != depths:
+        return False
+    return not getattr(connector.engine.scheduler.config, "wavefront_chunked_prefill", False)
+
+
+class LayerWatch:
+    """Stands in for ``cache._write_prepared`` on one cache manager instance."""
+
+    def __init__(self, connector):
+        self.connector = connector
+        self.cache = connector.cache
+        self.write = self.cache._write_prepared  # the bound original
+        self.shadowed = self.cache.__dict__.get("_write_prepared")  # normally None: the original is the class's method
+        self.plan_of = None   # the batch object the plan below was made for
+        self.plan = ()        # [(request id, plane, first token, end token)]
+        self.reported = 0     # slices that left early, for the metrics
+        self.event_factory = None  # None: the connector records a CUDA event on the current stream when a slice leaves
+
+    def install(self) -> "LayerWatch":
+        self.cache._write_prepared = self
+        return self
+
+    def remove(self) -> None:
+        if self.cache.__dict__.get("_write_prepared") is self:
+            if self.shadowed is None:
+                del self.cache.__dict__["_write_prepared"]
+            else:
+                self.cache._write_prepared = self.shadowed
+
+    def __call__(self, layer, batch, k, v):
+        self.write(layer, batch, k, v)
+        rows = getattr(batch, "rows", None)
+        if not rows or not self.connector.transfers:
+            return
+        if self.plan_of is not batch:  # one descriptor serves every layer of a traversal: plan once
+            self.plan_of, self.plan = batch, self._plan(batch)
+        for request_id, plane, start, end in self.plan:
+            event = self.event_factory() if self.event_factory is not None else None
+            if self.connector.report_layer(request_id, plane, layer, start, end, event=event):
+                self.reported += 1
+
+    def _plan(self, batch):
+        names = {id(allocation): request_id for request_id, allocation in batch.allocations}
+        spans = {}
+        for allocation, depth, position in batch.rows:
+            key = (id(allocation), depth)
+            span = spans.get(key)
+            if span is None:
+                spans[key] = [position, position + 1, 1]
+            else:
+                span[0] = min(span[0], position)
+                span[1] = max(span[1], position + 1)
+                span[2] += 1
+        plan = []
+        for (allocation, depth), (start, end, count) in spans.items():
+            request_id = names.get(allocation)
+            if request_id is not None and end - start == count:  # one gap-free run of tokens
+                plan.append((request_id, self.cache._plane(depth), start, end))
+        return tuple(plan)
