@@ -362,6 +362,30 @@ def test_a_watched_cache_reports_its_own_writes_and_the_step_end_sends_only_the_
     assert "_write_prepared" in p.pool.__dict__ and p.pool._write_prepared is not watch  # the stand-in of this test is back
 
 
+def test_planes_before_the_last_can_leave_whole_so_that_a_step_costs_fewer_launches():
+    from vllm_rlt_b200.pd import layer_watch
+
+    p, d = make_pair()
+    cache_that_writes(p.pool)
+    watch = layer_watch.LayerWatch(p.connector).install()
+    watch.event_factory = FakeEvent
+    p.connector.stream_layers, p.connector.stream_whole_planes = 1, True
+    request, reserved = handoff_ready(p, d, "s", 10)
+    traversal(p.pool, "s", 0, 0, 10)
+    assert watch.reported == 1  # plane 0 in one piece, after its last layer
+    traversal(p.pool, "s", 1, 0, 10)
+    assert watch.reported == 4  # the last plane layer by layer
+    request.num_prefilled_tokens, request.hidden_state = 10, torch.ones(16)
+    p.connector.prefill_submitted(request, phase="PREFILL", start=0,
+                                  progress=SimpleNamespace(chunk_complete=True, prompt_complete=True), event=None, stream=None)
+    settle(p, d)
+    (commit,) = p.take("commit")
+    d.connector.command(dict(kind="commit", tid="s", count=commit["count"]))
+    settle(p, d)
+    assert commit["count"] == 5 and d.take("received")
+    assert torch.equal(pool_rows(p.pool, p.pool.plane_block_tables("s"), 0, 10), pool_rows(d.pool, reserved["tables"], 0, 10))
+
+
 def test_a_plane_written_twice_in_one_window_withdraws_the_window_and_the_step_end_sends_all_of_it():
     from vllm_rlt_b200.pd import layer_watch
 

@@ -158,6 +158,7 @@ class PDStageConnector:
         self.transfer_cursor = 0
         self.prefill_tokens = 0
         self.stream_layers = 4  # layers per slice that ``layer_written`` lets go at once
+        self.stream_whole_planes = False  # True: planes before the last leave in one piece (fewer launches per step)
         self.layer_watch = None  # set by ``create`` when this worker reports its KV writes itself (pd/layer_watch.py)
         self.exporter = Exporter(self)
         self.importer = Importer(self)
@@ -196,6 +197,7 @@ class PDStageConnector:
 
         if layer_watch.wanted() and stage.accepts_prompt and layer_watch.eligible(connector):
             connector.layer_watch = layer_watch.LayerWatch(connector).install()
+            connector.stream_whole_planes = True
         return connector
 
     def startup_info(self):
@@ -526,6 +528,8 @@ class Exporter:
         if layer + 1 <= sent:
             raise ValueError("layers of a plane must be reported in increasing order")
         group = max(1, int(c.stream_layers))
+        if c.stream_whole_planes and plane + 1 < len(t.target_tables):
+            group = layers_total  # only the last plane's last slice is left after the step: earlier planes leave whole
         if layer + 1 - sent < group and layer + 1 < layers_total:
             return False
         if event is None:
