@@ -889,6 +889,8 @@ def suite_deployment(args):
         "transfer_seconds_sum": seconds,
         "gbps_while_transferring": (sent / seconds / 1e9) if seconds else None, "startup_s": startup,
         "layer_streaming": bool(args.stream), "streamed_slices": sum(m.get("streamed_slices", 0) for m in worker_metrics.values()),
+        "stream_host_ms_per_request": (sum(m.get("stream_host_seconds", 0.0) for m in worker_metrics.values()) * 1e3
+                                       / max(1, args.requests + 1)),
         "pulled_bytes": sum(m.get("bytes_received", 0) for m in worker_metrics.values()),
         "pull_device_seconds": sum(m.get("pull_seconds", 0.0) for m in worker_metrics.values()),
         # median over the pull launches of the run (the first one of a process carries the module load)

@@ -362,7 +362,7 @@ def test_a_watched_cache_reports_its_own_writes_and_the_step_end_sends_only_the_
     assert "_write_prepared" in p.pool.__dict__ and p.pool._write_prepared is not watch  # the stand-in of this test is back
 
 
-def test_planes_before_the_last_can_leave_whole_so_that_a_step_costs_fewer_launches():
+def test_planes_can_leave_whole_and_the_last_in_two_pieces_so_that_a_step_costs_few_launches():
     from vllm_rlt_b200.pd import layer_watch
 
     p, d = make_pair()
@@ -374,7 +374,7 @@ def test_planes_before_the_last_can_leave_whole_so_that_a_step_costs_fewer_launc
     traversal(p.pool, "s", 0, 0, 10)
     assert watch.reported == 1  # plane 0 in one piece, after its last layer
     traversal(p.pool, "s", 1, 0, 10)
-    assert watch.reported == 4  # the last plane layer by layer
+    assert watch.reported == 3  # the last plane in two pieces: layers 0-1, then the last layer
     request.num_prefilled_tokens, request.hidden_state = 10, torch.ones(16)
     p.connector.prefill_submitted(request, phase="PREFILL", start=0,
                                   progress=SimpleNamespace(chunk_complete=True, prompt_complete=True), event=None, stream=None)
@@ -382,7 +382,7 @@ def test_planes_before_the_last_can_leave_whole_so_that_a_step_costs_fewer_launc
     (commit,) = p.take("commit")
     d.connector.command(dict(kind="commit", tid="s", count=commit["count"]))
     settle(p, d)
-    assert commit["count"] == 5 and d.take("received")
+    assert commit["count"] == 4 and d.take("received")  # three early slices and the hidden row
     assert torch.equal(pool_rows(p.pool, p.pool.plane_block_tables("s"), 0, 10), pool_rows(d.pool, reserved["tables"], 0, 10))
 
 

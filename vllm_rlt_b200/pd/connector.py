@@ -158,7 +158,7 @@ class PDStageConnector:
         self.transfer_cursor = 0
         self.prefill_tokens = 0
         self.stream_layers = 4  # layers per slice that ``layer_written`` lets go at once
-        self.stream_whole_planes = False  # True: planes before the last leave in one piece (fewer launches per step)
+        self.stream_whole_planes = False  # True: a plane leaves in one piece, the last plane in two (few launches per step)
         self.layer_watch = None  # set by ``create`` when this worker reports its KV writes itself (pd/layer_watch.py)
         self.exporter = Exporter(self)
         self.importer = Importer(self)
@@ -255,6 +255,7 @@ class PDStageConnector:
         if self.layer_watch is not None:
             self.layer_watch.remove()
             metrics["streamed_slices"] = self.layer_watch.reported
+            metrics["stream_host_seconds"] = self.layer_watch.host_seconds
         received = getattr(t, "bytes_received", 0)
         if isinstance(received, int) and received:  # the pull direction: what this worker's GPU read, and for how long
             rates = sorted(getattr(t, "pull_rates", ()))
@@ -528,9 +529,14 @@ class Exporter:
         if layer + 1 <= sent:
             raise ValueError("layers of a plane must be reported in increasing order")
         group = max(1, int(c.stream_layers))
-        if c.stream_whole_planes and plane + 1 < len(t.target_tables):
-            group = layers_total  # only the last plane's last slice is left after the step: earlier planes leave whole
-        if layer + 1 - sent < group and layer + 1 < layers_total:
+        if c.stream_whole_planes:
+            # Only what is still to move when the step ends counts as latency: a plane leaves in one piece after its
+            # last layer, and the last plane in two, so that its final ``stream_layers`` layers are all that is left.
+            cut = layers_total - group
+            early = plane + 1 == len(t.target_tables) and layer + 1 == cut and cut > sent
+            if not early and layer + 1 < layers_total:
+                return False
+        elif layer + 1 - sent < group and layer + 1 < layers_total:
             return False
         if event is None:
             import torch

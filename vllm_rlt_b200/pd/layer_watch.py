@@ -23,6 +23,7 @@ next ``prefill_submitted`` sends whatever was not streamed, as it always does.
 from __future__ import annotations
 
 import os
+import time
 
 
 def wanted() -> bool:
@@ -52,6 +53,7 @@ class LayerWatch:
         self.plan_of = None   # the batch object the plan below was made for
         self.plan = ()        # [(request id, plane, first token, end token)]
         self.reported = 0     # slices that left early, for the metrics
+        self.host_seconds = 0.0  # time this object added to the forward, for the metrics
         self.event_factory = None  # None: the connector records a CUDA event on the current stream when a slice leaves
 
     def install(self) -> "LayerWatch":
@@ -70,12 +72,14 @@ class LayerWatch:
         rows = getattr(batch, "rows", None)
         if not rows or not self.connector.transfers:
             return
+        began = time.perf_counter()
         if self.plan_of is not batch:  # one descriptor serves every layer of a traversal: plan once
             self.plan_of, self.plan = batch, self._plan(batch)
         for request_id, plane, start, end in self.plan:
             event = self.event_factory() if self.event_factory is not None else None
             if self.connector.report_layer(request_id, plane, layer, start, end, event=event):
                 self.reported += 1
+        self.host_seconds += time.perf_counter() - began
 
     def _plan(self, batch):
         """``(request id, plane, first token, end token)`` for every (request, depth) of the batch whose rows are one
