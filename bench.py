@@ -825,7 +825,7 @@ def suite_deployment(args):
     os.environ["PYTHONPATH"] = os.pathsep.join([str(checkout), str(ROOT), os.environ.get("PYTHONPATH", "")])
     os.environ.setdefault("RLT_KV_DIRECTION", args.direction)
     if args.stream:  # the prefill worker reports its KV writes layer by layer (vllm_rlt_b200/pd/layer_watch.py)
-        os.environ["RLT_KV_STREAM"] = "1"
+        os.environ["RLT_KV_STREAM"] = "alternate" if args.stream == "alternate" else "1"
     from vllm_rlt import CacheConfig, SamplingParams, SchedulerConfig
     from vllm_rlt.models.ouro import OuroConfig
     from vllm_rlt.pd.config import PDConfig
@@ -872,6 +872,15 @@ def suite_deployment(args):
     tail = [(t["d_received"] - t["prefill_compute_completed"]) * 1e3 for t in marks]
     total = [(t["d_received"] - t["prefill_started"]) * 1e3 for t in marks]
     prefill = [(t["prefill_compute_completed"] - t["prefill_started"]) * 1e3 for t in marks]
+    halves = None
+    if args.stream == "alternate" and args.concurrency == 1:
+        # the prefill worker saw "warm" first, so r0, r2, ... streamed and r1, r3, ... did not
+        def stats(keep):
+            rows = [(tail[i], total[i], prefill[i]) for i in range(len(marks)) if keep(i)]
+            return {"requests": len(rows), "handoff_tail_ms_p50": statistics.median(r[0] for r in rows),
+                    "handoff_total_ms_p50": statistics.median(r[1] for r in rows),
+                    "prefill_ms_p50": statistics.median(r[2] for r in rows)} if rows else None
+        halves = {"streamed": stats(lambda i: i % 2 == 0), "not_streamed": stats(lambda i: i % 2 == 1)}
     sent = sum(m.get("bytes_sent", 0) for m in worker_metrics.values())
     seconds = sum(m.get("transfer_seconds", 0.0) for m in worker_metrics.values())
     per_request = args.tokens * config.total_ut_steps * 2 * config.num_hidden_layers * config.num_key_value_heads * config.head_dim * (
@@ -888,7 +897,7 @@ def suite_deployment(args):
         "bytes_sent": sent, "transfers": sum(m.get("transfers", 0) for m in worker_metrics.values()),
         "transfer_seconds_sum": seconds,
         "gbps_while_transferring": (sent / seconds / 1e9) if seconds else None, "startup_s": startup,
-        "layer_streaming": bool(args.stream), "streamed_slices": sum(m.get("streamed_slices", 0) for m in worker_metrics.values()),
+        "layer_streaming": args.stream or False, "alternate": halves, "streamed_slices": sum(m.get("streamed_slices", 0) for m in worker_metrics.values()),
         "stream_host_ms_per_request": (sum(m.get("stream_host_seconds", 0.0) for m in worker_metrics.values()) * 1e3
                                        / max(1, args.requests + 1)),
         "pulled_bytes": sum(m.get("bytes_received", 0) for m in worker_metrics.values()),
@@ -936,8 +945,9 @@ def main():
     ap.add_argument("--concurrency", type=int, default=1, help="--suite deployment: requests submitted at once")
     ap.add_argument("--chunk", type=int, default=2048, help="--suite deployment: prefill chunk size")
     ap.add_argument("--kv-dtype", default="auto", choices=["auto", "fp8_e4m3"], help="--suite deployment")
-    ap.add_argument("--stream", action="store_true",
-                    help="--suite deployment: stream finished layers behind the prefill (RLT_KV_STREAM=1 in the workers)")
+    ap.add_argument("--stream", nargs="?", const="all", default=None, choices=["all", "alternate"],
+                    help="--suite deployment: stream finished layers behind the prefill (RLT_KV_STREAM in the workers); "
+                         "'alternate' streams every second request, so that one process yields both figures")
     args = ap.parse_args()
     if args.suite is not None:
         {"kernels": suite_kernels, "peer": suite_peer, "deployment": suite_deployment}[args.suite](args)

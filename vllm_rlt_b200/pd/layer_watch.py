@@ -27,7 +27,13 @@ import time
 
 
 def wanted() -> bool:
-    return os.environ.get("RLT_KV_STREAM", "").strip().lower() in ("1", "true", "yes", "on")
+    return os.environ.get("RLT_KV_STREAM", "").strip().lower() in ("1", "true", "yes", "on", "alternate")
+
+
+def alternate() -> bool:
+    """``RLT_KV_STREAM=alternate``: every second request streams, the others leave at the chunk's end as usual. For
+    measuring what streaming costs and saves inside ONE process, where run-to-run differences cannot blur it."""
+    return os.environ.get("RLT_KV_STREAM", "").strip().lower() == "alternate"
 
 
 def eligible(connector) -> bool:
@@ -54,6 +60,8 @@ class LayerWatch:
         self.plan = ()        # [(request id, plane, first token, end token)]
         self.reported = 0     # slices that left early, for the metrics
         self.host_seconds = 0.0  # time this object added to the forward, for the metrics
+        self.alternate = alternate()
+        self.order = {}       # request id -> the order in which requests were first seen (alternate mode)
         self.event_factory = None  # None: the connector records a CUDA event on the current stream when a slice leaves
 
     def install(self) -> "LayerWatch":
@@ -76,6 +84,8 @@ class LayerWatch:
         if self.plan_of is not batch:  # one descriptor serves every layer of a traversal: plan once
             self.plan_of, self.plan = batch, self._plan(batch)
         for request_id, plane, start, end in self.plan:
+            if self.alternate and self.order.setdefault(request_id, len(self.order)) % 2 == 0:
+                continue  # even-numbered requests (the first is number 0) do not stream
             event = self.event_factory() if self.event_factory is not None else None
             if self.connector.report_layer(request_id, plane, layer, start, end, event=event):
                 self.reported += 1

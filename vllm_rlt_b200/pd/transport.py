@@ -442,12 +442,19 @@ class CudaBackend:
             target = np.asarray([r[1] for r in requests], dtype=np.int32)
         except (ValueError, OverflowError):
             return None
-        if source.ndim != 3 or target.ndim != 3 or source.shape[2] != target.shape[2] or source.shape[2] < 1:
-            return None
-        if source.shape[1] != src.num_planes or target.shape[1] != dst.num_planes:
+        if source.ndim != 3 or target.ndim != 3 or source.shape[1] != src.num_planes or target.shape[1] != dst.num_planes:
             return None
         begin = np.asarray([r[2] for r in requests], dtype=np.int64)
         end = np.asarray([r[3] for r in requests], dtype=np.int64)
+        # a decode worker reserves pages for the tokens it will generate, so its tables run past the prompt's: tables
+        # are only ever indexed by the pages a range touches, and both sides are cut to the shorter one
+        width = min(source.shape[2], target.shape[2])
+        if width < 1:
+            return None
+        if source.shape[2] != width:
+            source = np.ascontiguousarray(source[:, :, :width])
+        if target.shape[2] != width:
+            target = np.ascontiguousarray(target[:, :, :width])
         if self._host_limit is None:
             from ..kernels import kv_handoff as kh
 
