@@ -841,7 +841,8 @@ def suite_deployment(args):
     started = time.monotonic()
     with PDEngine(
         config,
-        pd_config=PDConfig(prefill_devices=(0,), decode_devices=(1,), startup_timeout=600, request_timeout=600),
+        pd_config=PDConfig(prefill_devices=(0,), decode_devices=(1,), startup_timeout=600, request_timeout=600,
+                           max_inflight_bytes=args.inflight_gib << 30),
         prefill_cache_config=cache,
         decode_cache_config=cache,
         prefill_scheduler_config=SchedulerConfig(max_num_seqs=8, max_num_batched_tokens=args.chunk, prefill_chunk_size=args.chunk),
@@ -945,6 +946,9 @@ def main():
     ap.add_argument("--concurrency", type=int, default=1, help="--suite deployment: requests submitted at once")
     ap.add_argument("--chunk", type=int, default=2048, help="--suite deployment: prefill chunk size")
     ap.add_argument("--kv-dtype", default="auto", choices=["auto", "fp8_e4m3"], help="--suite deployment")
+    ap.add_argument("--inflight-gib", type=int, default=2,
+                    help="--suite deployment: PDConfig.max_inflight_bytes in GiB (tickets are only returned between steps, so a\n"
+                         "request that streams during one step needs its whole KV inside this budget)")
     ap.add_argument("--stream", nargs="?", const="all", default=None, choices=["all", "alternate"],
                     help="--suite deployment: stream finished layers behind the prefill (RLT_KV_STREAM in the workers); "
                          "'alternate' streams every second request, so that one process yields both figures")
