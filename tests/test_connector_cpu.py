@@ -412,6 +412,23 @@ def test_a_plane_written_twice_in_one_window_withdraws_the_window_and_the_step_e
     assert torch.equal(pool_rows(p.pool, p.pool.plane_block_tables("s"), 0, 6), pool_rows(d.pool, reserved["tables"], 0, 6))
 
 
+def test_the_watch_reads_requests_planes_and_token_runs_off_a_batch():
+    from vllm_rlt_b200.pd.layer_watch import LayerWatch
+
+    watch = LayerWatch.__new__(LayerWatch)
+    watch.cache = SimpleNamespace(_plane=lambda depth: depth)
+    a, b = object(), object()
+    one = SimpleNamespace(rows=tuple((a, 2, t) for t in range(40, 140)), allocations=(("s", a),))
+    assert watch._plan(one) == (("s", 2, 40, 140),)
+    gap = SimpleNamespace(rows=tuple((a, 2, t) for t in (*range(40, 90), *range(91, 141))), allocations=(("s", a),))
+    assert watch._plan(gap) == ()  # not one run of tokens: nothing is reported, the chunk leaves at its end
+    mixed = SimpleNamespace(rows=tuple((a, 1 + (t > 100), t) for t in range(40, 140)), allocations=(("s", a),))
+    assert watch._plan(mixed) == ()  # two depths in one batch of one request
+    two = SimpleNamespace(rows=tuple((a, 1, t) for t in range(100, 1100)) + tuple((b, 0, t) for t in range(0, 1000))
+                          + tuple((b, 1, t) for t in (5, 7)), allocations=(("s", a), ("q", b)))
+    assert sorted(watch._plan(two)) == [("q", 0, 0, 1000), ("s", 1, 100, 1100)]  # q's two stray rows at depth 1 are no run
+
+
 def test_the_watch_is_refused_where_depths_share_a_plane_or_prefill_is_wavefront_chunked(monkeypatch):
     from vllm_rlt_b200.pd import layer_watch
 
