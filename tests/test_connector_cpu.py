@@ -412,6 +412,38 @@ def test_a_plane_written_twice_in_one_window_withdraws_the_window_and_the_step_e
     assert torch.equal(pool_rows(p.pool, p.pool.plane_block_tables("s"), 0, 6), pool_rows(d.pool, reserved["tables"], 0, 6))
 
 
+@pytest.mark.parametrize("direction", DIRECTIONS)
+def test_a_step_that_streams_more_than_the_budget_holds_gets_its_tickets_back_inside_the_step(direction):
+    """One plane of this request is 1,920 bytes and the budget 2,000: without returning tickets inside the step the
+    second plane would wait for the next progress(); the watch's report polls when half the budget is taken."""
+    from vllm_rlt_b200.pd import layer_watch
+
+    config = PDConfig(transfer_chunk_bytes=1000, max_inflight_bytes=2000)
+    p, d = make_pair(config, direction=direction)
+    p.transport.device_ordered = True  # as on a device: submissions leave when they are reported, not at the next progress()
+    cache_that_writes(p.pool)
+    watch = layer_watch.LayerWatch(p.connector).install()
+    watch.event_factory = FakeEvent
+    p.connector.stream_layers, p.connector.stream_whole_planes = 1, True
+    request, reserved = handoff_ready(p, d, "s", 10)
+    t = p.connector.transfers["s"]
+    traversal(p.pool, "s", 0, 0, 10)
+    assert watch.reported == 1 and not t.chunks  # plane 0 is on its way
+    if direction == "pull":
+        d.connector.progress()  # the decode worker reads the offered chunk and says so
+    traversal(p.pool, "s", 1, 0, 10)
+    assert watch.reported == 3 and not t.chunks  # both pieces of plane 1 left during the step: nothing is queued
+    request.num_prefilled_tokens, request.hidden_state = 10, torch.ones(16)
+    p.connector.prefill_submitted(request, phase="PREFILL", start=0,
+                                  progress=SimpleNamespace(chunk_complete=True, prompt_complete=True), event=None, stream=None)
+    settle(p, d)
+    (commit,) = p.take("commit")
+    d.connector.command(dict(kind="commit", tid="s", count=commit["count"]))
+    settle(p, d)
+    assert d.take("received")
+    assert torch.equal(pool_rows(p.pool, p.pool.plane_block_tables("s"), 0, 10), pool_rows(d.pool, reserved["tables"], 0, 10))
+
+
 def test_the_watch_reads_requests_planes_and_token_runs_off_a_batch():
     from vllm_rlt_b200.pd.layer_watch import LayerWatch
 

@@ -160,6 +160,7 @@ class PDStageConnector:
         self.stream_layers = 4  # layers per slice that ``layer_written`` lets go at once
         self.stream_whole_planes = False  # True: a plane leaves in one piece, the last plane in two (few launches per step)
         self.layer_watch = None  # set by ``create`` when this worker reports its KV writes itself (pd/layer_watch.py)
+        self._early_arrivals: list = []  # arrivals a poll inside a step brought in (see ``report_layer``)
         self.exporter = Exporter(self)
         self.importer = Importer(self)
         self._control = {
@@ -319,6 +320,11 @@ class PDStageConnector:
             return False
         if not 0 <= plane < len(t.target_tables) or not 0 <= layer < self.transport.info["num_layers"]:
             return False
+        if 2 * self.transport.inflight_bytes > self.config.max_inflight_bytes:
+            # tickets are normally returned by progress(), between steps; a step that streams more than the budget
+            # holds would stall its own later slices, so finished ones are returned here and what the poll brought
+            # in is kept for the next progress()
+            self._early_arrivals += self.transport.poll()[1]
         return self.exporter.layer_written(t, plane, layer, event, start, end)
 
     # ------------------------------------------------------------------ planning
@@ -434,6 +440,8 @@ class PDStageConnector:
     def progress(self):
         self.cache.poll_prefixes()
         _, arrivals = self.transport.poll()
+        if self._early_arrivals:
+            arrivals, self._early_arrivals = self._early_arrivals + list(arrivals), []
         self.importer.book(arrivals)
         turn = list(self.transfers.values())
         if turn:
