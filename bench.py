@@ -947,8 +947,7 @@ def main():
     ap.add_argument("--chunk", type=int, default=2048, help="--suite deployment: prefill chunk size")
     ap.add_argument("--kv-dtype", default="auto", choices=["auto", "fp8_e4m3"], help="--suite deployment")
     ap.add_argument("--inflight-gib", type=int, default=2,
-                    help="--suite deployment: PDConfig.max_inflight_bytes in GiB (tickets are only returned between steps, so a\n"
-                         "request that streams during one step needs its whole KV inside this budget)")
+                    help="--suite deployment: PDConfig.max_inflight_bytes in GiB")
     ap.add_argument("--stream", nargs="?", const="all", default=None, choices=["all", "alternate"],
                     help="--suite deployment: stream finished layers behind the prefill (RLT_KV_STREAM in the workers); "
                          "'alternate' streams every second request, so that one process yields both figures")
