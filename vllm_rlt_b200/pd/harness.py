@@ -23,8 +23,6 @@ import random
 import statistics
 import time
 
-import numpy as np
-
 MODES = {"exit_only": 2, "dedup": 1, "all": 0}
 
 
