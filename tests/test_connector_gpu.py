@@ -213,6 +213,81 @@ def test_layers_reported_by_the_producer_stream_through_the_connector_and_the_ta
 
 
 @pytest.mark.parametrize("direction", DIRECTIONS)
+def test_a_watched_cache_streams_rows_that_are_only_written_while_the_step_runs(direction):
+    """The layer watch on a real device. The source pool starts EMPTY (zeros); a stand-in for the cache manager's
+    prepared write copies each layer's rows into it on the compute stream, behind a sleep, and the watch reports the
+    write from inside that call with an event it records itself. A slice that did not wait for its event would carry
+    zeros: the destination must equal the oracle's handoff of the complete source, byte for byte."""
+    import numpy as np
+
+    from oracle import handoff_oracle as ho
+    from vllm_rlt_b200.pd import layer_watch
+    from vllm_rlt_b200.pd.config import PDConfig
+
+    shape = dict(shape=(8, 4, 64), page=16, planes=2, blocks=48)
+    p = Worker("prefill", PDConfig(), 0, seed=1, device="cuda:0", direction=direction, **shape)
+    d = Worker("decode", PDConfig(), 1, seed=2, device="cuda:0", direction=direction, **shape)
+    p.connector.command(dict(kind="connect", peers=[d.transport.info]))
+    d.connector.command(dict(kind="connect", peers=[p.transport.info]))
+    tokens = 70
+    d.connector.command(dict(kind="reserve", tid="req", tokens=list(range(tokens)), params=Params(), peer="prefill-0"))
+    (reserved,) = d.take("reserved")
+    p.connector.command(dict(kind="prefill", tid="req", tokens=list(range(tokens)), params=Params(), peer="decode-0",
+                             tables=reserved["tables"], slot=reserved["slot"], cached_tokens=0))
+    request = p.engine.scheduler.requests["req"]
+    P, D = oracle_of(p, 1 << 30), oracle_of(d, 1 << 40)
+    tables = p.pool.plane_block_tables("req")
+    ho.handoff_rows(P, D, tables, reserved["tables"], 0, tokens)
+    full = [p.pool.key_cache.clone(), p.pool.value_cache.clone()]
+    for t in (p.pool.key_cache, p.pool.value_cache):
+        t.zero_()
+    positions = torch.arange(tokens, device="cuda:0")
+
+    def write_prepared(layer, batch, k, v):  # what a model's attention layer does: this layer's rows of this depth
+        plane = batch.rows[0][1]
+        blocks = torch.tensor(tables[plane], device="cuda:0")[positions // 16]
+        torch.cuda._sleep(int(0.003 * 1.9e9))
+        for cache, source in zip((p.pool.key_cache, p.pool.value_cache), full):
+            cache[blocks, layer, positions % 16] = source[blocks, layer, positions % 16]
+
+    p.pool.max_loops, p.pool._plane, p.pool._write_prepared = 2, (lambda depth: depth), write_prepared
+    assert layer_watch.eligible(p.connector)
+    watch = layer_watch.LayerWatch(p.connector).install()
+    p.connector.stream_layers, p.connector.stream_whole_planes = 2, True
+    compute = torch.cuda.Stream()
+    allocation = object()
+    with torch.cuda.stream(compute):
+        for depth in range(2):
+            batch = SimpleNamespace(rows=tuple((allocation, depth, t) for t in range(tokens)), allocations=(("req", allocation),))
+            for layer in range(8):
+                p.pool._write_prepared(layer, batch, None, None)
+        end_of_compute = torch.cuda.Event()
+        end_of_compute.record(compute)
+    transfer = p.connector.transfers["req"]
+    assert watch.reported == 3 and not transfer.chunks  # plane 0 whole, plane 1 in two pieces, each behind its own event
+    request.num_prefilled_tokens, request.hidden_state = tokens, torch.full((16,), 2.0, device="cuda:0")
+    p.connector.prefill_submitted(request, phase="PREFILL", start=0,
+                                  progress=SimpleNamespace(chunk_complete=True, prompt_complete=True),
+                                  event=end_of_compute, stream=compute)
+    pump(p, d, lambda: bool([m for m in p.messages if m["kind"] == "commit"]))
+    (commit,) = p.take("commit")
+    assert commit["count"] == 4  # the three slices and the hidden row
+    d.connector.command(dict(kind="commit", tid="req", count=4))
+    pump(p, d, lambda: bool([m for m in d.messages if m["kind"] == "received"]))
+    torch.cuda.synchronize()
+    for got, want in zip(device_bytes(d.pool), (D.key.data.reshape(-1), D.value.data.reshape(-1))):
+        assert np.array_equal(got, want)
+    d.engine.admit("req")
+    p.connector.command(dict(kind="ack", tid="req"))
+    pump(p, d, lambda: not p.connector.transfers)
+    del d.engine.scheduler.requests["req"]
+    d.connector.output_finished("req")
+    watch.remove()
+    p.connector.close()
+    d.connector.close()
+
+
+@pytest.mark.parametrize("direction", DIRECTIONS)
 def test_a_prefix_resident_on_the_decode_side_is_reserved_skipped_and_left_untouched(direction):
     """The decode-side reservation hook end to end on the device (mirrors tests/test_pd.py:626-687 and
     tests/test_stage_engine.py:595-648 of the reference): D imports a prompt, which publishes its pages; a second
