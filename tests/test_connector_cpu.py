@@ -444,6 +444,36 @@ def test_a_step_that_streams_more_than_the_budget_holds_gets_its_tickets_back_in
     assert torch.equal(pool_rows(p.pool, p.pool.plane_block_tables("s"), 0, 10), pool_rows(d.pool, reserved["tables"], 0, 10))
 
 
+def test_an_error_inside_the_watch_stops_streaming_and_never_reaches_the_forward():
+    from vllm_rlt_b200.pd import layer_watch
+
+    p, d = make_pair()
+    cache_that_writes(p.pool)
+    watch = layer_watch.LayerWatch(p.connector).install()
+    watch.event_factory = FakeEvent
+    p.connector.stream_layers = 2
+    request, reserved = handoff_ready(p, d, "s", 10)
+    traversal(p.pool, "s", 0, 0, 10)
+    assert watch.reported == 2
+    original = p.connector.report_layer
+    p.connector.report_layer = lambda *a, **k: (_ for _ in ()).throw(RuntimeError("boom"))
+    traversal(p.pool, "s", 1, 0, 10)  # the writes still happen, nothing is raised
+    p.connector.report_layer = original
+    assert watch.failure == "RuntimeError: boom" and p.pool.writes == [0, 1, 2] * 2
+    assert p.connector.transfers["s"].streamed_window is None
+    traversal(p.pool, "s", 1, 0, 10)
+    assert watch.reported == 2  # it stays off
+    request.num_prefilled_tokens, request.hidden_state = 10, torch.ones(16)
+    p.connector.prefill_submitted(request, phase="PREFILL", start=0,
+                                  progress=SimpleNamespace(chunk_complete=True, prompt_complete=True), event=None, stream=None)
+    settle(p, d)
+    (commit,) = p.take("commit")
+    d.connector.command(dict(kind="commit", tid="s", count=commit["count"]))
+    settle(p, d)
+    assert d.take("received")
+    assert torch.equal(pool_rows(p.pool, p.pool.plane_block_tables("s"), 0, 10), pool_rows(d.pool, reserved["tables"], 0, 10))
+
+
 def test_the_watch_reads_requests_planes_and_token_runs_off_a_batch():
     from vllm_rlt_b200.pd.layer_watch import LayerWatch
 

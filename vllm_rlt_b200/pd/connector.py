@@ -257,6 +257,8 @@ class PDStageConnector:
             self.layer_watch.remove()
             metrics["streamed_slices"] = self.layer_watch.reported
             metrics["stream_host_seconds"] = self.layer_watch.host_seconds
+            if self.layer_watch.failure is not None:
+                metrics["stream_failure"] = self.layer_watch.failure
         received = getattr(t, "bytes_received", 0)
         if isinstance(received, int) and received:  # the pull direction: what this worker's GPU read, and for how long
             rates = sorted(getattr(t, "pull_rates", ()))

@@ -60,6 +60,7 @@ class LayerWatch:
         self.plan = ()        # [(request id, plane, first token, end token)]
         self.reported = 0     # slices that left early, for the metrics
         self.host_seconds = 0.0  # time this object added to the forward, for the metrics
+        self.failure = None   # what made this object stop reporting, if anything did
         self.alternate = alternate()
         self.order = {}       # request id -> the order in which requests were first seen (alternate mode)
         self.event_factory = None  # None: the connector records a CUDA event on the current stream when a slice leaves
@@ -80,15 +81,25 @@ class LayerWatch:
         rows = getattr(batch, "rows", None)
         if not rows or not self.connector.transfers:
             return
+        if self.failure is not None:
+            return
         began = time.perf_counter()
-        if self.plan_of is not batch:  # one descriptor serves every layer of a traversal: plan once
-            self.plan_of, self.plan = batch, self._plan(batch)
-        for request_id, plane, start, end in self.plan:
-            if self.alternate and self.order.setdefault(request_id, len(self.order)) % 2 == 0:
-                continue  # even-numbered requests (the first is number 0) do not stream
-            event = self.event_factory() if self.event_factory is not None else None
-            if self.connector.report_layer(request_id, plane, layer, start, end, event=event):
-                self.reported += 1
+        try:
+            if self.plan_of is not batch:  # one descriptor serves every layer of a traversal: plan once
+                self.plan_of, self.plan = batch, self._plan(batch)
+            for request_id, plane, start, end in self.plan:
+                if self.alternate and self.order.setdefault(request_id, len(self.order)) % 2 == 0:
+                    continue  # even-numbered requests (the first is number 0) do not stream
+                event = self.event_factory() if self.event_factory is not None else None
+                if self.connector.report_layer(request_id, plane, layer, start, end, event=event):
+                    self.reported += 1
+        except Exception as error:  # noqa: BLE001 - the KV write itself succeeded: the model's forward must go on
+            # Streaming is an extra. Whatever went wrong, stop reporting for good and take back what was streamed of
+            # the windows that are open, so that each leaves whole at its chunk's end, where the ordinary path runs
+            # (and raises, if the cause is still there, in a place that is prepared for it).
+            self.failure = f"{type(error).__name__}: {error}"
+            for transfer in self.connector.transfers.values():
+                transfer.streamed_window, transfer.streamed_layers = None, {}
         self.host_seconds += time.perf_counter() - began
 
     def _plan(self, batch):
